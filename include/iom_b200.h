@@ -1,0 +1,222 @@
+/*
+ * iom_b200 — C ABI of the B200 (sm_100a) device tensor-op kernels for IOM.
+ *
+ * This is the drop-in boundary: plain pointers, sizes and POD descriptors, no
+ * C++ or torch types. Every entry point replaces one device operation of the
+ * reference CUDA backend (rlewczuk/iom, src/cuda + src/shared) and takes the
+ * same information the reference's backend hooks receive in their value
+ * snapshots. Reference citations are paths inside the reference project.
+ *
+ * Conventions shared by all entry points
+ *   - Tensors live in the reference's standard 16x16 tiled layout
+ *     (src/tensor.cpp:136-164): leading plane, tile row, tile column, row in
+ *     tile, column in tile; both matrix axes padded to multiples of 16. Padding
+ *     slots are never read for arithmetic and never written.
+ *   - `stream` is a cudaStream_t passed as void*. Launches are asynchronous on
+ *     that stream. No entry point allocates, frees or synchronises.
+ *   - Return value: IOMB_OK or a positive iomb_status. The codes are the
+ *     magnitudes of the reference's negative OidError values
+ *     (include/iom/oid.hpp:16-23), so a host layer maps status s to oid -s.
+ *     iomb_last_error() returns a thread-local description of the last failure.
+ *   - There is no CPU fallback: without a CUDA device every compute entry point
+ *     returns IOMB_ERR_DEVICE.
+ */
+#ifndef IOM_B200_H
+#define IOM_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define IOMB_MAX_RANK 8
+#define IOMB_MAX_LEADING 6
+#define IOMB_TILE 16
+
+/* Mirrors OidError (include/iom/oid.hpp:16-23) with the sign dropped. */
+typedef enum iomb_status {
+    IOMB_OK = 0,
+    IOMB_ERR_INVALID_ARGUMENT = 1,
+    IOMB_ERR_UNSUPPORTED = 2,
+    IOMB_ERR_OVERFLOW = 3,
+    IOMB_ERR_RESOURCE_EXHAUSTED = 4,
+    IOMB_ERR_DEVICE = 5,
+    IOMB_ERR_INTERNAL = 6
+} iomb_status;
+
+/* Leaf encodings with the ordinals of iom::DataType (include/iom/tensor.hpp:10-32). */
+typedef enum iomb_dtype {
+    IOMB_BOOL = 0,
+    IOMB_I2 = 1, IOMB_U2 = 2, IOMB_I4 = 3, IOMB_U4 = 4,
+    IOMB_I8 = 5, IOMB_U8 = 6, IOMB_I16 = 7, IOMB_U16 = 8,
+    IOMB_I32 = 9, IOMB_U32 = 10, IOMB_I64 = 11, IOMB_U64 = 12,
+    IOMB_F4_E2M1 = 13, IOMB_F6_E2M3 = 14, IOMB_F6_E3M2 = 15,
+    IOMB_F8_E4M3FN = 16, IOMB_F8_E5M2 = 17, IOMB_F8_E8M0 = 18,
+    IOMB_F16 = 19, IOMB_BF16 = 20, IOMB_F32 = 21, IOMB_F64 = 22
+} iomb_dtype;
+
+/* DeviceOps::BinaryOperation (include/iom/iom.hpp:381). */
+typedef enum iomb_binary_op {
+    IOMB_ADD = 0,
+    IOMB_MUL = 1
+} iomb_binary_op;
+
+/*
+ * Value snapshot of one tensor view: what BinaryViewSnapshot / CopyViewSnapshot /
+ * CacheAppendViewSnapshot carry (include/iom/iom.hpp:382-426).
+ *   base           owner storage (device pointer, at least 32-byte aligned)
+ *   storage_bytes  bytes the owner reserves (TensorSpec::tiled_storage_nbytes)
+ *   dims           full logical shape, rank 2..8; dims[rank-2], dims[rank-1]
+ *                  are the owner's matrix extents (views never transform them)
+ *   plane_offset,
+ *   plane_strides  in whole owner planes, one stride per leading axis
+ */
+typedef struct iomb_view {
+    void* base;
+    uint64_t storage_bytes;
+    uint32_t dtype;
+    uint32_t rank;
+    uint64_t dims[IOMB_MAX_RANK];
+    uint64_t plane_offset;
+    uint64_t plane_strides[IOMB_MAX_LEADING];
+} iomb_view;
+
+/* RMSNorm accumulation order (see iomb_rmsnorm). */
+typedef enum iomb_rms_order {
+    /* 16 column accumulators per row, each summed in tile order, then the fixed
+     * tree ((l0+l4)+l8)+l12 ... of src/cpu/avx512_bf16_rmsnorm_reduction.cpp:69-81.
+     * Bit-identical to the reference's AVX-512 BF16 CPU build for BF16. */
+    IOMB_RMS_LANES16 = 0,
+    /* One accumulator per row walking the features in order: the portable CPU
+     * recurrence (src/cpu/queue.cpp:1187-1196). Bit-identical to it. Slower. */
+    IOMB_RMS_SEQUENTIAL = 1
+} iomb_rms_order;
+
+const char* iomb_last_error(void);
+
+/* Library/ABI version, bumped when a struct or signature changes. */
+uint32_t iomb_abi_version(void);
+
+/* Pure helpers of the layout contract (no device needed). */
+uint32_t iomb_dtype_bits(uint32_t dtype);                 /* detail::leaf_bits, src/tensor.cpp:107-134 */
+int iomb_tiled_storage_nbytes(const uint64_t* dims, uint32_t rank, uint32_t dtype,
+                              uint64_t* out_bytes);      /* TensorSpec::tiled_storage_nbytes, src/tensor.cpp:95-102 */
+int iomb_logical_nbytes(const uint64_t* dims, uint32_t rank, uint32_t dtype,
+                        uint64_t* out_bytes);            /* TensorSpec::logical_nbytes, src/tensor.cpp:88-93 */
+uint64_t iomb_plane_slot(uint64_t rows, uint64_t columns, uint64_t plane,
+                         uint64_t row, uint64_t column); /* detail::standard_plane_slot, src/tensor.cpp:136-164 */
+
+/*
+ * out = lhs (+|*) rhs with right-aligned broadcasting.
+ * Replaces GpuQueue::binary_impl + grid_stride_binary_kernel / alias_safe_binary_kernel
+ * (src/shared/gpu_queue_operations.inl:65-124,756-818; src/shared/standard_tiled_add.inl:206-464);
+ * admission rules of DeviceOps::validate_binary (src/device_ops_binary.cpp:102-181).
+ * Leaves: I32/U32 (wrap), F32, BF16. Arithmetic equals the scalar codec
+ * (src/shared/scalar_binary_codec.hpp:120-178): IEEE binary32 op, one RNE encode,
+ * every NaN result is the positive quiet NaN (0x7FC00000 / 0x7FC0).
+ * Exact in-place alias (out is the same view as an input) is allowed.
+ */
+int iomb_binary(int op, const iomb_view* lhs, const iomb_view* rhs,
+                const iomb_view* out, void* stream);
+
+/*
+ * out[..., r, :] = x[..., r, :] / sqrt(mean(x[..., r, :]^2) + eps) * scale[0, :]
+ * Replaces GpuQueue::rmsnorm_impl + standard_tiled_rmsnorm_kernel
+ * (src/shared/gpu_queue_operations.inl:206-267,841-869; src/shared/standard_tiled_rmsnorm.inl:437-637);
+ * arithmetic of rmsnorm_plane (src/cpu/queue.cpp:1145-1244): FP32 sum of rounded
+ * squares, sum/F, +eps, 1/sqrtf (true division), (x*inv)*w, NaN sign cleared,
+ * one RNE encode. Leaves: BF16, F32. `order` is an iomb_rms_order.
+ */
+int iomb_rmsnorm(const iomb_view* x, const iomb_view* scale, const iomb_view* out,
+                 float eps, int order, void* stream);
+
+/*
+ * Fused residual add + RMSNorm: sum = x + residual (stored, rounded to the leaf),
+ * out = rmsnorm(sum, scale). Results equal iomb_binary(ADD) followed by
+ * iomb_rmsnorm on the stored sum; the rounded residual is always materialised
+ * (docs/ARCHITECTURE.md:465-476). No counterpart in the reference: its session
+ * issues the two operations separately (src/session.cpp:2500-2503,1996-2000).
+ * `sum` may alias `x` or `residual` exactly; `out` must not alias anything.
+ */
+int iomb_add_rmsnorm(const iomb_view* x, const iomb_view* residual,
+                     const iomb_view* scale, const iomb_view* sum,
+                     const iomb_view* out, float eps, int order, void* stream);
+
+/*
+ * Bit-exact copy between two views of identical specification.
+ * Replaces GpuQueue copy path + grid_stride_copy_kernel
+ * (src/shared/standard_tiled_copy_metadata.inl:177-282; admission src/device_ops_copy.cpp:17-52).
+ * Any byte-multiple leaf (8/16/32/64 bits). An identical window is a no-op.
+ */
+int iomb_copy(const iomb_view* source, const iomb_view* destination, void* stream);
+
+/*
+ * BF16 <-> F32 conversion between views of identical logical shape.
+ * No counterpart operation in the reference; semantics are the scalar codec's
+ * decode/encode (src/shared/scalar_binary_codec.hpp:45-108): BF16->F32 exact
+ * widening, F32->BF16 round-to-nearest-even with overflow to infinity and
+ * gradual underflow; a NaN converts to the positive quiet NaN of the target.
+ */
+int iomb_cast(const iomb_view* source, const iomb_view* destination, void* stream);
+
+/*
+ * out[b, r, f] = table[indices[b, 0, r], f] (raw bits).
+ * Replaces GpuQueue::embedding_impl + embedding_word_kernel and its status protocol
+ * (src/shared/standard_tiled_embedding.inl:117-199; src/shared/gpu_queue_operations.inl:870-919;
+ * admission src/device_ops_embedding.cpp:93-162). `status` points at a 4-byte
+ * device word inside the caller's {32,32} workspace: the call resets it to 0 in
+ * stream order and the kernel sets it to 1 when any index is negative or >= V;
+ * such rows are not written and no table address is formed for them.
+ * Payload: byte-multiple leaves. Index: I8..U64.
+ */
+int iomb_embedding(const iomb_view* table, const iomb_view* indices,
+                   const iomb_view* out, uint32_t* status, void* stream);
+
+/*
+ * destination[..., h, a + r, d] = source[..., h, r, d] (raw bits); only the
+ * appended rows are touched.
+ * Replaces cache_append_kernel (src/cuda/copy.cu:111-338); admission
+ * src/device_ops_cache_append.cpp:157-269 (a <= C, R <= C - a).
+ */
+int iomb_cache_append(const iomb_view* source, const iomb_view* destination,
+                      uint64_t a, void* stream);
+
+/*
+ * Batched variant with one row offset per index of the first leading axis:
+ * destination[b, ..., a[b] + r, d] = source[b, ..., r, d]. `positions` is a
+ * device array of dims[0] uint32 values. `status` (device word) is reset to 0
+ * and set to 1 when some a[b] + R exceeds the cache length; that b is skipped.
+ * No counterpart in the reference, whose call carries one scalar offset
+ * (include/iom/iom.hpp:179-185); results equal dims[0] reference calls on
+ * select(0, b) views.
+ */
+int iomb_cache_append_batched(const iomb_view* source, const iomb_view* destination,
+                              const uint32_t* positions, uint32_t* status, void* stream);
+
+/*
+ * Whole-view sum of squares in FP32 with a fixed, launch-independent order.
+ * No counterpart in the reference. `scratch` holds iomb_sumsq_scratch_bytes()
+ * bytes of device memory (per-CTA partials); `result` receives one float.
+ * Leaves: BF16, F32.
+ */
+uint64_t iomb_sumsq_scratch_bytes(void);
+int iomb_sumsq(const iomb_view* x, void* scratch, float* result, void* stream);
+
+/*
+ * Host-layout <-> tiled conversion on the device.
+ * Replaces scatter_plane_kernel / gather_plane_kernel and their per-plane launch
+ * loops (src/shared/standard_tiled_copy.inl:286-441). `staging` is a device
+ * buffer holding the view's logical row-major payload (exactly
+ * logical_nbytes, LSB-first packed; include/iom/tensor.hpp:330-342).
+ * Byte-multiple leaves.
+ */
+int iomb_scatter(const iomb_view* destination, const void* staging, void* stream);
+int iomb_gather(const iomb_view* source, void* staging, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* IOM_B200_H */

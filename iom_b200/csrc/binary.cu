@@ -1,0 +1,342 @@
+// Elementwise ADD / MUL with right-aligned broadcasting on tiled storage.
+//
+// Replaces grid_stride_binary_kernel / alias_safe_binary_kernel of the
+// reference (src/shared/standard_tiled_add.inl:206-464). Two kernels:
+//
+//   binary_linear_kernel  every operand has the result's shape, tile-multiple
+//                         extents and dense planes: the three storages are
+//                         walked as one linear stream of 16-byte vectors.
+//   binary_tiled_kernel   everything else: a warp owns a run of tiles of one
+//                         16-row band; broadcast operands are fetched once per
+//                         tile (row vector) or once per band (column scalar),
+//                         logical bounds mask the stores so padding is never
+//                         written.
+//
+// Arithmetic: IEEE binary32 add/mul without contraction, one RNE encode for
+// BF16, canonical positive quiet NaN (src/shared/scalar_binary_codec.hpp:120-178).
+// Integers wrap. Each lane reads its inputs before it stores the same slots, so
+// the exact in-place alias the reference handles with a shared-memory snapshot
+// needs no special path here.
+#include "host.hpp"
+
+namespace iomb {
+
+enum class Leaf : int { I32 = 0, F32 = 1, BF16 = 2 };
+
+template <Leaf L, int OP>
+__device__ __forceinline__ uint32_t apply_word(uint32_t a, uint32_t b) {
+    if constexpr (L == Leaf::I32) {
+        return OP == IOMB_ADD ? a + b : a * b;
+    } else if constexpr (L == Leaf::F32) {
+        const float x = __uint_as_float(a), y = __uint_as_float(b);
+        const float r = OP == IOMB_ADD ? __fadd_rn(x, y) : __fmul_rn(x, y);
+        return f32_canonical_bits(r);
+    } else {
+        const float lo = OP == IOMB_ADD ? __fadd_rn(bf16_lo(a), bf16_lo(b))
+                                        : __fmul_rn(bf16_lo(a), bf16_lo(b));
+        const float hi = OP == IOMB_ADD ? __fadd_rn(bf16_hi(a), bf16_hi(b))
+                                        : __fmul_rn(bf16_hi(a), bf16_hi(b));
+        return pack_bf16x2_canonical(lo, hi);
+    }
+}
+
+template <Leaf L, int OP>
+__device__ __forceinline__ uint4 apply_vector(uint4 a, uint4 b) {
+    return make_uint4(apply_word<L, OP>(a.x, b.x), apply_word<L, OP>(a.y, b.y),
+                      apply_word<L, OP>(a.z, b.z), apply_word<L, OP>(a.w, b.w));
+}
+
+// ---- linear stream --------------------------------------------------------
+
+constexpr int kLinearThreads = 256;
+constexpr int kLinearUnroll = 4;
+
+template <Leaf L, int OP>
+__global__ void __launch_bounds__(kLinearThreads)
+binary_linear_kernel(const uint4* __restrict__ lhs, const uint4* __restrict__ rhs,
+                     uint4* __restrict__ out, uint64_t vectors) {
+    const uint64_t stride = static_cast<uint64_t>(gridDim.x) * kLinearThreads;
+    uint64_t index = static_cast<uint64_t>(blockIdx.x) * kLinearThreads + threadIdx.x;
+    // Unrolled body: kLinearUnroll independent 16-byte loads per operand in flight.
+    for (; index + stride * (kLinearUnroll - 1) < vectors; index += stride * kLinearUnroll) {
+        uint4 a[kLinearUnroll], b[kLinearUnroll];
+#pragma unroll
+        for (int u = 0; u < kLinearUnroll; ++u) {
+            a[u] = load_u4_stream(lhs + index + stride * u);
+            b[u] = load_u4_stream(rhs + index + stride * u);
+        }
+#pragma unroll
+        for (int u = 0; u < kLinearUnroll; ++u) {
+            store_u4_stream(out + index + stride * u, apply_vector<L, OP>(a[u], b[u]));
+        }
+    }
+    for (; index < vectors; index += stride) {
+        store_u4_stream(out + index,
+                        apply_vector<L, OP>(load_u4_stream(lhs + index),
+                                            load_u4_stream(rhs + index)));
+    }
+}
+
+// ---- tiled general kernel --------------------------------------------------
+
+struct BinaryParams {
+    Operand lhs;
+    Operand rhs;
+    Operand out;
+    Leading leading;
+    uint32_t rows;        // result rows
+    uint32_t cols;        // result columns
+    uint32_t tile_rows;   // result tile rows
+    uint32_t tile_cols;   // result tile columns
+    uint32_t run_tiles;   // tiles one warp handles per work item
+    uint32_t runs;        // work items per band
+    uint64_t items;       // planes * tile_rows * runs
+};
+
+constexpr int kTiledThreads = 256;
+constexpr int kTiledWarps = kTiledThreads / 32;
+
+// Loads one operand's 16-byte vector for (tile row tr, tile column tc, slot
+// offset `slot` inside the tile). ELEM is the leaf size in bytes. A broadcast
+// operand replicates its row 0 / column 0 value into the vector.
+template <int ELEM>
+__device__ __forceinline__ uint4 load_operand(
+        const Operand& operand, uint64_t plane, uint32_t tr, uint32_t tc, uint32_t slot) {
+    constexpr uint32_t kTileBytes = kTileSlots * ELEM;
+    constexpr uint32_t kPerVector = 16 / ELEM;
+    const uint32_t row = slot / kTile;
+    const uint32_t col = slot % kTile;
+    const uint32_t otr = operand.bc_rows ? 0u : tr;
+    const uint32_t otc = operand.bc_cols ? 0u : tc;
+    const unsigned char* tile = operand.base
+            + ((plane * operand.tile_rows + otr) * operand.tile_cols + otc)
+                    * static_cast<uint64_t>(kTileBytes);
+    const uint32_t orow = operand.bc_rows ? 0u : row;
+    if (!operand.bc_cols) {
+        return load_u4(tile + (orow * kTile + col) * ELEM);
+    }
+    // Column broadcast: one scalar per row, replicated.
+    if constexpr (ELEM == 4) {
+        const uint32_t value =
+                *reinterpret_cast<const uint32_t*>(tile + orow * kTile * ELEM);
+        return make_uint4(value, value, value, value);
+    } else {
+        const uint32_t half =
+                *reinterpret_cast<const uint16_t*>(tile + orow * kTile * ELEM);
+        const uint32_t value = half | (half << 16);
+        (void)kPerVector;
+        return make_uint4(value, value, value, value);
+    }
+}
+
+template <int ELEM>
+__device__ __forceinline__ void store_masked(
+        unsigned char* address, uint4 value, uint32_t valid) {
+    constexpr uint32_t kPerVector = 16 / ELEM;
+    if (valid >= kPerVector) {
+        store_u4(address, value);
+        return;
+    }
+    const uint32_t words[4] = {value.x, value.y, value.z, value.w};
+    if constexpr (ELEM == 4) {
+        for (uint32_t e = 0; e < valid; ++e) {
+            reinterpret_cast<uint32_t*>(address)[e] = words[e];
+        }
+    } else {
+        for (uint32_t e = 0; e < valid; ++e) {
+            reinterpret_cast<uint16_t*>(address)[e] =
+                    static_cast<uint16_t>(words[e / 2] >> ((e & 1u) * 16));
+        }
+    }
+}
+
+template <Leaf L, int OP>
+__global__ void __launch_bounds__(kTiledThreads)
+binary_tiled_kernel(const BinaryParams p) {
+    constexpr int ELEM = L == Leaf::BF16 ? 2 : 4;
+    constexpr uint32_t kTileBytes = kTileSlots * ELEM;
+    constexpr uint32_t kVectorsPerLane = kTileBytes / 512;   // 1 (16-bit) or 2 (32-bit)
+    constexpr uint32_t kPerVector = 16 / ELEM;
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint64_t warp = static_cast<uint64_t>(blockIdx.x) * kTiledWarps + (threadIdx.x >> 5);
+    const uint64_t warps = static_cast<uint64_t>(gridDim.x) * kTiledWarps;
+    for (uint64_t item = warp; item < p.items; item += warps) {
+        const uint32_t run = static_cast<uint32_t>(item % p.runs);
+        const uint64_t band = item / p.runs;
+        const uint32_t tr = static_cast<uint32_t>(band % p.tile_rows);
+        const uint64_t index = band / p.tile_rows;
+        const uint64_t lhs_plane = operand_plane(p.lhs, p.leading, index);
+        const uint64_t rhs_plane = operand_plane(p.rhs, p.leading, index);
+        const uint64_t out_plane = operand_plane(p.out, p.leading, index);
+        const uint32_t first = run * p.run_tiles;
+        const uint32_t last = min(first + p.run_tiles, p.tile_cols);
+        unsigned char* out_band = p.out.base
+                + (out_plane * p.out.tile_rows + tr) * p.out.tile_cols
+                        * static_cast<uint64_t>(kTileBytes);
+        const uint32_t rows_left = p.rows - tr * kTile;   // >= 1
+#pragma unroll 2
+        for (uint32_t tc = first; tc < last; ++tc) {
+            const uint32_t cols_left = p.cols - tc * kTile;   // >= 1
+            uint4 a[kVectorsPerLane], b[kVectorsPerLane];
+#pragma unroll
+            for (uint32_t v = 0; v < kVectorsPerLane; ++v) {
+                const uint32_t slot = (v * 512 + lane * 16) / ELEM;
+                a[v] = load_operand<ELEM>(p.lhs, lhs_plane, tr, tc, slot);
+                b[v] = load_operand<ELEM>(p.rhs, rhs_plane, tr, tc, slot);
+            }
+#pragma unroll
+            for (uint32_t v = 0; v < kVectorsPerLane; ++v) {
+                const uint32_t slot = (v * 512 + lane * 16) / ELEM;
+                const uint32_t row = slot / kTile;
+                const uint32_t col = slot % kTile;
+                if (row >= rows_left || col >= cols_left) continue;
+                const uint32_t valid = min(kPerVector, cols_left - col);
+                store_masked<ELEM>(
+                        out_band + static_cast<uint64_t>(tc) * kTileBytes + slot * ELEM,
+                        apply_vector<L, OP>(a[v], b[v]), valid);
+            }
+        }
+    }
+}
+
+// ---- host dispatch --------------------------------------------------------
+
+template <Leaf L, int OP>
+static int launch(const BinaryParams& params, bool linear, uint64_t linear_vectors,
+                  cudaStream_t stream) {
+    if (linear) {
+        const uint64_t per_cta = static_cast<uint64_t>(kLinearThreads) * kLinearUnroll;
+        const unsigned grid = grid_for((linear_vectors + per_cta - 1) / per_cta, 8);
+        binary_linear_kernel<L, OP><<<grid, kLinearThreads, 0, stream>>>(
+                reinterpret_cast<const uint4*>(params.lhs.base),
+                reinterpret_cast<const uint4*>(params.rhs.base),
+                reinterpret_cast<uint4*>(params.out.base), linear_vectors);
+    } else {
+        const unsigned grid = grid_for((params.items + kTiledWarps - 1) / kTiledWarps, 8);
+        binary_tiled_kernel<L, OP><<<grid, kTiledThreads, 0, stream>>>(params);
+    }
+    return check_launch("binary launch");
+}
+
+template <Leaf L>
+static int launch_op(int op, const BinaryParams& params, bool linear,
+                     uint64_t linear_vectors, cudaStream_t stream) {
+    return op == IOMB_ADD ? launch<L, IOMB_ADD>(params, linear, linear_vectors, stream)
+                          : launch<L, IOMB_MUL>(params, linear, linear_vectors, stream);
+}
+
+}  // namespace iomb
+
+extern "C" int iomb_binary(int op, const iomb_view* lhs, const iomb_view* rhs,
+                           const iomb_view* out, void* stream) {
+    using namespace iomb;
+    if (op != IOMB_ADD && op != IOMB_MUL) {
+        return fail(IOMB_ERR_UNSUPPORTED, "binary: only ADD and MUL are implemented");
+    }
+    ViewFacts fl{}, fr{}, fo{};
+    int status = check_view(lhs, "binary lhs", &fl);
+    if (status == IOMB_OK) status = check_view(rhs, "binary rhs", &fr);
+    if (status == IOMB_OK) status = check_view(out, "binary out", &fo);
+    if (status != IOMB_OK) return status;
+    if (lhs->dtype != rhs->dtype || lhs->dtype != out->dtype) {
+        return fail(IOMB_ERR_INVALID_ARGUMENT, "binary specifications do not match");
+    }
+    // Right-aligned broadcast shape (src/device_ops_binary.cpp:121-143).
+    const uint32_t rank = lhs->rank > rhs->rank ? lhs->rank : rhs->rank;
+    uint64_t result[IOMB_MAX_RANK];
+    for (uint32_t i = 0; i < rank; ++i) {
+        const uint64_t la = i < rank - lhs->rank ? 1 : lhs->dims[i - (rank - lhs->rank)];
+        const uint64_t ra = i < rank - rhs->rank ? 1 : rhs->dims[i - (rank - rhs->rank)];
+        if (la != ra && la != 1 && ra != 1) {
+            return fail(IOMB_ERR_INVALID_ARGUMENT, "binary shapes are not broadcast compatible");
+        }
+        result[i] = la > ra ? la : ra;
+    }
+    if (out->rank != rank) {
+        return fail(IOMB_ERR_INVALID_ARGUMENT, "binary output shape is incorrect");
+    }
+    for (uint32_t i = 0; i < rank; ++i) {
+        if (out->dims[i] != result[i]) {
+            return fail(IOMB_ERR_INVALID_ARGUMENT, "binary output shape is incorrect");
+        }
+    }
+    // Aligned plane strides, zero on broadcast axes (snapshot_binary_view,
+    // src/device_ops_binary.cpp:61-100).
+    const uint32_t lead_rank = rank - 2;
+    const iomb_view* views[3] = {lhs, rhs, out};
+    uint64_t strides[3][kMaxLead] = {};
+    bool broadcasts[3] = {false, false, false};
+    for (int k = 0; k < 3; ++k) {
+        const uint32_t offset = rank - views[k]->rank;
+        broadcasts[k] = offset != 0;
+        for (uint32_t axis = 0; axis < lead_rank; ++axis) {
+            if (axis < offset) {
+                broadcasts[k] = broadcasts[k] || result[axis] != 1;
+                continue;
+            }
+            const uint32_t source_axis = axis - offset;
+            if (views[k]->dims[source_axis] == 1 && result[axis] != 1) {
+                broadcasts[k] = true;
+                continue;
+            }
+            strides[k][axis] = views[k]->plane_strides[source_axis];
+        }
+    }
+    const bool lhs_bc_rows = fl.rows == 1 && result[rank - 2] != 1;
+    const bool rhs_bc_rows = fr.rows == 1 && result[rank - 2] != 1;
+    const bool lhs_bc_cols = fl.cols == 1 && result[rank - 1] != 1;
+    const bool rhs_bc_cols = fr.cols == 1 && result[rank - 1] != 1;
+    broadcasts[0] = broadcasts[0] || lhs_bc_rows || lhs_bc_cols;
+    broadcasts[1] = broadcasts[1] || rhs_bc_rows || rhs_bc_cols;
+    // Alias rule (src/device_ops_binary.cpp:152-169): an input that shares the
+    // output's owner must be exactly the output window and must not broadcast.
+    const iomb_view* inputs[2] = {lhs, rhs};
+    for (int k = 0; k < 2; ++k) {
+        if (inputs[k]->base == out->base
+                && (broadcasts[k] || !same_window(*inputs[k], *out))) {
+            return fail(IOMB_ERR_INVALID_ARGUMENT, "binary input/output alias is forbidden");
+        }
+    }
+    Leaf leaf;
+    switch (out->dtype) {
+        case IOMB_I32: case IOMB_U32: leaf = Leaf::I32; break;
+        case IOMB_F32: leaf = Leaf::F32; break;
+        case IOMB_BF16: leaf = Leaf::BF16; break;
+        default:
+            return fail(IOMB_ERR_UNSUPPORTED, "binary: leaf is not I32, U32, F32 or BF16");
+    }
+
+    BinaryParams params{};
+    collapse_leading(lead_rank, result, strides, 3, &params.leading);
+    params.lhs = make_operand(*lhs, fl, strides[0], params.leading, lhs_bc_rows, lhs_bc_cols);
+    params.rhs = make_operand(*rhs, fr, strides[1], params.leading, rhs_bc_rows, rhs_bc_cols);
+    params.out = make_operand(*out, fo, strides[2], params.leading, false, false);
+    params.rows = static_cast<uint32_t>(fo.rows);
+    params.cols = static_cast<uint32_t>(fo.cols);
+    if (fo.rows > 0xFFFFFFFFull || fo.cols > 0xFFFFFFFFull) {
+        return fail(IOMB_ERR_UNSUPPORTED, "binary: matrix extent exceeds the kernel limit");
+    }
+    params.tile_rows = static_cast<uint32_t>(fo.tile_rows);
+    params.tile_cols = static_cast<uint32_t>(fo.tile_cols);
+    params.run_tiles = fo.bytes == 2 ? 16u : 8u;   // 8 KiB of output per work item
+    params.runs = (params.tile_cols + params.run_tiles - 1) / params.run_tiles;
+    params.items = params.leading.planes * params.tile_rows * params.runs;
+
+    const bool full = !broadcasts[0] && !broadcasts[1];
+    const bool tile_multiple = fo.rows % kTile == 0 && fo.cols % kTile == 0;
+    const bool linear = full && tile_multiple && params.leading.contiguous;
+    uint64_t linear_vectors = 0;
+    if (linear) {
+        // Dense planes: advance each base to its first plane and stream.
+        params.lhs.base += lhs->plane_offset * fl.plane_bytes;
+        params.rhs.base += rhs->plane_offset * fr.plane_bytes;
+        params.out.base += out->plane_offset * fo.plane_bytes;
+        linear_vectors = params.leading.planes * fo.plane_bytes / 16;
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    switch (leaf) {
+        case Leaf::I32: return launch_op<Leaf::I32>(op, params, linear, linear_vectors, s);
+        case Leaf::F32: return launch_op<Leaf::F32>(op, params, linear, linear_vectors, s);
+        default: return launch_op<Leaf::BF16>(op, params, linear, linear_vectors, s);
+    }
+}

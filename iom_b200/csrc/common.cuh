@@ -1,0 +1,110 @@
+// Shared device/host helpers of the iom_b200 kernels (sm_100a only).
+//
+// Layout facts used throughout (reference: src/tensor.cpp:136-164): the last
+// two dimensions are stored as 16x16 tiles, tile-row major inside a plane, and
+// a tile is 256 consecutive slots (row in tile, then column in tile). A tile is
+// therefore 512 bytes for 16-bit leaves and 1024 bytes for 32-bit leaves, one
+// in-tile row is 32 / 64 contiguous bytes, and a 16-row band of a plane is one
+// contiguous run of tile_columns tiles.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+#include "../../include/iom_b200.h"
+
+namespace iomb {
+
+constexpr uint32_t kTile = 16;
+constexpr uint32_t kTileSlots = 256;
+constexpr uint32_t kMaxLead = IOMB_MAX_LEADING;
+
+// Thread-local error text behind iomb_last_error().
+void set_error(const char* text);
+int fail(int status, const char* text);
+int check_launch(const char* what);
+
+// Number of SMs of the current device (cached per device ordinal).
+int sm_count();
+
+// One operand as the kernels see it: plane mapping aligned to the (collapsed)
+// leading axes of the operation, zero stride on broadcast axes.
+struct Operand {
+    unsigned char* base;
+    uint64_t plane0;
+    uint64_t stride[kMaxLead];
+    uint32_t tile_rows;   // tile rows of this operand's own matrix
+    uint32_t tile_cols;   // tile columns of this operand's own matrix
+    uint32_t bc_rows;     // operand has one row, the result has more
+    uint32_t bc_cols;     // operand has one column, the result has more
+};
+
+// Collapsed leading iteration space shared by all operands of one launch.
+struct Leading {
+    uint32_t count;
+    uint32_t contiguous;  // every operand advances by exactly one plane per index
+    uint64_t dims[kMaxLead];
+    uint64_t planes;      // product of dims
+};
+
+// Owner plane of logical plane `index` for one operand.
+__device__ __forceinline__ uint64_t operand_plane(
+        const Operand& operand, const Leading& leading, uint64_t index) {
+    uint64_t plane = operand.plane0;
+    if (leading.count == 1) {
+        return plane + index * operand.stride[0];
+    }
+    for (int axis = static_cast<int>(leading.count) - 1; axis >= 0; --axis) {
+        const uint64_t extent = leading.dims[axis];
+        const uint64_t coordinate = index % extent;
+        index /= extent;
+        plane += coordinate * operand.stride[axis];
+    }
+    return plane;
+}
+
+// ---- numeric helpers ------------------------------------------------------
+
+// BF16 pair packed in one 32-bit word -> two binary32 values (exact widening).
+__device__ __forceinline__ float bf16_lo(uint32_t word) {
+    return __uint_as_float(word << 16);
+}
+__device__ __forceinline__ float bf16_hi(uint32_t word) {
+    return __uint_as_float(word & 0xFFFF0000u);
+}
+
+// Two binary32 values -> packed BF16 pair, round-to-nearest-even, overflow to
+// infinity, gradual underflow; every NaN becomes the positive quiet NaN 0x7FC0
+// (the reference's canonical encoding, src/shared/scalar_binary_codec.hpp:79-85).
+__device__ __forceinline__ uint32_t pack_bf16x2_canonical(float lo, float hi) {
+    const __nv_bfloat162 packed = __floats2bfloat162_rn(lo, hi);
+    uint32_t word = *reinterpret_cast<const uint32_t*>(&packed);
+    // A half is a NaN exactly when (half & 0x7FFF) > 0x7F80; adding 0x7F then
+    // carries into bit 15 of that half and never into the neighbouring half.
+    const uint32_t probe = (word & 0x7FFF7FFFu) + 0x007F007Fu;
+    if (probe & 0x80008000u) {
+        if (probe & 0x00008000u) word = (word & 0xFFFF0000u) | 0x00007FC0u;
+        if (probe & 0x80000000u) word = (word & 0x0000FFFFu) | 0x7FC00000u;
+    }
+    return word;
+}
+
+__device__ __forceinline__ uint32_t f32_canonical_bits(float value) {
+    return value != value ? 0x7FC00000u : __float_as_uint(value);
+}
+
+__device__ __forceinline__ uint4 load_u4(const void* address) {
+    return *reinterpret_cast<const uint4*>(address);
+}
+__device__ __forceinline__ uint4 load_u4_stream(const void* address) {
+    return __ldcs(reinterpret_cast<const uint4*>(address));
+}
+__device__ __forceinline__ void store_u4(void* address, uint4 value) {
+    *reinterpret_cast<uint4*>(address) = value;
+}
+__device__ __forceinline__ void store_u4_stream(void* address, uint4 value) {
+    __stcs(reinterpret_cast<uint4*>(address), value);
+}
+
+}  // namespace iomb

@@ -1,0 +1,386 @@
+// Bit-exact view copy, BF16<->F32 conversion and host-layout scatter/gather on
+// tiled storage.
+//
+// Replaces the word-owner read-modify-write kernels of the reference
+// (grid_stride_copy_kernel, src/shared/standard_tiled_copy_metadata.inl:177-282;
+// scatter_plane_kernel / gather_plane_kernel with one launch per plane,
+// src/shared/standard_tiled_copy.inl:286-441). Here a warp owns whole tiles and
+// moves them as 16-byte vectors; logical bounds mask the stores, so padding and
+// unselected planes are never written; all planes of a view go in one launch.
+#include "host.hpp"
+
+namespace iomb {
+
+constexpr int kCopyThreads = 256;
+constexpr int kCopyWarps = kCopyThreads / 32;
+constexpr int kCopyUnroll = 4;
+
+enum class Move : int { Copy = 0, Bf16ToF32 = 1, F32ToBf16 = 2 };
+
+// ---- element conversion ---------------------------------------------------
+
+// BF16 -> F32: exact widening; a NaN becomes the positive quiet NaN
+// (decode of src/shared/scalar_binary_codec.hpp:45-56 drops sign and payload).
+__device__ __forceinline__ uint32_t widen_bf16(uint32_t half) {
+    const uint32_t bits = half << 16;
+    return (bits & 0x7FFFFFFFu) > 0x7F800000u ? 0x7FC00000u : bits;
+}
+
+__device__ __forceinline__ void widen_vector(uint4 in, uint4* lo, uint4* hi) {
+    *lo = make_uint4(widen_bf16(in.x & 0xFFFFu), widen_bf16(in.x >> 16),
+                     widen_bf16(in.y & 0xFFFFu), widen_bf16(in.y >> 16));
+    *hi = make_uint4(widen_bf16(in.z & 0xFFFFu), widen_bf16(in.z >> 16),
+                     widen_bf16(in.w & 0xFFFFu), widen_bf16(in.w >> 16));
+}
+
+__device__ __forceinline__ uint4 narrow_vectors(uint4 lo, uint4 hi) {
+    return make_uint4(
+            pack_bf16x2_canonical(__uint_as_float(lo.x), __uint_as_float(lo.y)),
+            pack_bf16x2_canonical(__uint_as_float(lo.z), __uint_as_float(lo.w)),
+            pack_bf16x2_canonical(__uint_as_float(hi.x), __uint_as_float(hi.y)),
+            pack_bf16x2_canonical(__uint_as_float(hi.z), __uint_as_float(hi.w)));
+}
+
+// ---- linear streams ---------------------------------------------------------
+
+__global__ void __launch_bounds__(kCopyThreads)
+copy_linear_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, uint64_t vectors) {
+    const uint64_t stride = static_cast<uint64_t>(gridDim.x) * kCopyThreads;
+    uint64_t index = static_cast<uint64_t>(blockIdx.x) * kCopyThreads + threadIdx.x;
+    for (; index + stride * (kCopyUnroll - 1) < vectors; index += stride * kCopyUnroll) {
+        uint4 v[kCopyUnroll];
+#pragma unroll
+        for (int u = 0; u < kCopyUnroll; ++u) v[u] = load_u4_stream(src + index + stride * u);
+#pragma unroll
+        for (int u = 0; u < kCopyUnroll; ++u) store_u4_stream(dst + index + stride * u, v[u]);
+    }
+    for (; index < vectors; index += stride) {
+        store_u4_stream(dst + index, load_u4_stream(src + index));
+    }
+}
+
+// `groups` counts runs of 8 elements: 16 bytes of BF16, 32 bytes of F32.
+template <Move M>
+__global__ void __launch_bounds__(kCopyThreads)
+cast_linear_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, uint64_t groups) {
+    const uint64_t stride = static_cast<uint64_t>(gridDim.x) * kCopyThreads;
+    for (uint64_t index = static_cast<uint64_t>(blockIdx.x) * kCopyThreads + threadIdx.x;
+         index < groups; index += stride) {
+        if constexpr (M == Move::Bf16ToF32) {
+            uint4 lo, hi;
+            widen_vector(load_u4_stream(src + index), &lo, &hi);
+            store_u4_stream(dst + 2 * index, lo);
+            store_u4_stream(dst + 2 * index + 1, hi);
+        } else {
+            const uint4 lo = load_u4_stream(src + 2 * index);
+            const uint4 hi = load_u4_stream(src + 2 * index + 1);
+            store_u4_stream(dst + index, narrow_vectors(lo, hi));
+        }
+    }
+}
+
+// ---- tiled general kernel ----------------------------------------------------
+
+struct MoveParams {
+    Operand src;
+    Operand dst;
+    Leading leading;
+    uint32_t rows;
+    uint32_t cols;
+    uint32_t tile_rows;
+    uint32_t tile_cols;
+    uint32_t elem;        // destination leaf bytes for Copy; unused for casts
+    uint64_t items;       // planes * tile_rows * tile_cols
+};
+
+__device__ __forceinline__ void store_bytes_masked(
+        unsigned char* address, uint4 value, uint32_t valid_bytes) {
+    if (valid_bytes >= 16) {
+        store_u4(address, value);
+        return;
+    }
+    const uint32_t words[4] = {value.x, value.y, value.z, value.w};
+    for (uint32_t b = 0; b < valid_bytes; ++b) {
+        address[b] = static_cast<unsigned char>(words[b / 4] >> ((b & 3u) * 8));
+    }
+}
+
+// One warp per tile. Copy: the tile is 256*elem bytes = elem*16 vectors of 16
+// bytes; vector k covers elements [k*16/elem, (k+1)*16/elem) of the tile.
+__global__ void __launch_bounds__(kCopyThreads)
+copy_tiled_kernel(const MoveParams p) {
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint64_t warp = static_cast<uint64_t>(blockIdx.x) * kCopyWarps + (threadIdx.x >> 5);
+    const uint64_t warps = static_cast<uint64_t>(gridDim.x) * kCopyWarps;
+    const uint32_t tile_bytes = kTileSlots * p.elem;
+    const uint32_t tile_vectors = tile_bytes / 16;
+    const uint32_t per_vector = 16 / p.elem;      // elements per vector (>= 2)
+    for (uint64_t item = warp; item < p.items; item += warps) {
+        const uint32_t tc = static_cast<uint32_t>(item % p.tile_cols);
+        const uint64_t band = item / p.tile_cols;
+        const uint32_t tr = static_cast<uint32_t>(band % p.tile_rows);
+        const uint64_t index = band / p.tile_rows;
+        const uint64_t tile_in_plane = static_cast<uint64_t>(tr) * p.tile_cols + tc;
+        const unsigned char* src = p.src.base
+                + (operand_plane(p.src, p.leading, index) * p.tile_rows * p.tile_cols
+                   + tile_in_plane) * tile_bytes;
+        unsigned char* dst = p.dst.base
+                + (operand_plane(p.dst, p.leading, index) * p.tile_rows * p.tile_cols
+                   + tile_in_plane) * tile_bytes;
+        const uint32_t rows_left = p.rows - tr * kTile;
+        const uint32_t cols_left = p.cols - tc * kTile;
+        for (uint32_t k = lane; k < tile_vectors; k += 32) {
+            const uint32_t slot = k * per_vector;
+            const uint32_t row = slot / kTile, col = slot % kTile;
+            if (row >= rows_left || col >= cols_left) continue;
+            const uint32_t valid = min(per_vector, cols_left - col);
+            store_bytes_masked(dst + k * 16, load_u4(src + k * 16), valid * p.elem);
+        }
+    }
+}
+
+// One warp per tile; lane L owns 8 elements: BF16 bytes [16L,16L+16) and F32
+// bytes [32L,32L+32) of the same tile (row L/2, columns (L%2)*8 .. +7).
+template <Move M>
+__global__ void __launch_bounds__(kCopyThreads)
+cast_tiled_kernel(const MoveParams p) {
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint64_t warp = static_cast<uint64_t>(blockIdx.x) * kCopyWarps + (threadIdx.x >> 5);
+    const uint64_t warps = static_cast<uint64_t>(gridDim.x) * kCopyWarps;
+    constexpr uint32_t kSrcTile = M == Move::Bf16ToF32 ? 512u : 1024u;
+    constexpr uint32_t kDstTile = M == Move::Bf16ToF32 ? 1024u : 512u;
+    const uint32_t row = lane / 2, col = (lane % 2) * 8;
+    for (uint64_t item = warp; item < p.items; item += warps) {
+        const uint32_t tc = static_cast<uint32_t>(item % p.tile_cols);
+        const uint64_t band = item / p.tile_cols;
+        const uint32_t tr = static_cast<uint32_t>(band % p.tile_rows);
+        const uint64_t index = band / p.tile_rows;
+        const uint64_t tile_in_plane = static_cast<uint64_t>(tr) * p.tile_cols + tc;
+        const unsigned char* src = p.src.base
+                + (operand_plane(p.src, p.leading, index) * p.tile_rows * p.tile_cols
+                   + tile_in_plane) * kSrcTile;
+        unsigned char* dst = p.dst.base
+                + (operand_plane(p.dst, p.leading, index) * p.tile_rows * p.tile_cols
+                   + tile_in_plane) * kDstTile;
+        const uint32_t rows_left = p.rows - tr * kTile;
+        const uint32_t cols_left = p.cols - tc * kTile;
+        if (row >= rows_left || col >= cols_left) continue;
+        const uint32_t valid = min(8u, cols_left - col);
+        if constexpr (M == Move::Bf16ToF32) {
+            uint4 lo, hi;
+            widen_vector(load_u4(src + lane * 16), &lo, &hi);
+            store_bytes_masked(dst + lane * 32, lo, min(valid, 4u) * 4);
+            if (valid > 4) store_bytes_masked(dst + lane * 32 + 16, hi, (valid - 4) * 4);
+        } else {
+            const uint4 lo = load_u4(src + lane * 32);
+            const uint4 hi = load_u4(src + lane * 32 + 16);
+            store_bytes_masked(dst + lane * 16, narrow_vectors(lo, hi), valid * 2);
+        }
+    }
+}
+
+// ---- host layout <-> tiled ---------------------------------------------------
+
+struct LayoutParams {
+    Operand view;
+    Leading leading;
+    unsigned char* logical;   // row-major payload of the view
+    uint32_t rows;
+    uint32_t cols;
+    uint32_t tile_rows;
+    uint32_t tile_cols;
+    uint32_t elem;
+    uint32_t vector_ok;       // logical rows start 16-byte aligned
+    uint64_t items;
+};
+
+template <bool TO_TILED>
+__global__ void __launch_bounds__(kCopyThreads)
+layout_kernel(const LayoutParams p) {
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint64_t warp = static_cast<uint64_t>(blockIdx.x) * kCopyWarps + (threadIdx.x >> 5);
+    const uint64_t warps = static_cast<uint64_t>(gridDim.x) * kCopyWarps;
+    const uint32_t tile_bytes = kTileSlots * p.elem;
+    const uint32_t tile_vectors = tile_bytes / 16;
+    const uint32_t per_vector = 16 / p.elem;
+    for (uint64_t item = warp; item < p.items; item += warps) {
+        const uint32_t tc = static_cast<uint32_t>(item % p.tile_cols);
+        const uint64_t band = item / p.tile_cols;
+        const uint32_t tr = static_cast<uint32_t>(band % p.tile_rows);
+        const uint64_t index = band / p.tile_rows;
+        unsigned char* tile = p.view.base
+                + (operand_plane(p.view, p.leading, index) * p.tile_rows * p.tile_cols
+                   + static_cast<uint64_t>(tr) * p.tile_cols + tc) * tile_bytes;
+        const uint32_t rows_left = p.rows - tr * kTile;
+        const uint32_t cols_left = p.cols - tc * kTile;
+        for (uint32_t k = lane; k < tile_vectors; k += 32) {
+            const uint32_t slot = k * per_vector;
+            const uint32_t row = slot / kTile, col = slot % kTile;
+            if (row >= rows_left || col >= cols_left) continue;
+            const uint32_t valid = min(per_vector, cols_left - col);
+            unsigned char* host = p.logical
+                    + ((index * p.rows + tr * kTile + row) * static_cast<uint64_t>(p.cols)
+                       + tc * kTile + col) * p.elem;
+            unsigned char* tiled = tile + k * 16;
+            if (p.vector_ok && valid == per_vector) {
+                if (TO_TILED) store_u4(tiled, load_u4(host));
+                else store_u4(host, load_u4(tiled));
+            } else {
+                const uint32_t bytes = valid * p.elem;
+                for (uint32_t b = 0; b < bytes; ++b) {
+                    if (TO_TILED) tiled[b] = host[b];
+                    else host[b] = tiled[b];
+                }
+            }
+        }
+    }
+}
+
+// ---- host dispatch -----------------------------------------------------------
+
+static bool same_shape(const iomb_view& a, const iomb_view& b) {
+    if (a.rank != b.rank) return false;
+    for (uint32_t i = 0; i < a.rank; ++i) {
+        if (a.dims[i] != b.dims[i]) return false;
+    }
+    return true;
+}
+
+static int move_dispatch(const iomb_view* source, const iomb_view* destination, Move move,
+                         void* stream) {
+    ViewFacts fs{}, fd{};
+    int status = check_view(source, "copy source", &fs);
+    if (status == IOMB_OK) status = check_view(destination, "copy destination", &fd);
+    if (status != IOMB_OK) return status;
+    if (!same_shape(*source, *destination)) {
+        return fail(IOMB_ERR_INVALID_ARGUMENT, "copy views must have identical shape");
+    }
+    if (fd.rows > 0xFFFFFFFFull || fd.cols > 0xFFFFFFFFull) {
+        return fail(IOMB_ERR_UNSUPPORTED, "copy: matrix extent exceeds the kernel limit");
+    }
+    MoveParams p{};
+    uint64_t strides[2][kMaxLead] = {};
+    for (uint32_t axis = 0; axis < fs.leading; ++axis) {
+        strides[0][axis] = source->plane_strides[axis];
+        strides[1][axis] = destination->plane_strides[axis];
+    }
+    collapse_leading(fs.leading, source->dims, strides, 2, &p.leading);
+    p.src = make_operand(*source, fs, strides[0], p.leading, false, false);
+    p.dst = make_operand(*destination, fd, strides[1], p.leading, false, false);
+    p.rows = static_cast<uint32_t>(fd.rows);
+    p.cols = static_cast<uint32_t>(fd.cols);
+    p.tile_rows = static_cast<uint32_t>(fd.tile_rows);
+    p.tile_cols = static_cast<uint32_t>(fd.tile_cols);
+    p.elem = fd.bytes;
+    p.items = p.leading.planes * fd.tile_rows * fd.tile_cols;
+    const bool linear = p.leading.contiguous && fd.rows % kTile == 0 && fd.cols % kTile == 0;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (linear) {
+        const unsigned char* src = p.src.base + source->plane_offset * fs.plane_bytes;
+        unsigned char* dst = p.dst.base + destination->plane_offset * fd.plane_bytes;
+        if (move == Move::Copy) {
+            const uint64_t vectors = p.leading.planes * fd.plane_bytes / 16;
+            const uint64_t per_cta = static_cast<uint64_t>(kCopyThreads) * kCopyUnroll;
+            copy_linear_kernel<<<grid_for((vectors + per_cta - 1) / per_cta, 8), kCopyThreads, 0, s>>>(
+                    reinterpret_cast<const uint4*>(src), reinterpret_cast<uint4*>(dst), vectors);
+        } else {
+            const uint64_t groups = p.leading.planes * fd.tile_rows * fd.tile_cols * kTileSlots / 8;
+            const unsigned grid = grid_for((groups + kCopyThreads - 1) / kCopyThreads, 16);
+            if (move == Move::Bf16ToF32) {
+                cast_linear_kernel<Move::Bf16ToF32><<<grid, kCopyThreads, 0, s>>>(
+                        reinterpret_cast<const uint4*>(src), reinterpret_cast<uint4*>(dst), groups);
+            } else {
+                cast_linear_kernel<Move::F32ToBf16><<<grid, kCopyThreads, 0, s>>>(
+                        reinterpret_cast<const uint4*>(src), reinterpret_cast<uint4*>(dst), groups);
+            }
+        }
+    } else {
+        const unsigned grid = grid_for((p.items + kCopyWarps - 1) / kCopyWarps, 8);
+        if (move == Move::Copy) {
+            copy_tiled_kernel<<<grid, kCopyThreads, 0, s>>>(p);
+        } else if (move == Move::Bf16ToF32) {
+            cast_tiled_kernel<Move::Bf16ToF32><<<grid, kCopyThreads, 0, s>>>(p);
+        } else {
+            cast_tiled_kernel<Move::F32ToBf16><<<grid, kCopyThreads, 0, s>>>(p);
+        }
+    }
+    return check_launch("copy launch");
+}
+
+static int layout_dispatch(const iomb_view* view, void* logical, bool to_tiled, void* stream) {
+    ViewFacts f{};
+    const int status = check_view(view, to_tiled ? "scatter destination" : "gather source", &f);
+    if (status != IOMB_OK) return status;
+    if (logical == nullptr) return fail(IOMB_ERR_INVALID_ARGUMENT, "staging buffer is null");
+    if (f.bytes == 0) return fail(IOMB_ERR_UNSUPPORTED, "host transfer: sub-byte leaves are not implemented");
+    if (f.rows > 0xFFFFFFFFull || f.cols > 0xFFFFFFFFull) {
+        return fail(IOMB_ERR_UNSUPPORTED, "host transfer: matrix extent exceeds the kernel limit");
+    }
+    LayoutParams p{};
+    uint64_t strides[1][kMaxLead] = {};
+    for (uint32_t axis = 0; axis < f.leading; ++axis) strides[0][axis] = view->plane_strides[axis];
+    // The logical payload enumerates planes in the view's own leading order, so
+    // the axes are kept as they are (a merge would not change the order either).
+    collapse_leading(f.leading, view->dims, strides, 1, &p.leading);
+    p.view = make_operand(*view, f, strides[0], p.leading, false, false);
+    p.logical = static_cast<unsigned char*>(logical);
+    p.rows = static_cast<uint32_t>(f.rows);
+    p.cols = static_cast<uint32_t>(f.cols);
+    p.tile_rows = static_cast<uint32_t>(f.tile_rows);
+    p.tile_cols = static_cast<uint32_t>(f.tile_cols);
+    p.elem = f.bytes;
+    p.vector_ok = (reinterpret_cast<uintptr_t>(logical) % 16 == 0
+                   && (f.cols * f.bytes) % 16 == 0) ? 1u : 0u;
+    p.items = p.leading.planes * f.tile_rows * f.tile_cols;
+    const unsigned grid = grid_for((p.items + kCopyWarps - 1) / kCopyWarps, 8);
+    if (to_tiled) {
+        layout_kernel<true><<<grid, kCopyThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    } else {
+        layout_kernel<false><<<grid, kCopyThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    }
+    return check_launch("host transfer launch");
+}
+
+}  // namespace iomb
+
+extern "C" int iomb_copy(const iomb_view* source, const iomb_view* destination, void* stream) {
+    using namespace iomb;
+    if (source != nullptr && destination != nullptr) {
+        if (source->dtype != destination->dtype) {
+            return fail(IOMB_ERR_INVALID_ARGUMENT, "copy views must have identical leaf type");
+        }
+        const uint32_t bits = iomb_dtype_bits(source->dtype);
+        if (bits != 0 && bits % 8 != 0) {
+            return fail(IOMB_ERR_UNSUPPORTED, "copy: sub-byte leaves are not implemented");
+        }
+    }
+    ViewFacts fs{}, fd{};
+    int status = check_view(source, "copy source", &fs);
+    if (status == IOMB_OK) status = check_view(destination, "copy destination", &fd);
+    if (status != IOMB_OK) return status;
+    // An identical window is an accepted no-op (src/device_ops_copy.cpp:28-37).
+    if (same_window(*source, *destination)) return IOMB_OK;
+    return move_dispatch(source, destination, Move::Copy, stream);
+}
+
+extern "C" int iomb_cast(const iomb_view* source, const iomb_view* destination, void* stream) {
+    using namespace iomb;
+    if (source == nullptr || destination == nullptr) {
+        return fail(IOMB_ERR_INVALID_ARGUMENT, "cast: view is null");
+    }
+    if (source->dtype == IOMB_BF16 && destination->dtype == IOMB_F32) {
+        return move_dispatch(source, destination, Move::Bf16ToF32, stream);
+    }
+    if (source->dtype == IOMB_F32 && destination->dtype == IOMB_BF16) {
+        return move_dispatch(source, destination, Move::F32ToBf16, stream);
+    }
+    return fail(IOMB_ERR_UNSUPPORTED, "cast: only BF16<->F32 is implemented");
+}
+
+extern "C" int iomb_scatter(const iomb_view* destination, const void* staging, void* stream) {
+    return iomb::layout_dispatch(destination, const_cast<void*>(staging), true, stream);
+}
+
+extern "C" int iomb_gather(const iomb_view* source, void* staging, void* stream) {
+    return iomb::layout_dispatch(source, staging, false, stream);
+}

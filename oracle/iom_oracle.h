@@ -1,0 +1,69 @@
+/*
+ * TEST INFRASTRUCTURE — not part of the product.
+ *
+ * Plain-C CPU restatement of the reference's (rlewczuk/iom) device tensor-op
+ * path, operating on host copies of the tiled storage. Only tests, the smoke
+ * check and the bench's cpu_baseline leg may load this library; the product
+ * never does.
+ *
+ * Pinning: tests/test_oracle_vs_reference.py runs this restatement against the
+ * unmodified reference CPU backend (oracle/_ref, built by the Makefile beside
+ * this file) and against the golden vectors committed under tests/golden/.
+ */
+#ifndef IOM_ORACLE_H
+#define IOM_ORACLE_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Same field layout as the product's view descriptor, defined independently. */
+typedef struct iomo_view {
+    void* base;               /* host copy of the owner's tiled storage */
+    uint64_t storage_bytes;
+    uint32_t dtype;           /* iom::DataType ordinal */
+    uint32_t rank;
+    uint64_t dims[8];
+    uint64_t plane_offset;
+    uint64_t plane_strides[6];
+} iomo_view;
+
+uint32_t iomo_leaf_bits(uint32_t dtype);
+uint64_t iomo_plane_slot(uint64_t rows, uint64_t columns, uint64_t plane,
+                         uint64_t row, uint64_t column);
+uint64_t iomo_tiled_storage_nbytes(const uint64_t* dims, uint32_t rank, uint32_t dtype);
+uint64_t iomo_logical_nbytes(const uint64_t* dims, uint32_t rank, uint32_t dtype);
+
+/* op: 0 add, 1 mul, 2 sub, 3 div. The codec with the x87 long double carrier. */
+uint64_t iomo_scalar_binary(int op, uint32_t dtype, uint64_t a, uint64_t b);
+/* Plain IEEE binary32 arithmetic + canonical NaN, for I32/U32/F32/BF16 add/mul. */
+uint64_t iomo_scalar_binary_ieee(int op, uint32_t dtype, uint64_t a, uint64_t b);
+uint64_t iomo_codec_mismatches(int op, uint32_t dtype, const void* a, uint64_t na,
+                               const void* b, uint64_t nb);
+uint64_t iomo_decode_encode(uint32_t src_dtype, uint32_t dst_dtype, uint64_t raw);
+
+/* Each returns 0 on success, 1 for invalid arguments. `ieee` selects the fast
+ * arithmetic (valid for I32/U32/F32/BF16 only) instead of the codec. */
+int iomo_binary(int op, const iomo_view* lhs, const iomo_view* rhs,
+                const iomo_view* out, int ieee);
+/* order 0: 16-lane accumulators + fixed tree for BF16 rows without inf/NaN
+ * (the reference's AVX-512 BF16 build); order 1: sequential recurrence. */
+int iomo_rmsnorm(const iomo_view* x, const iomo_view* scale, const iomo_view* out,
+                 float eps, int order);
+int iomo_copy(const iomo_view* source, const iomo_view* destination);
+int iomo_cast(const iomo_view* source, const iomo_view* destination);
+/* *status = 1 and nothing is written when any index is negative or >= V. */
+int iomo_embedding(const iomo_view* table, const iomo_view* indices,
+                   const iomo_view* out, uint32_t* status);
+int iomo_cache_append(const iomo_view* source, const iomo_view* destination, uint64_t a);
+double iomo_sumsq(const iomo_view* x);
+/* Logical row-major LSB-first packed payload <-> tiled storage. */
+int iomo_scatter(const iomo_view* destination, const void* logical);
+int iomo_gather(const iomo_view* source, void* logical);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,311 @@
+// TEST INFRASTRUCTURE — not part of the product.
+//
+// C-ABI shim over the *unmodified* reference CPU backend (rlewczuk/iom). It is
+// compiled together with the reference's own sources where they lie (see the
+// Makefile beside this file) into oracle/_ref/libiomref_{portable,avx512}.so.
+// The shim only exposes the reference's public API (Device, Tensor,
+// TensorView transforms, DeviceOps facades, wait) to ctypes so that tests can
+//   * pin the plain-C restatement in iom_oracle.c against the real reference,
+//   * generate the golden fixtures committed under tests/golden/,
+//   * time the reference CPU backend as the reported CPU baseline.
+// Nothing in the product library links or loads this file.
+//
+// Reference interfaces wrapped here:
+//   make_cpu_device                 include/iom/cpu/device.hpp:19-20
+//   Device::create_tensor/create_ops include/iom/device.hpp:86-99
+//   TensorView transforms/transfers include/iom/tensor.hpp:322-342
+//   DeviceOps::{copy,add,mul,sub,div,rmsnorm,embedding,cache_append,wait}
+//                                   include/iom/iom.hpp:121-323
+
+#include <cstddef>
+#include <cstdint>
+#include <cstring>
+#include <exception>
+#include <memory>
+#include <new>
+#include <span>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "iom/cpu/device.hpp"
+#include "iom/iom.hpp"
+#include "iom/tensor.hpp"
+
+namespace iom::cpu_detail {
+// src/cpu/avx512_bf16.hpp: true when this build and this CPU may enter the
+// isolated AVX-512 BF16 workers.
+bool avx512_bf16_available() noexcept;
+}  // namespace iom::cpu_detail
+
+namespace {
+
+thread_local std::string g_last_error;
+
+class AlignedHostAllocator final : public iom::Allocator {
+public:
+    void* alloc(std::size_t size) override {
+        return ::operator new(size, std::align_val_t(64));
+    }
+    void free(void* buffer) override {
+        ::operator delete(buffer, std::align_val_t(64));
+    }
+    void reset() override {}
+};
+
+struct DeviceBox {
+    AlignedHostAllocator allocator;
+    std::unique_ptr<iom::Device> device;
+};
+
+struct TensorBox {
+    std::unique_ptr<iom::Tensor> tensor;
+};
+
+struct ViewBox {
+    iom::TensorView view;
+};
+
+struct QueueBox {
+    std::unique_ptr<iom::DeviceOps> ops;
+};
+
+// Exception class → small positive code (0 is success).
+int classify(std::exception_ptr failure) {
+    try {
+        std::rethrow_exception(failure);
+    } catch (const std::invalid_argument& e) {
+        g_last_error = e.what();
+        return 1;
+    } catch (const std::out_of_range& e) {
+        g_last_error = e.what();
+        return 2;
+    } catch (const std::overflow_error& e) {
+        g_last_error = e.what();
+        return 3;
+    } catch (const std::bad_alloc& e) {
+        g_last_error = e.what();
+        return 4;
+    } catch (const std::exception& e) {
+        g_last_error = e.what();
+        return 5;
+    } catch (...) {
+        g_last_error = "unknown exception";
+        return 6;
+    }
+}
+
+template <typename Body>
+void* guarded_pointer(Body&& body) {
+    try {
+        return body();
+    } catch (...) {
+        (void)classify(std::current_exception());
+        return nullptr;
+    }
+}
+
+template <typename Body>
+int guarded_status(Body&& body) {
+    try {
+        body();
+        return 0;
+    } catch (...) {
+        return classify(std::current_exception());
+    }
+}
+
+iom::TensorView& view_of(void* handle) {
+    return static_cast<ViewBox*>(handle)->view;
+}
+
+iom::DeviceOps& ops_of(void* handle) {
+    return *static_cast<QueueBox*>(handle)->ops;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* iomref_last_error() { return g_last_error.c_str(); }
+
+int iomref_avx512_bf16_active() {
+    return iom::cpu_detail::avx512_bf16_available() ? 1 : 0;
+}
+
+void* iomref_device_create() {
+    return guarded_pointer([]() -> void* {
+        auto box = std::make_unique<DeviceBox>();
+        box->device = iom::make_cpu_device(box->allocator);
+        return box.release();
+    });
+}
+
+void iomref_device_destroy(void* device) {
+    delete static_cast<DeviceBox*>(device);
+}
+
+void* iomref_tensor_create(
+        void* device, const std::uint64_t* dims, std::uint32_t rank,
+        std::uint32_t data_type) {
+    return guarded_pointer([&]() -> void* {
+        std::vector<std::size_t> shape(dims, dims + rank);
+        iom::TensorSpec spec{
+                iom::TensorShape{std::move(shape)},
+                static_cast<iom::DataType>(data_type)};
+        auto box = std::make_unique<TensorBox>();
+        box->tensor =
+                static_cast<DeviceBox*>(device)->device->create_tensor(spec);
+        return box.release();
+    });
+}
+
+void iomref_tensor_destroy(void* tensor) {
+    delete static_cast<TensorBox*>(tensor);
+}
+
+// Raw tiled owner storage of a CPU tensor (src/cpu/tensor.cpp:36-76 reports the
+// host buffer as the native handle).
+void* iomref_tensor_storage(void* tensor) {
+    return static_cast<TensorBox*>(tensor)->tensor->view().native_handle();
+}
+
+std::uint64_t iomref_tensor_storage_nbytes(void* tensor) {
+    return static_cast<TensorBox*>(tensor)
+            ->tensor->view().spec().tiled_storage_nbytes();
+}
+
+void* iomref_view_full(void* tensor) {
+    return guarded_pointer([&]() -> void* {
+        return new ViewBox{static_cast<TensorBox*>(tensor)->tensor->view()};
+    });
+}
+
+void* iomref_view_slice(
+        void* view, std::uint64_t dim, std::uint64_t first,
+        std::uint64_t count, std::uint64_t step) {
+    return guarded_pointer([&]() -> void* {
+        return new ViewBox{view_of(view).slice(dim, first, count, step)};
+    });
+}
+
+void* iomref_view_select(void* view, std::uint64_t dim, std::uint64_t index) {
+    return guarded_pointer([&]() -> void* {
+        return new ViewBox{view_of(view).select(dim, index)};
+    });
+}
+
+void* iomref_view_permute(
+        void* view, const std::uint64_t* order, std::uint32_t count) {
+    return guarded_pointer([&]() -> void* {
+        std::vector<std::size_t> leading(order, order + count);
+        return new ViewBox{view_of(view).permute(leading)};
+    });
+}
+
+void* iomref_view_reshape_leading(
+        void* view, const std::uint64_t* dims, std::uint32_t count) {
+    return guarded_pointer([&]() -> void* {
+        std::vector<std::size_t> leading(dims, dims + count);
+        return new ViewBox{view_of(view).reshape_leading(leading)};
+    });
+}
+
+void iomref_view_destroy(void* view) { delete static_cast<ViewBox*>(view); }
+
+// Reports the metadata an operation snapshots from a view: full logical
+// shape, leaf type, plane offset and leading plane strides (whole planes).
+int iomref_view_describe(
+        void* view, std::uint32_t* rank, std::uint64_t* dims,
+        std::uint64_t* plane_offset, std::uint64_t* plane_strides,
+        std::uint32_t* data_type) {
+    return guarded_status([&] {
+        const iom::TensorView& v = view_of(view);
+        const auto shape = v.spec().shape.dimensions();
+        *rank = static_cast<std::uint32_t>(shape.size());
+        for (std::size_t i = 0; i < shape.size(); ++i) dims[i] = shape[i];
+        *plane_offset = v.plane_offset();
+        const auto strides = v.plane_strides();
+        for (std::size_t i = 0; i < strides.size(); ++i) {
+            plane_strides[i] = strides[i];
+        }
+        *data_type = static_cast<std::uint32_t>(v.spec().data_type);
+    });
+}
+
+std::uint64_t iomref_view_logical_nbytes(void* view) {
+    try {
+        return view_of(view).spec().logical_nbytes();
+    } catch (...) {
+        (void)classify(std::current_exception());
+        return 0;
+    }
+}
+
+int iomref_view_from_host(void* view, const void* bytes, std::uint64_t count) {
+    return guarded_status([&] {
+        view_of(view).copy_from_host(std::span<const std::byte>(
+                static_cast<const std::byte*>(bytes), count));
+    });
+}
+
+int iomref_view_to_host(void* view, void* bytes, std::uint64_t count) {
+    return guarded_status([&] {
+        view_of(view).copy_to_host(
+                std::span<std::byte>(static_cast<std::byte*>(bytes), count));
+    });
+}
+
+void* iomref_queue_create(void* device) {
+    return guarded_pointer([&]() -> void* {
+        auto box = std::make_unique<QueueBox>();
+        box->ops = static_cast<DeviceBox*>(device)->device->create_ops();
+        return box.release();
+    });
+}
+
+void iomref_queue_destroy(void* queue) { delete static_cast<QueueBox*>(queue); }
+
+// operation: 0 add, 1 mul, 2 sub, 3 div. Returns the facade's oid unchanged
+// (negative = synchronous OidError, positive = accepted token).
+std::int64_t iomref_binary(
+        void* queue, int operation, void* lhs, void* rhs, void* out) {
+    iom::DeviceOps& ops = ops_of(queue);
+    switch (operation) {
+        case 0: return ops.add(view_of(lhs), view_of(rhs), view_of(out));
+        case 1: return ops.mul(view_of(lhs), view_of(rhs), view_of(out));
+        case 2: return ops.sub(view_of(lhs), view_of(rhs), view_of(out));
+        case 3: return ops.div(view_of(lhs), view_of(rhs), view_of(out));
+        default: return -1;
+    }
+}
+
+std::int64_t iomref_rmsnorm(
+        void* queue, void* x, void* scale, void* out, float epsilon) {
+    return ops_of(queue).rmsnorm(
+            view_of(x), view_of(scale), view_of(out), epsilon);
+}
+
+std::int64_t iomref_copy(void* queue, void* source, void* destination) {
+    return ops_of(queue).copy(view_of(source), view_of(destination));
+}
+
+std::int64_t iomref_embedding(
+        void* queue, void* table, void* indices, void* out) {
+    return ops_of(queue).embedding(
+            view_of(table), view_of(indices), view_of(out));
+}
+
+std::int64_t iomref_cache_append(
+        void* queue, void* source, void* destination, std::uint64_t a) {
+    return ops_of(queue).cache_append(
+            view_of(source), view_of(destination), a);
+}
+
+// 0 when the accepted work completed; otherwise the class of the retained or
+// validation failure `wait` rethrew (1 invalid_argument, 3 overflow, ...).
+int iomref_wait(void* queue, std::int64_t token) {
+    return guarded_status([&] { ops_of(queue).wait(token); });
+}
+
+}  // extern "C"

@@ -1,0 +1,12 @@
+"""pytest configuration: markers and import path."""
+import sys
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent.parent
+for entry in (str(ROOT), str(ROOT / "tests")):
+    if entry not in sys.path:
+        sys.path.insert(0, entry)
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
