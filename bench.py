@@ -1,0 +1,423 @@
+#!/usr/bin/env python
+"""Benchmark of the hot path: fused residual ADD + RMSNorm on tiled BF16 storage.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+A step is one pass of iomb_add_rmsnorm over one batch of synthetic input: 16
+planes of the TinyLlama prefill shape (rows 8192, hidden 2048, BF16, eps 1e-5),
+one launch, 2.1 GB of algorithmic traffic, so every step streams from HBM (the
+batch is 17 times the L2 capacity). With N > 1 every rank runs the same batch on
+its own GPU (row shards are independent: no data-path collective) and rank 0
+prints the aggregate. One JSON line is printed; see the keys below.
+
+`--impl reference` times the reference's own CPU backend (oracle/_ref when the
+shim is built, else the plain-C oracle port) on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+for entry in (str(ROOT), str(ROOT / "tests")):
+    if entry not in sys.path:
+        sys.path.insert(0, entry)
+
+PLANES, ROWS, HIDDEN, EPS = 16, 8192, 2048, 1e-5
+ELEM = 2
+ELEMENTS = PLANES * ROWS * HIDDEN
+# x and residual read, rounded sum and normalised output written, scale read once
+ALGORITHMIC_BYTES = 4 * ELEMENTS * ELEM + HIDDEN * ELEM
+METRIC = "achieved HBM GB/s, fused residual ADD + RMSNorm (BF16, TinyLlama prefill shape)"
+WORKLOAD = (f"C2 x{PLANES}: BF16 [{PLANES},{ROWS},{HIDDEN}] residual ADD + RMSNorm, eps 1e-5, "
+            "x,r ~ N(0,1), w ~ N(1,0.02)")
+# dram__bytes_read.sum + dram__bytes_write.sum of one rmsnorm_kernel launch, from
+# the ncu capture summarised in profiles/ (a [2,8192,2048] case scaled by 8:
+# traffic is proportional to the rows processed). None until a capture exists.
+NCU_TRAFFIC_BYTES = None
+
+
+def configure(planes: int) -> None:
+    """Resizes the batch (the default is the benchmark's; profiler captures shrink it)."""
+    global PLANES, ELEMENTS, ALGORITHMIC_BYTES, WORKLOAD
+    PLANES = planes
+    ELEMENTS = PLANES * ROWS * HIDDEN
+    ALGORITHMIC_BYTES = 4 * ELEMENTS * ELEM + HIDDEN * ELEM
+    WORKLOAD = (f"C2 x{PLANES}: BF16 [{PLANES},{ROWS},{HIDDEN}] residual ADD + RMSNorm, "
+                "eps 1e-5, x,r ~ N(0,1), w ~ N(1,0.02)")
+
+
+def measured_peak():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi during a timed region."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        clocks, maxima, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                clocks.append(float(parts[0]))
+                maxima.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[2:6]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        if not clocks:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(clocks), "sm_max_mhz": max(maxima),
+                "reasons": sorted(reasons), "samples": len(clocks)}
+
+
+def synthetic_inputs(seed: int):
+    """Seeded logical payloads (BF16 codes) of the batch; C2's distributions."""
+    import numpy as np
+
+    def f32_to_bf16_bits(values):
+        bits = np.ascontiguousarray(values, dtype=np.float32).view(np.uint32).astype(np.uint64)
+        return ((bits + 0x7FFF + ((bits >> 16) & 1)) >> 16).astype(np.uint16)
+
+    rng = np.random.default_rng(seed)
+    shape = (PLANES, ROWS, HIDDEN)
+    x = f32_to_bf16_bits(rng.standard_normal(shape, dtype=np.float32))
+    r = f32_to_bf16_bits(rng.standard_normal(shape, dtype=np.float32))
+    w = f32_to_bf16_bits((1.0 + 0.02 * rng.standard_normal((1, HIDDEN))).astype(np.float32))
+    return x, r, w
+
+
+def run_ours(args) -> dict:
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    from iom_b200.device import DeviceMemoryConfig, make_b200_device
+    from iom_b200.tensor import DataType, TensorSpec
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the B200 backend has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    arena = 5 * PLANES * ROWS * HIDDEN * ELEM + (64 << 20)
+    device = make_b200_device(local_rank, DeviceMemoryConfig(arena // 32 * 32))
+    queue = device.create_ops()
+    shape = (PLANES, ROWS, HIDDEN)
+    spec = TensorSpec(shape, DataType.BF16)
+    x, r, total, out = (device.create_tensor(spec) for _ in range(4))
+    scale = device.create_tensor(TensorSpec((1, HIDDEN), DataType.BF16))
+    logical_bytes = spec.logical_nbytes()
+    staging = device.create_workspace(logical_bytes + 64)
+
+    # Seeded inputs live in pinned host memory in the logical row-major layout the
+    # reference's copy_from_host takes.
+    x_host, r_host, w_host = synthetic_inputs(seed=1000 + rank)
+    pinned = {}
+    for name, array in (("x", x_host), ("r", r_host)):
+        buffer = torch.empty(array.size, dtype=torch.int16, pin_memory=True)
+        buffer.numpy().view(np.uint16)[:] = array.reshape(-1)
+        pinned[name] = buffer
+    out_host = torch.empty(ELEMENTS, dtype=torch.int16, pin_memory=True)
+    scale.view().copy_from_host(w_host, staging.view())
+    x.view().copy_from_host(pinned["x"].numpy(), staging.view())
+    r.view().copy_from_host(pinned["r"].numpy(), staging.view())
+
+    def step():
+        token = queue.add_rmsnorm(x.view(), r.view(), scale.view(), total.view(), out.view(), EPS)
+        if token <= 0:
+            raise RuntimeError(f"add_rmsnorm rejected with oid {token}")
+        return token
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident throughput (`value`) -----------------------------
+    for _ in range(args.warmup):
+        token = step()
+    queue.wait(token)
+    barrier()
+    start = torch.cuda.Event(enable_timing=True)
+    stop = torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as sampler:
+        start.record(queue.stream)
+        for _ in range(args.steps):
+            token = step()
+        stop.record(queue.stream)
+        queue.wait(token)
+        barrier()
+    elapsed_ms = start.elapsed_time(stop)
+    clocks = sampler.summary()
+
+    # ---- end to end through the public API with host buffers (`e2e`) -------
+    e2e_steps = max(1, min(args.steps, 3))
+
+    def e2e_step():
+        x.view().copy_from_host(pinned["x"].numpy(), staging.view())
+        r.view().copy_from_host(pinned["r"].numpy(), staging.view())
+        queue.wait(step())
+        out.view().copy_to_host(out_host.numpy(), staging.view())
+
+    e2e_ms = float("nan")
+    if not args.no_e2e:
+        e2e_step()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            e2e_step()
+        torch.cuda.synchronize()
+        e2e_ms = (time.perf_counter() - t0) * 1e3
+
+    times = torch.tensor([elapsed_ms, e2e_ms], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    elapsed_ms, e2e_ms = (float(v) for v in times.tolist())
+
+    result = None
+    if rank == 0:
+        peak, peak_kind = measured_peak()
+        per_launch_ms = elapsed_ms / args.steps
+        achieved = ALGORITHMIC_BYTES / per_launch_ms / 1e6
+        result = {
+            "metric": METRIC,
+            "value": world * ALGORITHMIC_BYTES * args.steps / elapsed_ms / 1e6,
+            "unit": "GB/s",
+            "n_gpus": world,
+            "steps": args.steps,
+            "warmup": args.warmup,
+            "ms_per_step": per_launch_ms,
+            "higher_is_better": True,
+            "scaling": "weak",
+            "vs_baseline": None,
+            "dtype": "f32 accumulate, bf16 storage",
+            "data": "synthetic (seeded normal, BASELINE config 2 distributions)",
+            "config": {"workload": WORKLOAD, "launches_per_step": 1,
+                       "algorithmic_bytes_per_step": ALGORITHMIC_BYTES,
+                       "l2": f"inputs larger than L2 ({ALGORITHMIC_BYTES / 1e9:.2f} GB touched "
+                             "per step, L2 is 126 MB)",
+                       "order": "LANES16", "pct_of_8TBps": None},
+            "clocks": clocks,
+            "e2e": {"value": world * ALGORITHMIC_BYTES * e2e_steps / e2e_ms / 1e6, "unit": "GB/s",
+                    "h2d_bytes_per_step": 2 * logical_bytes, "d2h_bytes_per_step": logical_bytes,
+                    "steps": e2e_steps,
+                    "path": "copy_from_host(x), copy_from_host(r), add_rmsnorm, copy_to_host(out)"},
+            "gpu_launches": args.steps,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES,
+                         "peak_source": f"of {peak_kind}", "kernel": "rmsnorm_kernel<2,16,true>",
+                         "algorithmic_bytes_per_launch": ALGORITHMIC_BYTES},
+        }
+        result["config"]["pct_of_8TBps"] = 100.0 * achieved / 8000.0
+    queue.close()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return result
+
+
+# ---- CPU side: the reference's own CPU backend (or the oracle port) ---------------
+
+def _cpu_arm(threads: int, repeats: int, warmup: int) -> dict:
+    """Times add(x, r, s) followed by rmsnorm(s, w, n) — the reference's contract
+    path for this step — on `threads` independent row shards, one reference
+    device + queue (one worker thread) per shard. Bytes are counted like the GPU
+    arm's (fused-equivalent algorithmic bytes for the rows processed) so the two
+    GB/s figures describe the same amount of work."""
+    import ctypes
+
+    import numpy as np
+    import support
+    from iom_b200.tensor import DataType
+
+    kind = None
+    for candidate in ("avx512", "portable"):
+        if support.REF_LIBS[candidate].exists():
+            probe = support.Reference(candidate)
+            active = probe.lib.iomref_avx512_bf16_active() == 1
+            probe.close()
+            if candidate == "portable" or active:
+                kind = candidate
+                break
+    rng = np.random.default_rng(7)
+
+    def payloads(rows):
+        x = support.f32_to_bf16_bits(rng.standard_normal((rows, HIDDEN), dtype=np.float32))
+        r = support.f32_to_bf16_bits(rng.standard_normal((rows, HIDDEN), dtype=np.float32))
+        w = support.f32_to_bf16_bits(
+            (1.0 + 0.02 * rng.standard_normal((1, HIDDEN))).astype(np.float32))
+        return x, r, w
+
+    if kind is None:
+        # Oracle port: scalar plain-C restatement, one core.
+        rows, threads = 128, 1
+        x, r, w = payloads(rows)
+        hosts = {}
+        for name, data in (("x", x), ("r", r), ("w", w), ("s", x), ("n", x)):
+            tensor = support.HostTensor(data.shape, DataType.BF16)
+            tensor.view().copy_from_host(data)
+            hosts[name] = tensor
+        lib = support.oracle()
+
+        def once():
+            assert lib.iomo_binary(0, support.abi(hosts["x"].view()), support.abi(hosts["r"].view()),
+                                   support.abi(hosts["s"].view()), 0) == 0
+            assert lib.iomo_rmsnorm(support.abi(hosts["s"].view()), support.abi(hosts["w"].view()),
+                                    support.abi(hosts["n"].view()), EPS, 1) == 0
+        label, sample_kind = "oracle port (plain C, scalar codec)", "port"
+    else:
+        rows = 4096 if kind == "avx512" else 128
+        shards = []
+        for _ in range(threads):
+            ref = support.Reference(kind)
+            x, r, w = payloads(rows)
+            tensors = {}
+            for name, data in (("x", x), ("r", r), ("w", w), ("s", x), ("n", x)):
+                tensor = ref.tensor(data.shape, DataType.BF16)
+                tensor.view().from_host(data)
+                tensors[name] = tensor.view()
+            shards.append((ref, tensors))
+
+        def once():
+            tokens = []
+            for ref, t in shards:
+                a = ref.lib.iomref_binary(ref.queue, 0, t["x"].handle, t["r"].handle, t["s"].handle)
+                b = ref.lib.iomref_rmsnorm(ref.queue, t["s"].handle, t["w"].handle, t["n"].handle,
+                                           ctypes.c_float(EPS))
+                assert a > 0 and b > 0, ref.error()
+                tokens.append((ref, b))
+            for ref, token in tokens:
+                assert ref.lib.iomref_wait(ref.queue, token) == 0, ref.error()
+        label = f"reference CPU backend, {kind} build (oracle/_ref)"
+        sample_kind = "reference"
+
+    for _ in range(warmup):
+        once()
+    samples = []
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        once()
+        samples.append(time.perf_counter() - t0)
+    seconds = statistics.median(samples)
+    elements = threads * rows * HIDDEN
+    bytes_per_step = 4 * elements * ELEM + threads * HIDDEN * ELEM
+    return {"value": bytes_per_step / seconds / 1e9, "unit": "GB/s", "cores": threads,
+            "kind": sample_kind,
+            "sample": f"{label}: add + rmsnorm on {threads} shard(s) of [{rows},{HIDDEN}] BF16, "
+                      f"median of {repeats} runs, {seconds * 1e3:.1f} ms per run",
+            "ms_per_step": seconds * 1e3}
+
+
+def run_reference(args) -> dict | None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return None
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    threads = max(1, min(os.cpu_count() or 1, 64))
+    cpu = _cpu_arm(threads, repeats=max(1, args.steps), warmup=max(1, min(args.warmup, 2)))
+    return {
+        "impl": "reference",
+        "metric": METRIC,
+        "value": cpu["value"],
+        "unit": "GB/s",
+        "n_gpus": world,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": cpu["ms_per_step"],
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "f32 accumulate, bf16 storage",
+        "data": "synthetic (seeded normal, BASELINE config 2 distributions)",
+        "config": {"workload": WORKLOAD, "sample": cpu["sample"]},
+        "cpu_baseline": {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": cpu["value"], "unit": "GB/s", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--warmup", type=int, default=3)
+    parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--no-e2e", action="store_true",
+                        help="skip the host-buffer leg (used for profiler captures)")
+    parser.add_argument("--planes", type=int, default=PLANES,
+                        help="planes of [8192,2048] per step; smaller values give the "
+                             "small case profiler captures use")
+    args = parser.parse_args()
+    configure(args.planes)
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        result = run_reference(args)
+    else:
+        result = run_ours(args)
+        if result is not None and result["n_gpus"] == 1 and not args.no_cpu_baseline:
+            cpu = _cpu_arm(1, repeats=3, warmup=1)
+            result["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
+    if result is not None:
+        print(json.dumps(result), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -90,6 +90,12 @@ __device__ __forceinline__ uint32_t pack_bf16x2_canonical(float lo, float hi) {
     return word;
 }
 
+// Plain RNE pack for values known not to be NaN.
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    const __nv_bfloat162 packed = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&packed);
+}
+
 __device__ __forceinline__ uint32_t f32_canonical_bits(float value) {
     return value != value ? 0x7FC00000u : __float_as_uint(value);
 }

@@ -43,19 +43,25 @@ __device__ __forceinline__ uint4 narrow_vectors(uint4 lo, uint4 hi) {
 
 // ---- linear streams ---------------------------------------------------------
 
+// One contiguous chunk of kCopyThreads * kCopyUnroll vectors per CTA.
 __global__ void __launch_bounds__(kCopyThreads)
 copy_linear_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, uint64_t vectors) {
-    const uint64_t stride = static_cast<uint64_t>(gridDim.x) * kCopyThreads;
-    uint64_t index = static_cast<uint64_t>(blockIdx.x) * kCopyThreads + threadIdx.x;
-    for (; index + stride * (kCopyUnroll - 1) < vectors; index += stride * kCopyUnroll) {
-        uint4 v[kCopyUnroll];
+    constexpr uint64_t kChunk = static_cast<uint64_t>(kCopyThreads) * kCopyUnroll;
+    const uint64_t chunks = (vectors + kChunk - 1) / kChunk;
+    for (uint64_t chunk = blockIdx.x; chunk < chunks; chunk += gridDim.x) {
+        const uint64_t base = chunk * kChunk + threadIdx.x;
+        if (base + kCopyThreads * (kCopyUnroll - 1) < vectors) {
+            uint4 v[kCopyUnroll];
 #pragma unroll
-        for (int u = 0; u < kCopyUnroll; ++u) v[u] = load_u4_stream(src + index + stride * u);
+            for (int u = 0; u < kCopyUnroll; ++u) v[u] = load_u4_stream(src + base + u * kCopyThreads);
 #pragma unroll
-        for (int u = 0; u < kCopyUnroll; ++u) store_u4_stream(dst + index + stride * u, v[u]);
-    }
-    for (; index < vectors; index += stride) {
-        store_u4_stream(dst + index, load_u4_stream(src + index));
+            for (int u = 0; u < kCopyUnroll; ++u) store_u4_stream(dst + base + u * kCopyThreads, v[u]);
+        } else {
+            for (int u = 0; u < kCopyUnroll; ++u) {
+                const uint64_t index = base + u * kCopyThreads;
+                if (index < vectors) store_u4_stream(dst + index, load_u4_stream(src + index));
+            }
+        }
     }
 }
 
@@ -63,18 +69,46 @@ copy_linear_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, uint6
 template <Move M>
 __global__ void __launch_bounds__(kCopyThreads)
 cast_linear_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, uint64_t groups) {
-    const uint64_t stride = static_cast<uint64_t>(gridDim.x) * kCopyThreads;
-    for (uint64_t index = static_cast<uint64_t>(blockIdx.x) * kCopyThreads + threadIdx.x;
-         index < groups; index += stride) {
+    constexpr int kBatch = 4;
+    constexpr uint64_t kChunk = static_cast<uint64_t>(kCopyThreads) * kBatch;
+    const uint64_t chunks = (groups + kChunk - 1) / kChunk;
+    for (uint64_t chunk = blockIdx.x; chunk < chunks; chunk += gridDim.x) {
+        const uint64_t base = chunk * kChunk + threadIdx.x;
+        const bool whole = base + kCopyThreads * (kBatch - 1) < groups;
         if constexpr (M == Move::Bf16ToF32) {
-            uint4 lo, hi;
-            widen_vector(load_u4_stream(src + index), &lo, &hi);
-            store_u4_stream(dst + 2 * index, lo);
-            store_u4_stream(dst + 2 * index + 1, hi);
+            uint4 in[kBatch];
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u) {
+                const uint64_t index = base + u * kCopyThreads;
+                if (whole || index < groups) in[u] = load_u4_stream(src + index);
+            }
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u) {
+                const uint64_t index = base + u * kCopyThreads;
+                if (whole || index < groups) {
+                    uint4 lo, hi;
+                    widen_vector(in[u], &lo, &hi);
+                    store_u4_stream(dst + 2 * index, lo);
+                    store_u4_stream(dst + 2 * index + 1, hi);
+                }
+            }
         } else {
-            const uint4 lo = load_u4_stream(src + 2 * index);
-            const uint4 hi = load_u4_stream(src + 2 * index + 1);
-            store_u4_stream(dst + index, narrow_vectors(lo, hi));
+            uint4 lo[kBatch], hi[kBatch];
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u) {
+                const uint64_t index = base + u * kCopyThreads;
+                if (whole || index < groups) {
+                    lo[u] = load_u4_stream(src + 2 * index);
+                    hi[u] = load_u4_stream(src + 2 * index + 1);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u) {
+                const uint64_t index = base + u * kCopyThreads;
+                if (whole || index < groups) {
+                    store_u4_stream(dst + index, narrow_vectors(lo[u], hi[u]));
+                }
+            }
         }
     }
 }
@@ -281,11 +315,11 @@ static int move_dispatch(const iomb_view* source, const iomb_view* destination, 
         if (move == Move::Copy) {
             const uint64_t vectors = p.leading.planes * fd.plane_bytes / 16;
             const uint64_t per_cta = static_cast<uint64_t>(kCopyThreads) * kCopyUnroll;
-            copy_linear_kernel<<<grid_for((vectors + per_cta - 1) / per_cta, 8), kCopyThreads, 0, s>>>(
+            copy_linear_kernel<<<grid_one_shot((vectors + per_cta - 1) / per_cta), kCopyThreads, 0, s>>>(
                     reinterpret_cast<const uint4*>(src), reinterpret_cast<uint4*>(dst), vectors);
         } else {
             const uint64_t groups = p.leading.planes * fd.tile_rows * fd.tile_cols * kTileSlots / 8;
-            const unsigned grid = grid_for((groups + kCopyThreads - 1) / kCopyThreads, 16);
+            const unsigned grid = grid_one_shot((groups + kCopyThreads * 4 - 1) / (kCopyThreads * 4));
             if (move == Move::Bf16ToF32) {
                 cast_linear_kernel<Move::Bf16ToF32><<<grid, kCopyThreads, 0, s>>>(
                         reinterpret_cast<const uint4*>(src), reinterpret_cast<uint4*>(dst), groups);
@@ -295,7 +329,7 @@ static int move_dispatch(const iomb_view* source, const iomb_view* destination, 
             }
         }
     } else {
-        const unsigned grid = grid_for((p.items + kCopyWarps - 1) / kCopyWarps, 8);
+        const unsigned grid = grid_one_shot((p.items + kCopyWarps - 1) / kCopyWarps);
         if (move == Move::Copy) {
             copy_tiled_kernel<<<grid, kCopyThreads, 0, s>>>(p);
         } else if (move == Move::Bf16ToF32) {

@@ -56,6 +56,11 @@ unsigned grid_for(uint64_t work_items, unsigned ctas_per_sm) {
     return static_cast<unsigned>(grid);
 }
 
+unsigned grid_one_shot(uint64_t work_items) {
+    if (work_items == 0) return 1;
+    return static_cast<unsigned>(work_items > 0x7FFFFFFFull ? 0x7FFFFFFFull : work_items);
+}
+
 static bool mul_overflows(uint64_t a, uint64_t b, uint64_t* out) {
     return __builtin_mul_overflow(a, b, out);
 }

@@ -50,4 +50,7 @@ Operand make_operand(const iomb_view& view, const ViewFacts& facts,
 // `ctas_per_sm` times, never more than `work_items`.
 unsigned grid_for(uint64_t work_items, unsigned ctas_per_sm);
 
+// Grid with one CTA per work item (kernels still loop, so the cap is harmless).
+unsigned grid_one_shot(uint64_t work_items);
+
 }  // namespace iomb

@@ -125,87 +125,106 @@ __device__ __forceinline__ void store_vector_masked(
     }
 }
 
-// Shared memory: [unit: tile_cols * g * 16 * ELEM bytes][scale: tile_cols*16*ELEM]
-//                [lanes: 16 rows x 16 floats][inverse: 16 floats]
-template <int ELEM, bool FUSED>
+// Shared memory of one CTA:
+//   [unit : tile_cols * G * 16 * ELEM bytes]  the staged rows, tile by tile
+//   [scale: tile_cols * 16 floats]            row 0 of the scale tiles, widened
+//   [lanes: 16 x 16 floats][inverse: 16 floats][flags: 16 x uint32]
+//
+// G (rows per unit) is a template parameter so that every index split below is a
+// shift. Thread t always owns the same (row, column group) of every tile it
+// touches: vector v = t % (G * ELEM) of tiles t / (G * ELEM) + k * 256 / (G * ELEM).
+template <int ELEM, int G, bool FUSED>
 __global__ void __launch_bounds__(kRmsThreads)
 rmsnorm_kernel(const RmsParams p) {
     extern __shared__ __align__(16) unsigned char smem[];
     constexpr uint32_t kTileBytes = kTileSlots * ELEM;
-    constexpr uint32_t kRowBytes = kTile * ELEM;          // one in-tile row
-    constexpr uint32_t kVectorsPerRow = kRowBytes / 16;   // 2 (16-bit) or 4 (32-bit)
+    constexpr uint32_t kRowBytes = kTile * ELEM;             // one in-tile row
+    constexpr uint32_t kVectorsPerRow = kRowBytes / 16;      // 2 (16-bit) or 4 (32-bit)
     constexpr uint32_t kPerVector = 16 / ELEM;
-    const uint32_t g = p.group_rows;
-    const uint32_t piece_bytes = g * kRowBytes;           // per tile
-    const uint32_t piece_vectors = g * kVectorsPerRow;
-    const uint32_t unit_vectors = p.tile_cols * piece_vectors;
+    constexpr uint32_t kPieceBytes = G * kRowBytes;          // per tile
+    constexpr uint32_t kPieceVectors = G * kVectorsPerRow;   // 2 .. 64, divides 256
+    constexpr uint32_t kTilesPerStep = kRmsThreads / kPieceVectors;
     unsigned char* unit = smem;
-    unsigned char* scale = unit + static_cast<size_t>(p.tile_cols) * piece_bytes;
-    float* lanes = reinterpret_cast<float*>(scale + static_cast<size_t>(p.tile_cols) * kRowBytes);
+    float* scale = reinterpret_cast<float*>(unit + static_cast<size_t>(p.tile_cols) * kPieceBytes);
+    float* lanes = scale + static_cast<size_t>(p.tile_cols) * kTile;
     float* inverse = lanes + kTile * kTile;
+    uint32_t* clean = reinterpret_cast<uint32_t*>(inverse + kTile);
+    __shared__ uint32_t scale_not_finite;
     const uint32_t tid = threadIdx.x;
+    const uint32_t v = tid % kPieceVectors;                  // vector inside a piece
+    const uint32_t tile0 = tid / kPieceVectors;
+    const uint32_t row = v / kVectorsPerRow;                 // row inside the unit
+    const uint32_t cv = v % kVectorsPerRow;
+    const uint32_t col_in_tile = cv * kPerVector;
+    const uint32_t full_tiles = p.cols / kTile;
+    const uint32_t tail_cols = p.cols % kTile;
 
-    // Stage row 0 of every scale tile once per CTA.
-    for (uint32_t i = tid; i < p.tile_cols * kVectorsPerRow; i += kRmsThreads) {
-        const uint32_t tile = i / kVectorsPerRow, v = i % kVectorsPerRow;
-        cp_async_16(scale + i * 16, p.scale_row + static_cast<size_t>(tile) * kTileBytes + v * 16);
+    // Widen row 0 of every scale tile once per CTA and note whether every
+    // logical scale value is finite.
+    if (tid == 0) scale_not_finite = 0;
+    __syncthreads();
+    for (uint32_t c = tid; c < p.tile_cols * kTile; c += kRmsThreads) {
+        const float w = decode_element<ELEM>(
+                p.scale_row + static_cast<size_t>(c / kTile) * kTileBytes + (c % kTile) * ELEM);
+        scale[c] = w;
+        if (c < p.cols && !(fabsf(w) <= 3.402823466e+38f)) scale_not_finite = 1;
     }
+    __syncthreads();
+    const bool scale_finite = scale_not_finite == 0;
 
     for (uint64_t u = blockIdx.x; u < p.units; u += gridDim.x) {
         const uint32_t group = static_cast<uint32_t>(u % p.groups_per_band);
         const uint64_t band = u / p.groups_per_band;
         const uint32_t tr = static_cast<uint32_t>(band % p.tile_rows);
         const uint64_t index = band / p.tile_rows;
-        const uint32_t row0 = group * g;                         // first in-tile row
+        const uint32_t row0 = group * G;                         // first in-tile row
         const uint32_t rows_in_band = min(kTile, p.rows - tr * kTile);
         if (row0 >= rows_in_band) continue;                      // uniform per CTA
-        const uint32_t live_rows = min(g, rows_in_band - row0);
-        const size_t band_offset_rows = static_cast<size_t>(row0) * kRowBytes;
+        const uint32_t live_rows = min(static_cast<uint32_t>(G), rows_in_band - row0);
+        const bool row_live = row < live_rows;
         auto band_base = [&](const Operand& operand) {
             const uint64_t plane = operand_plane(operand, p.leading, index);
             return operand.base
                     + (plane * operand.tile_rows + tr) * operand.tile_cols
                             * static_cast<uint64_t>(kTileBytes)
-                    + band_offset_rows;
+                    + static_cast<size_t>(row0) * kRowBytes + v * 16;
         };
-        const unsigned char* x_band = band_base(p.x);
-        unsigned char* out_band = band_base(p.out);
+        // Per-thread cursors: the same vector of successive tiles.
+        const unsigned char* x_cursor = band_base(p.x);
+        unsigned char* out_cursor = band_base(p.out);
+        unsigned char* unit_cursor = unit + static_cast<size_t>(tile0) * kPieceBytes + v * 16;
 
         // ---- stage the unit ---------------------------------------------
         if constexpr (!FUSED) {
-            for (uint32_t i = tid; i < unit_vectors; i += kRmsThreads) {
-                const uint32_t tile = i / piece_vectors, v = i % piece_vectors;
-                cp_async_16(unit + static_cast<size_t>(i) * 16,
-                            x_band + static_cast<size_t>(tile) * kTileBytes + v * 16);
+            for (uint32_t tile = tile0; tile < p.tile_cols; tile += kTilesPerStep) {
+                cp_async_16(unit + static_cast<size_t>(tile) * kPieceBytes + v * 16,
+                            x_cursor + static_cast<size_t>(tile) * kTileBytes);
             }
         } else {
-            const unsigned char* r_band = band_base(p.residual);
-            unsigned char* s_band = band_base(p.sum);
+            const unsigned char* r_cursor = band_base(p.residual);
+            unsigned char* s_cursor = band_base(p.sum);
             constexpr uint32_t kBatch = 4;
-            for (uint32_t i0 = tid; i0 < unit_vectors; i0 += kRmsThreads * kBatch) {
+            for (uint32_t t0 = tile0; t0 < p.tile_cols; t0 += kTilesPerStep * kBatch) {
                 uint4 a[kBatch], b[kBatch];
 #pragma unroll
                 for (uint32_t k = 0; k < kBatch; ++k) {
-                    const uint32_t i = i0 + k * kRmsThreads;
-                    if (i < unit_vectors) {
-                        const uint32_t tile = i / piece_vectors, v = i % piece_vectors;
-                        const size_t offset = static_cast<size_t>(tile) * kTileBytes + v * 16;
-                        a[k] = load_u4_stream(x_band + offset);
-                        b[k] = load_u4_stream(r_band + offset);
+                    const uint32_t tile = t0 + k * kTilesPerStep;
+                    if (tile < p.tile_cols) {
+                        a[k] = load_u4_stream(x_cursor + static_cast<size_t>(tile) * kTileBytes);
+                        b[k] = load_u4_stream(r_cursor + static_cast<size_t>(tile) * kTileBytes);
                     }
                 }
 #pragma unroll
                 for (uint32_t k = 0; k < kBatch; ++k) {
-                    const uint32_t i = i0 + k * kRmsThreads;
-                    if (i < unit_vectors) {
-                        const uint32_t tile = i / piece_vectors, v = i % piece_vectors;
-                        const uint32_t row = v / kVectorsPerRow;
-                        const uint32_t col = tile * kTile + (v % kVectorsPerRow) * kPerVector;
-                        const uint4 s = add_vectors<ELEM>(a[k], b[k]);
-                        *reinterpret_cast<uint4*>(unit + static_cast<size_t>(i) * 16) = s;
-                        if (row < live_rows && col < p.cols) {
+                    const uint32_t tile = t0 + k * kTilesPerStep;
+                    if (tile < p.tile_cols) {
+                        const uint4 total = add_vectors<ELEM>(a[k], b[k]);
+                        *reinterpret_cast<uint4*>(
+                                unit + static_cast<size_t>(tile) * kPieceBytes + v * 16) = total;
+                        const uint32_t col = tile * kTile + col_in_tile;
+                        if (row_live && col < p.cols) {
                             store_vector_masked<ELEM>(
-                                    s_band + static_cast<size_t>(tile) * kTileBytes + v * 16, s,
+                                    s_cursor + static_cast<size_t>(tile) * kTileBytes, total,
                                     min(kPerVector, p.cols - col));
                         }
                     }
@@ -217,80 +236,123 @@ rmsnorm_kernel(const RmsParams p) {
 
         // ---- pass 1: row sums of squares ---------------------------------
         if (p.order == IOMB_RMS_LANES16) {
-            if (tid < g * kTile) {
-                const uint32_t row = tid / kTile, lane = tid % kTile;
-                const unsigned char* cursor = unit + (row * kTile + lane) * ELEM;
-                const uint32_t full_tiles = p.cols / kTile;
+            if (tid < G * kTile) {
+                const uint32_t chain_row = tid / kTile, lane = tid % kTile;
+                const unsigned char* cursor = unit + (chain_row * kTile + lane) * ELEM;
                 float acc = 0.0f;
 #pragma unroll 8
                 for (uint32_t tile = 0; tile < full_tiles; ++tile) {
                     acc = accumulate_square(acc, decode_element<ELEM>(cursor));
-                    cursor += piece_bytes;
+                    cursor += kPieceBytes;
                 }
-                if (full_tiles < p.tile_cols && lane < p.cols % kTile) {
+                if (lane < tail_cols) {
                     acc = accumulate_square(acc, decode_element<ELEM>(cursor));
                 }
-                lanes[row * kTile + lane] = acc;
+                lanes[chain_row * kTile + lane] = acc;
             }
             __syncthreads();
-            if (tid < g) {
+        }
+        if (tid < G) {
+            float sum;
+            if (p.order == IOMB_RMS_LANES16) {
                 const float* l = lanes + tid * kTile;
                 float total[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     total[j] = __fadd_rn(__fadd_rn(__fadd_rn(l[j], l[j + 4]), l[j + 8]), l[j + 12]);
                 }
-                const float sum = __fadd_rn(__fadd_rn(total[0], total[2]),
-                                            __fadd_rn(total[1], total[3]));
-                const float mean = __fdiv_rn(sum, static_cast<float>(p.cols));
-                const float root = __fsqrt_rn(__fadd_rn(mean, p.eps));
-                inverse[tid] = __fdiv_rn(1.0f, root);
-            }
-        } else {
-            if (tid < g) {
+                sum = __fadd_rn(__fadd_rn(total[0], total[2]), __fadd_rn(total[1], total[3]));
+            } else {
                 const unsigned char* cursor = unit + tid * kRowBytes;
-                float sum = 0.0f;
-                uint32_t remaining = p.cols;
-                for (uint32_t tile = 0; tile < p.tile_cols; ++tile) {
-                    const uint32_t count = min(kTile, remaining);
-                    if (count == kTile) {
+                sum = 0.0f;
+                for (uint32_t tile = 0; tile < full_tiles; ++tile) {
 #pragma unroll
-                        for (uint32_t c = 0; c < kTile; ++c) {
-                            sum = accumulate_square(sum, decode_element<ELEM>(cursor + c * ELEM));
-                        }
-                    } else {
-                        for (uint32_t c = 0; c < count; ++c) {
-                            sum = accumulate_square(sum, decode_element<ELEM>(cursor + c * ELEM));
-                        }
+                    for (uint32_t c = 0; c < kTile; ++c) {
+                        sum = accumulate_square(sum, decode_element<ELEM>(cursor + c * ELEM));
                     }
-                    remaining -= count;
-                    cursor += piece_bytes;
+                    cursor += kPieceBytes;
                 }
-                const float mean = __fdiv_rn(sum, static_cast<float>(p.cols));
-                const float root = __fsqrt_rn(__fadd_rn(mean, p.eps));
-                inverse[tid] = __fdiv_rn(1.0f, root);
+                for (uint32_t c = 0; c < tail_cols; ++c) {
+                    sum = accumulate_square(sum, decode_element<ELEM>(cursor + c * ELEM));
+                }
             }
+            const float mean = __fdiv_rn(sum, static_cast<float>(p.cols));
+            const float root = __fsqrt_rn(__fadd_rn(mean, p.eps));
+            inverse[tid] = __fdiv_rn(1.0f, root);
+            // With a finite, not vanishing sum every |x * inv| stays near
+            // sqrt(F) at most, so (x * inv) * w cannot be a NaN for finite w and
+            // the canonical-NaN fix-up can be skipped for the whole row.
+            clean[tid] = (sum >= 5.421010862e-20f && sum <= 3.402823466e+38f && scale_finite)
+                    ? 1u : 0u;
         }
         __syncthreads();
 
         // ---- pass 2: normalise, scale, encode, store ----------------------
-        for (uint32_t i = tid; i < unit_vectors; i += kRmsThreads) {
-            const uint32_t tile = i / piece_vectors, v = i % piece_vectors;
-            const uint32_t row = v / kVectorsPerRow;
-            const uint32_t cv = v % kVectorsPerRow;
-            const uint32_t col = tile * kTile + cv * kPerVector;
-            if (row >= live_rows || col >= p.cols) continue;
-            const uint4 xv = *reinterpret_cast<const uint4*>(unit + static_cast<size_t>(i) * 16);
-            const uint4 y = normalize_vector<ELEM>(
-                    xv, scale + (static_cast<size_t>(tile) * kVectorsPerRow + cv) * 16,
-                    inverse[row]);
-            store_vector_masked<ELEM>(
-                    out_band + static_cast<size_t>(tile) * kTileBytes + v * 16, y,
-                    min(kPerVector, p.cols - col));
+        if (row_live) {
+            const float inv = inverse[row];
+            const bool fast = clean[row] != 0;
+            const float* w_cursor = scale + col_in_tile;
+            auto emit = [&](uint32_t tile, uint32_t valid) {
+                const uint4 xv = *reinterpret_cast<const uint4*>(
+                        unit + static_cast<size_t>(tile) * kPieceBytes + v * 16);
+                const float* w = w_cursor + tile * kTile;
+                uint4 y;
+                if constexpr (ELEM == 2) {
+                    const float4 w0 = *reinterpret_cast<const float4*>(w);
+                    const float4 w1 = *reinterpret_cast<const float4*>(w + 4);
+                    const float r0 = __fmul_rn(__fmul_rn(bf16_lo(xv.x), inv), w0.x);
+                    const float r1 = __fmul_rn(__fmul_rn(bf16_hi(xv.x), inv), w0.y);
+                    const float r2 = __fmul_rn(__fmul_rn(bf16_lo(xv.y), inv), w0.z);
+                    const float r3 = __fmul_rn(__fmul_rn(bf16_hi(xv.y), inv), w0.w);
+                    const float r4 = __fmul_rn(__fmul_rn(bf16_lo(xv.z), inv), w1.x);
+                    const float r5 = __fmul_rn(__fmul_rn(bf16_hi(xv.z), inv), w1.y);
+                    const float r6 = __fmul_rn(__fmul_rn(bf16_lo(xv.w), inv), w1.z);
+                    const float r7 = __fmul_rn(__fmul_rn(bf16_hi(xv.w), inv), w1.w);
+                    if (fast) {
+                        y = make_uint4(pack_bf16x2(r0, r1), pack_bf16x2(r2, r3),
+                                       pack_bf16x2(r4, r5), pack_bf16x2(r6, r7));
+                    } else {
+                        y = make_uint4(pack_bf16x2_canonical(r0, r1), pack_bf16x2_canonical(r2, r3),
+                                       pack_bf16x2_canonical(r4, r5), pack_bf16x2_canonical(r6, r7));
+                    }
+                } else {
+                    const float4 w0 = *reinterpret_cast<const float4*>(w);
+                    const float r0 = __fmul_rn(__fmul_rn(__uint_as_float(xv.x), inv), w0.x);
+                    const float r1 = __fmul_rn(__fmul_rn(__uint_as_float(xv.y), inv), w0.y);
+                    const float r2 = __fmul_rn(__fmul_rn(__uint_as_float(xv.z), inv), w0.z);
+                    const float r3 = __fmul_rn(__fmul_rn(__uint_as_float(xv.w), inv), w0.w);
+                    if (fast) {
+                        y = make_uint4(__float_as_uint(r0), __float_as_uint(r1),
+                                       __float_as_uint(r2), __float_as_uint(r3));
+                    } else {
+                        y = make_uint4(f32_canonical_bits(r0), f32_canonical_bits(r1),
+                                       f32_canonical_bits(r2), f32_canonical_bits(r3));
+                    }
+                }
+                store_vector_masked<ELEM>(out_cursor + static_cast<size_t>(tile) * kTileBytes, y,
+                                          valid);
+            };
+            uint32_t tile = tile0;
+            for (; tile < full_tiles; tile += kTilesPerStep) emit(tile, kPerVector);
+            if (tile == full_tiles && tail_cols > col_in_tile) {
+                emit(tile, min(kPerVector, tail_cols - col_in_tile));
+            }
         }
+        (void)unit_cursor;
         __syncthreads();   // the unit buffer is reused by the next iteration
     }
     cp_async_wait_all();
+}
+
+template <int ELEM, bool FUSED>
+static auto pick_kernel(uint32_t g) -> void (*)(const RmsParams) {
+    switch (g) {
+        case 16: return rmsnorm_kernel<ELEM, 16, FUSED>;
+        case 8: return rmsnorm_kernel<ELEM, 8, FUSED>;
+        case 4: return rmsnorm_kernel<ELEM, 4, FUSED>;
+        case 2: return rmsnorm_kernel<ELEM, 2, FUSED>;
+        default: return rmsnorm_kernel<ELEM, 1, FUSED>;
+    }
 }
 
 static int rms_dispatch(const iomb_view* x, const iomb_view* residual, const iomb_view* scale,
@@ -351,7 +413,8 @@ static int rms_dispatch(const iomb_view* x, const iomb_view* residual, const iom
     const uint64_t row_bytes = fx.tile_cols * kTile * elem;   // one row of a band
     uint32_t g = kTile;
     while (g > 1 && g * row_bytes > kUnitCapBytes) g /= 2;
-    const uint64_t smem_bytes = g * row_bytes + row_bytes + (kTile * kTile + kTile) * sizeof(float);
+    const uint64_t smem_bytes = g * row_bytes + fx.tile_cols * kTile * sizeof(float)
+            + (kTile * kTile + 2 * kTile) * sizeof(float);
     if (smem_bytes > 200 * 1024) {
         return fail(IOMB_ERR_UNSUPPORTED, "rmsnorm: feature extent exceeds the staging capacity");
     }
@@ -383,15 +446,15 @@ static int rms_dispatch(const iomb_view* x, const iomb_view* residual, const iom
     p.eps = eps;
     p.order = static_cast<uint32_t>(order);
 
-    auto kernel = elem == 2 ? (fused ? rmsnorm_kernel<2, true> : rmsnorm_kernel<2, false>)
-                            : (fused ? rmsnorm_kernel<4, true> : rmsnorm_kernel<4, false>);
+    auto kernel = elem == 2 ? (fused ? pick_kernel<2, true>(g) : pick_kernel<2, false>(g))
+                            : (fused ? pick_kernel<4, true>(g) : pick_kernel<4, false>(g));
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(smem_bytes)) != cudaSuccess) {
         return check_launch("rmsnorm shared-memory attribute");
     }
-    const unsigned per_sm = static_cast<unsigned>(
-            smem_bytes + 1024 > 0 ? (227 * 1024) / (smem_bytes + 1024) : 1);
-    const unsigned grid = grid_for(p.units, per_sm > 0 ? (per_sm > 8 ? 8 : per_sm) : 1);
+    // One unit per CTA in launch order: the hardware scheduler keeps every SM
+    // full and neighbouring CTAs stream neighbouring bands.
+    const unsigned grid = grid_one_shot(p.units);
     kernel<<<grid, kRmsThreads, smem_bytes, static_cast<cudaStream_t>(stream)>>>(p);
     return check_launch("rmsnorm launch");
 }

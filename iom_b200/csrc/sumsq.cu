@@ -1,8 +1,8 @@
 // Whole-view FP32 sum of squares with an order that does not depend on the
 // launch geometry. No counterpart in the reference.
 //
-// The view's tiles are dealt round-robin to kSlots logical accumulators. A CTA
-// serves one slot at a time: thread t of the CTA squares and adds its share of
+// The view's tiles are cut into kSlots contiguous runs, one per logical
+// accumulator. A CTA serves one slot at a time: thread t of the CTA squares and adds its share of
 // every tile of the slot in tile order (masked to the logical extents), the 256
 // thread sums are folded by a fixed shared-memory tree into partial[slot], and
 // the CTA that finishes last folds the kSlots partials the same way. Which CTA
@@ -63,35 +63,54 @@ sumsq_kernel(const SumsqParams p) {
     const uint32_t slot_in_tile = vector * kPerVector;
     const uint32_t row = slot_in_tile / kTile, col = slot_in_tile % kTile;
     const uint64_t groups = (p.tiles + kTilesPerStep - 1) / kTilesPerStep;
+    const uint64_t per_slot = (groups + kSlots - 1) / kSlots;   // contiguous run per slot
     for (uint32_t slot = blockIdx.x; slot < kSlots; slot += gridDim.x) {
         float acc = 0.0f;
-        for (uint64_t group = slot; group < groups; group += kSlots) {
-            const uint64_t tile = group * kTilesPerStep + sub;
-            if (tile >= p.tiles) continue;
-            const uint32_t tc = static_cast<uint32_t>(tile % p.tile_cols);
-            const uint64_t band = tile / p.tile_cols;
-            const uint32_t tr = static_cast<uint32_t>(band % p.tile_rows);
-            const uint64_t index = band / p.tile_rows;
-            const uint32_t rows_left = p.rows - tr * kTile;
-            const uint32_t cols_left = p.cols - tc * kTile;
-            if (row >= rows_left || col >= cols_left) continue;
-            const uint32_t valid = min(kPerVector, cols_left - col);
-            const unsigned char* address = p.x.base
-                    + (operand_plane(p.x, p.leading, index) * p.tile_rows * p.tile_cols
-                       + static_cast<uint64_t>(tr) * p.tile_cols + tc) * kTileBytes
-                    + vector * 16;
-            const uint4 v = load_u4_stream(address);
-            float e[8];
-            if constexpr (ELEM == 2) {
-                e[0] = bf16_lo(v.x); e[1] = bf16_hi(v.x); e[2] = bf16_lo(v.y); e[3] = bf16_hi(v.y);
-                e[4] = bf16_lo(v.z); e[5] = bf16_hi(v.z); e[6] = bf16_lo(v.w); e[7] = bf16_hi(v.w);
-            } else {
-                e[0] = __uint_as_float(v.x); e[1] = __uint_as_float(v.y);
-                e[2] = __uint_as_float(v.z); e[3] = __uint_as_float(v.w);
+        // Four tiles of the slot are fetched before any is added; the adds keep
+        // tile order, so batching does not change the result.
+        constexpr uint32_t kBatch = 4;
+        const uint64_t begin = slot * per_slot;
+        const uint64_t end = min(begin + per_slot, groups);
+        for (uint64_t group0 = begin; group0 < end; group0 += kBatch) {
+            uint4 v[kBatch];
+            uint32_t valid[kBatch];
+#pragma unroll
+            for (uint32_t b = 0; b < kBatch; ++b) {
+                valid[b] = 0;
+                const uint64_t group = group0 + b;
+                const uint64_t tile = group * kTilesPerStep + sub;
+                if (group >= end || tile >= p.tiles) continue;
+                const uint32_t tc = static_cast<uint32_t>(tile % p.tile_cols);
+                const uint64_t band = tile / p.tile_cols;
+                const uint32_t tr = static_cast<uint32_t>(band % p.tile_rows);
+                const uint64_t index = band / p.tile_rows;
+                const uint32_t rows_left = p.rows - tr * kTile;
+                const uint32_t cols_left = p.cols - tc * kTile;
+                if (row >= rows_left || col >= cols_left) continue;
+                valid[b] = min(kPerVector, cols_left - col);
+                v[b] = load_u4_stream(
+                        p.x.base
+                        + (operand_plane(p.x, p.leading, index) * p.tile_rows * p.tile_cols
+                           + static_cast<uint64_t>(tr) * p.tile_cols + tc) * kTileBytes
+                        + vector * 16);
             }
 #pragma unroll
-            for (uint32_t k = 0; k < kPerVector; ++k) {
-                if (k < valid) acc = __fadd_rn(acc, __fmul_rn(e[k], e[k]));
+            for (uint32_t b = 0; b < kBatch; ++b) {
+                if (valid[b] == 0) continue;
+                float e[8];
+                if constexpr (ELEM == 2) {
+                    e[0] = bf16_lo(v[b].x); e[1] = bf16_hi(v[b].x);
+                    e[2] = bf16_lo(v[b].y); e[3] = bf16_hi(v[b].y);
+                    e[4] = bf16_lo(v[b].z); e[5] = bf16_hi(v[b].z);
+                    e[6] = bf16_lo(v[b].w); e[7] = bf16_hi(v[b].w);
+                } else {
+                    e[0] = __uint_as_float(v[b].x); e[1] = __uint_as_float(v[b].y);
+                    e[2] = __uint_as_float(v[b].z); e[3] = __uint_as_float(v[b].w);
+                }
+#pragma unroll
+                for (uint32_t k = 0; k < kPerVector; ++k) {
+                    if (k < valid[b]) acc = __fadd_rn(acc, __fmul_rn(e[k], e[k]));
+                }
             }
         }
         const float total = fold_block(acc, shared);
@@ -158,7 +177,7 @@ extern "C" int iomb_sumsq(const iomb_view* x, void* scratch, float* result, void
     if (cudaMemsetAsync(p.counter, 0, sizeof(uint32_t), s) != cudaSuccess) {
         return check_launch("sumsq counter reset");
     }
-    const unsigned grid = grid_for(kSlots, 8);
+    const unsigned grid = kSlots;
     if (f.bytes == 2) {
         sumsq_kernel<2><<<grid, kSumThreads, 0, s>>>(p);
     } else {

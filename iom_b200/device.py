@@ -1,0 +1,563 @@
+"""B200 device, tensors, workspaces and the in-order operation queue.
+
+Python mirror of the reference's backend contract for the CUDA backend it
+replaces (include/iom/device.hpp:57-131, include/iom/iom.hpp:105-373,
+src/cuda/device.cpp:349-432): one device owns one fixed data arena reserved at
+construction, tensors and workspaces are 32-byte-aligned suballocations of it,
+an operation queue is one CUDA stream, every operation returns an `oid`
+(negative = synchronous error, positive = accepted token) and `wait` observes
+completion and rethrows retained failures. All device work goes through the C
+ABI of libiom_b200.so; torch supplies device memory, streams and events only.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+from dataclasses import dataclass
+from typing import Optional
+
+import numpy as np
+import torch
+
+from . import _abi
+from .tensor import DataType, TensorSpec, TensorView, dense_plane_strides
+
+# OidError (include/iom/oid.hpp:16-23)
+OID_INVALID_ARGUMENT = -1
+OID_UNSUPPORTED = -2
+OID_OVERFLOW = -3
+OID_RESOURCE_EXHAUSTED = -4
+OID_DEVICE_ERROR = -5
+OID_INTERNAL_ERROR = -6
+
+ADD, MUL = 0, 1
+RMS_LANES16, RMS_SEQUENTIAL = 0, 1
+
+_ALIGNMENT = 256          # arena suballocation granularity (the contract needs 32)
+_MAX_QUEUES = 4           # src/device_ops.cpp:210-218
+_SEQUENCE_BITS = 55       # token = (queue_id << 55) | sequence
+
+
+class UnsupportedOperation(Exception):
+    """detail::UnsupportedOperation -> OidError::Unsupported."""
+
+
+class DeviceError(RuntimeError):
+    """A CUDA runtime failure reported by the kernel library."""
+
+
+@dataclass(frozen=True)
+class QueueConfig:
+    max_in_flight_per_queue: int = 16
+
+    def __post_init__(self):
+        if self.max_in_flight_per_queue <= 0:
+            raise ValueError("QueueConfig max_in_flight_per_queue must be nonzero")
+
+
+@dataclass(frozen=True)
+class DeviceMemoryConfig:
+    tensor_arena_bytes: int = 0
+
+
+@dataclass(frozen=True)
+class WorkspaceRequirements:
+    bytes: int = 0
+    alignment: int = 1
+
+
+def compute_staging_size(logical_nbytes: int) -> int:
+    """gpu_algorithm::compute_staging_size (include/iom/gpu_algorithm.hpp:10-20)."""
+    return logical_nbytes + (4 - logical_nbytes % 4) % 4
+
+
+def _status_to_exception(status: int) -> Exception:
+    text = _abi.last_error()
+    if status == 1:
+        return ValueError(text)
+    if status == 2:
+        return UnsupportedOperation(text)
+    if status == 3:
+        return OverflowError(text)
+    if status == 4:
+        return MemoryError(text)
+    if status == 5:
+        return DeviceError(text)
+    return RuntimeError(text)
+
+
+def _exception_to_oid(error: BaseException) -> int:
+    """map_failure (src/device_ops.cpp:422-439)."""
+    if isinstance(error, UnsupportedOperation):
+        return OID_UNSUPPORTED
+    if isinstance(error, MemoryError):
+        return OID_RESOURCE_EXHAUSTED
+    if isinstance(error, OverflowError):
+        return OID_OVERFLOW
+    if isinstance(error, (ValueError, IndexError)):
+        return OID_INVALID_ARGUMENT
+    if isinstance(error, DeviceError):
+        return OID_DEVICE_ERROR
+    return OID_DEVICE_ERROR
+
+
+class _Arena:
+    """First-fit free list with coalescing over one device allocation
+    (the role of ListAllocator, include/iom/alloc.hpp:52-80)."""
+
+    def __init__(self, capacity: int):
+        self.capacity = capacity
+        self.free = [(0, capacity)]
+        self.lock = threading.Lock()
+
+    def alloc(self, size: int) -> int:
+        size = (size + _ALIGNMENT - 1) // _ALIGNMENT * _ALIGNMENT
+        with self.lock:
+            for i, (offset, length) in enumerate(self.free):
+                if length >= size:
+                    if length == size:
+                        del self.free[i]
+                    else:
+                        self.free[i] = (offset + size, length - size)
+                    return offset
+        raise MemoryError("device tensor arena is exhausted")
+
+    def release(self, offset: int, size: int) -> None:
+        size = (size + _ALIGNMENT - 1) // _ALIGNMENT * _ALIGNMENT
+        with self.lock:
+            self.free.append((offset, size))
+            self.free.sort()
+            merged = []
+            for start, length in self.free:
+                if merged and merged[-1][0] + merged[-1][1] == start:
+                    merged[-1] = (merged[-1][0], merged[-1][1] + length)
+                else:
+                    merged.append((start, length))
+            self.free = merged
+
+
+class RawWorkspaceView:
+    """Checked byte range over one live workspace (include/iom/tensor.hpp:186-241)."""
+
+    def __init__(self, owner: Optional["RawWorkspace"] = None, offset: int = 0, nbytes: int = 0):
+        self.owner = owner
+        self.offset = offset
+        self.nbytes = nbytes
+
+    def empty(self) -> bool:
+        return self.owner is None
+
+    def byte_size(self) -> int:
+        return self.nbytes
+
+    def address(self) -> int:
+        return 0 if self.owner is None else self.owner.address + self.offset
+
+    def subrange(self, offset: int, nbytes: int) -> "RawWorkspaceView":
+        if self.owner is None:
+            raise ValueError("empty workspace view has no subrange")
+        if offset % 32 != 0:
+            raise ValueError("workspace subrange offset must stay 32-byte aligned")
+        if offset > self.owner.nbytes or nbytes > self.owner.nbytes - offset:
+            raise ValueError("workspace subrange exceeds the owner range")
+        return RawWorkspaceView(self.owner, offset, nbytes)
+
+
+class RawWorkspace:
+    """Explicitly owned raw device scratch, an arena suballocation."""
+
+    def __init__(self, device: "B200Device", nbytes: int):
+        self.device = device
+        self.nbytes = nbytes
+        self._offset = device._arena.alloc(nbytes) if nbytes else None
+        self.address = device._arena_address + self._offset if nbytes else 0
+        device._live_workspaces.add(self)
+
+    def view(self) -> RawWorkspaceView:
+        return RawWorkspaceView(self if self.nbytes else None, 0, self.nbytes)
+
+    def tensor(self) -> torch.Tensor:
+        return self.device._arena_tensor[self._offset:self._offset + self.nbytes]
+
+    def close(self) -> None:
+        if self in self.device._live_workspaces:
+            self.device._live_workspaces.discard(self)
+            if self.nbytes:
+                self.device._arena.release(self._offset, self.nbytes)
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class B200Tensor:
+    """Tensor owner: zero-filled tiled storage inside the device arena
+    (src/cuda/device_tensor.cpp:81-103)."""
+
+    def __init__(self, device: "B200Device", spec: TensorSpec):
+        self.device = device
+        self.spec = spec
+        self.storage_nbytes = spec.tiled_storage_nbytes()
+        self._offset = device._arena.alloc(self.storage_nbytes)
+        self._address = device._arena_address + self._offset
+        self._view = TensorView(self, spec, 0, dense_plane_strides(spec.shape))
+        self._closed = False
+        self.storage().zero_()
+        torch.cuda.current_stream(device.torch_device).synchronize()
+
+    def storage(self) -> torch.Tensor:
+        """The owner's raw tiled bytes as a uint8 device tensor."""
+        return self.device._arena_tensor[self._offset:self._offset + self.storage_nbytes]
+
+    def storage_address(self) -> int:
+        return self._address
+
+    def view(self) -> TensorView:
+        return self._view
+
+    def host_transfer_workspace_requirements(self, logical_nbytes: int) -> WorkspaceRequirements:
+        return WorkspaceRequirements(compute_staging_size(logical_nbytes), 32)
+
+    def _staging(self, view: TensorView, workspace: Optional[RawWorkspaceView]) -> RawWorkspaceView:
+        need = self.host_transfer_workspace_requirements(view.spec.logical_nbytes())
+        if workspace is None or workspace.empty():
+            raise ValueError("host transfer requires a staging workspace")
+        if workspace.owner.device is not self.device or workspace.owner not in self.device._live_workspaces:
+            raise ValueError("host transfer workspace belongs to another device or is dead")
+        if workspace.byte_size() < need.bytes or workspace.address() % need.alignment != 0:
+            raise ValueError("host transfer workspace is too small or misaligned")
+        return workspace
+
+    def region_from_host(self, view: TensorView, source, workspace=None) -> None:
+        """Tensor::region_from_host (src/cuda/device_tensor.cpp:140-158): synchronous."""
+        payload = np.ascontiguousarray(source).view(np.uint8).reshape(-1)
+        if payload.size != view.spec.logical_nbytes():
+            raise ValueError("host source must hold exactly logical_nbytes bytes")
+        if view.spec.data_type == DataType.BOOL and payload.size and payload.max() > 1:
+            raise ValueError("BOOL host bytes must contain zero or one")
+        staging = self._staging(view, workspace)
+        with self.device._transfer_lock:
+            stream = torch.cuda.current_stream(self.device.torch_device)
+            target = staging.owner.tensor()[staging.offset:staging.offset + payload.size]
+            target.copy_(torch.from_numpy(payload), non_blocking=True)
+            abi_view = view.as_abi()
+            status = self.device._lib.iomb_scatter(
+                ctypes.byref(abi_view), staging.address(), stream.cuda_stream)
+            if status != 0:
+                raise _status_to_exception(status)
+            stream.synchronize()
+
+    def region_to_host(self, view: TensorView, destination=None, workspace=None):
+        nbytes = view.spec.logical_nbytes()
+        staging = self._staging(view, workspace)
+        with self.device._transfer_lock:
+            stream = torch.cuda.current_stream(self.device.torch_device)
+            abi_view = view.as_abi()
+            status = self.device._lib.iomb_gather(
+                ctypes.byref(abi_view), staging.address(), stream.cuda_stream)
+            if status != 0:
+                raise _status_to_exception(status)
+            device_bytes = staging.owner.tensor()[staging.offset:staging.offset + nbytes]
+            if destination is not None:
+                out = np.asarray(destination).view(np.uint8).reshape(-1)
+                if out.size != nbytes:
+                    raise ValueError("host destination must hold exactly logical_nbytes bytes")
+                torch.from_numpy(out).copy_(device_bytes, non_blocking=True)
+                stream.synchronize()
+                return destination
+            return device_bytes.cpu().numpy()
+
+    def close(self) -> None:
+        if not self._closed:
+            self._closed = True
+            self.device._arena.release(self._offset, self.storage_nbytes)
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class B200Device:
+    """One CUDA device ordinal with a fixed tensor arena."""
+
+    def __init__(self, ordinal: int, memory: DeviceMemoryConfig, queue_config: QueueConfig):
+        if memory.tensor_arena_bytes == 0 or memory.tensor_arena_bytes % 32 != 0:
+            raise ValueError("tensor_arena_bytes must be nonzero and divisible by 32")
+        self._lib = _abi.load_library()          # raises when the kernels are not built
+        if not torch.cuda.is_available():
+            raise RuntimeError("no CUDA device: the B200 backend has no CPU fallback")
+        if ordinal < 0 or ordinal >= torch.cuda.device_count():
+            raise ValueError("invalid CUDA device ordinal")
+        self.ordinal = ordinal
+        self.torch_device = torch.device("cuda", ordinal)
+        self.queue_config = queue_config
+        try:
+            self._arena_tensor = torch.empty(memory.tensor_arena_bytes, dtype=torch.uint8,
+                                             device=self.torch_device)
+        except torch.OutOfMemoryError as error:
+            raise MemoryError(str(error)) from None
+        self._arena_address = self._arena_tensor.data_ptr()
+        self._arena = _Arena(memory.tensor_arena_bytes)
+        self._live_workspaces = set()
+        self._live_queues = 0
+        self._next_queue_id = 1
+        self._transfer_lock = threading.Lock()
+        self._lock = threading.Lock()
+
+    def backend_kind(self) -> str:
+        return "CUDA"
+
+    def backend_device(self) -> int:
+        return self.ordinal
+
+    def supported_data_types(self):
+        return tuple(DataType)
+
+    def create_tensor(self, spec: TensorSpec) -> B200Tensor:
+        with torch.cuda.device(self.torch_device):
+            return B200Tensor(self, spec)
+
+    def create_workspace(self, nbytes: int) -> RawWorkspace:
+        return RawWorkspace(self, nbytes)
+
+    def owns_workspace(self, workspace: RawWorkspace) -> bool:
+        return workspace in self._live_workspaces
+
+    def create_ops(self) -> "B200Queue":
+        with self._lock:
+            if self._live_queues >= _MAX_QUEUES:
+                raise MemoryError("device queue capacity is exhausted")
+            self._live_queues += 1
+            queue_id = self._next_queue_id
+            self._next_queue_id += 1
+        return B200Queue(self, queue_id)
+
+
+def make_b200_device(ordinal: int, memory: DeviceMemoryConfig,
+                     queue_config: QueueConfig = QueueConfig()) -> B200Device:
+    """Factory with the signature of make_cuda_device (include/iom/cuda/device.hpp:22-24)."""
+    return B200Device(ordinal, memory, queue_config)
+
+
+class B200Queue:
+    """DeviceOps: one in-order asynchronous queue = one CUDA stream."""
+
+    def __init__(self, device: B200Device, queue_id: int):
+        self._device = device
+        self._lib = device._lib
+        self._queue_id = queue_id
+        self._stream = torch.cuda.Stream(device=device.torch_device)
+        self._sequence = 0
+        self._records = {}        # sequence -> (event, owners, status cell or None)
+        self._failures = {}       # sequence -> exception
+        self._completed = 0
+        self._closed = False
+
+    # -- plumbing -----------------------------------------------------------
+    def device(self) -> B200Device:
+        return self._device
+
+    @property
+    def stream(self) -> torch.cuda.Stream:
+        return self._stream
+
+    def close(self) -> None:
+        if not self._closed:
+            self._closed = True
+            self._stream.synchronize()
+            self._records.clear()
+            with self._device._lock:
+                self._device._live_queues -= 1
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _check_view(self, view: TensorView, what: str) -> None:
+        owner = view.owner_identity()
+        if owner is None or getattr(owner, "device", None) is not self._device:
+            raise ValueError(f"{what} view owner belongs to another device")
+
+    def _retire(self, limit: int) -> None:
+        """Bounds in-flight work to the configured credit count."""
+        while len(self._records) >= limit:
+            oldest = min(self._records)
+            self._finish(oldest)
+
+    def _finish(self, sequence: int) -> None:
+        record = self._records.pop(sequence, None)
+        if record is None:
+            return
+        event, _owners, status_cell = record
+        event.synchronize()
+        if status_cell is not None and int(status_cell.item()) != 0:
+            self._failures[sequence] = ValueError("embedding index is negative or out of range")
+
+    def _submit(self, launch, owners, status_cell=None) -> int:
+        try:
+            self._retire(self._device.queue_config.max_in_flight_per_queue)
+            with torch.cuda.device(self._device.torch_device):
+                status = launch(self._stream.cuda_stream)
+                if status != 0:
+                    raise _status_to_exception(status)
+                event = torch.cuda.Event()
+                event.record(self._stream)
+                pinned = None
+                if status_cell is not None:
+                    pinned = torch.empty(1, dtype=torch.int32, pin_memory=True)
+                    with torch.cuda.stream(self._stream):
+                        pinned.copy_(status_cell, non_blocking=True)
+                    event = torch.cuda.Event()
+                    event.record(self._stream)
+            self._sequence += 1
+            self._records[self._sequence] = (event, owners, pinned)
+            return (self._queue_id << _SEQUENCE_BITS) | self._sequence
+        except BaseException as error:  # the facade is noexcept: map to an oid
+            return _exception_to_oid(error)
+
+    def wait(self, token: int) -> None:
+        """DeviceOps::wait (src/device_ops.cpp:536-568)."""
+        if token <= 0 or (token >> _SEQUENCE_BITS) != self._queue_id:
+            raise ValueError("wait token is not an accepted token of this queue")
+        sequence = token & ((1 << _SEQUENCE_BITS) - 1)
+        if sequence == 0 or sequence > self._sequence:
+            raise ValueError("wait token was never submitted")
+        for pending in sorted(s for s in self._records if s <= sequence):
+            self._finish(pending)
+        if sequence in self._failures:
+            raise self._failures[sequence]
+
+    # -- operations -----------------------------------------------------------
+    def _binary(self, op: int, lhs: TensorView, rhs: TensorView, out: TensorView) -> int:
+        try:
+            for view, what in ((lhs, "lhs"), (rhs, "rhs"), (out, "out")):
+                self._check_view(view, what)
+            a, b, c = lhs.as_abi(), rhs.as_abi(), out.as_abi()
+        except BaseException as error:
+            return _exception_to_oid(error)
+        return self._submit(
+            lambda stream: self._lib.iomb_binary(op, ctypes.byref(a), ctypes.byref(b),
+                                                 ctypes.byref(c), stream),
+            (lhs.owner, rhs.owner, out.owner))
+
+    def add(self, lhs: TensorView, rhs: TensorView, out: TensorView, workspace=None) -> int:
+        return self._binary(ADD, lhs, rhs, out)
+
+    def mul(self, lhs: TensorView, rhs: TensorView, out: TensorView, workspace=None) -> int:
+        return self._binary(MUL, lhs, rhs, out)
+
+    def sub(self, lhs, rhs, out, workspace=None) -> int:
+        return OID_UNSUPPORTED
+
+    def div(self, lhs, rhs, out, workspace=None) -> int:
+        return OID_UNSUPPORTED
+
+    def rmsnorm(self, x: TensorView, scale: TensorView, out: TensorView, eps: float,
+                workspace: Optional[RawWorkspaceView] = None, order: int = RMS_LANES16) -> int:
+        try:
+            for view, what in ((x, "x"), (scale, "scale"), (out, "out")):
+                self._check_view(view, what)
+            if workspace is not None and not workspace.empty():
+                raise ValueError("rmsnorm takes no workspace")
+            a, b, c = x.as_abi(), scale.as_abi(), out.as_abi()
+        except BaseException as error:
+            return _exception_to_oid(error)
+        return self._submit(
+            lambda stream: self._lib.iomb_rmsnorm(ctypes.byref(a), ctypes.byref(b),
+                                                  ctypes.byref(c), eps, order, stream),
+            (x.owner, scale.owner, out.owner))
+
+    def add_rmsnorm(self, x: TensorView, residual: TensorView, scale: TensorView,
+                    total: TensorView, out: TensorView, eps: float,
+                    order: int = RMS_LANES16) -> int:
+        """Extension: residual ADD fused into the following RMSNorm."""
+        try:
+            views = (x, residual, scale, total, out)
+            for view in views:
+                self._check_view(view, "add_rmsnorm")
+            abis = [v.as_abi() for v in views]
+        except BaseException as error:
+            return _exception_to_oid(error)
+        return self._submit(
+            lambda stream: self._lib.iomb_add_rmsnorm(*[ctypes.byref(v) for v in abis], eps,
+                                                      order, stream),
+            tuple(v.owner for v in views))
+
+    def copy(self, source: TensorView, destination: TensorView) -> int:
+        try:
+            self._check_view(source, "source")
+            self._check_view(destination, "destination")
+            if source.spec != destination.spec:
+                raise ValueError("copy views must have identical shape, leaf type, and quantization")
+            a, b = source.as_abi(), destination.as_abi()
+        except BaseException as error:
+            return _exception_to_oid(error)
+        return self._submit(
+            lambda stream: self._lib.iomb_copy(ctypes.byref(a), ctypes.byref(b), stream),
+            (source.owner, destination.owner))
+
+    def cast(self, source: TensorView, destination: TensorView) -> int:
+        """Extension: BF16<->F32 conversion."""
+        try:
+            self._check_view(source, "source")
+            self._check_view(destination, "destination")
+            a, b = source.as_abi(), destination.as_abi()
+        except BaseException as error:
+            return _exception_to_oid(error)
+        return self._submit(
+            lambda stream: self._lib.iomb_cast(ctypes.byref(a), ctypes.byref(b), stream),
+            (source.owner, destination.owner))
+
+    def embedding_workspace_requirements(self, table, indices, out) -> WorkspaceRequirements:
+        return WorkspaceRequirements(32, 32)
+
+    def embedding(self, table: TensorView, indices: TensorView, out: TensorView,
+                  workspace: Optional[RawWorkspaceView] = None) -> int:
+        try:
+            for view, what in ((table, "table"), (indices, "indices"), (out, "out")):
+                self._check_view(view, what)
+            if workspace is None or workspace.empty() or workspace.byte_size() < 32 \
+                    or workspace.address() % 32 != 0 \
+                    or not self._device.owns_workspace(workspace.owner):
+                raise ValueError("embedding requires a live {32,32} workspace of this device")
+            a, b, c = table.as_abi(), indices.as_abi(), out.as_abi()
+            cell = workspace.owner.tensor()[workspace.offset:workspace.offset + 4].view(torch.int32)
+        except BaseException as error:
+            return _exception_to_oid(error)
+        return self._submit(
+            lambda stream: self._lib.iomb_embedding(ctypes.byref(a), ctypes.byref(b),
+                                                    ctypes.byref(c), workspace.address(), stream),
+            (table.owner, indices.owner, out.owner, workspace.owner), status_cell=cell)
+
+    def cache_append(self, source: TensorView, destination: TensorView, a: int,
+                     workspace=None) -> int:
+        try:
+            self._check_view(source, "source")
+            self._check_view(destination, "destination")
+            if a < 0 or a >= 1 << 64:
+                raise ValueError("cache_append offset is out of range")
+            s, d = source.as_abi(), destination.as_abi()
+        except BaseException as error:
+            return _exception_to_oid(error)
+        return self._submit(
+            lambda stream: self._lib.iomb_cache_append(ctypes.byref(s), ctypes.byref(d), a, stream),
+            (source.owner, destination.owner))
+
+    # The remaining operations of the contract are not part of this backend.
+    def silu(self, *args, **kwargs) -> int:
+        return OID_UNSUPPORTED
+
+    def linear(self, *args, **kwargs) -> int:
+        return OID_UNSUPPORTED
+
+    def rope(self, *args, **kwargs) -> int:
+        return OID_UNSUPPORTED
+
+    def sdpa(self, *args, **kwargs) -> int:
+        return OID_UNSUPPORTED

@@ -77,7 +77,7 @@ def oracle() -> ctypes.CDLL:
 NUMPY_OF = {
     DataType.I8: np.int8, DataType.U8: np.uint8, DataType.I16: np.int16, DataType.U16: np.uint16,
     DataType.I32: np.int32, DataType.U32: np.uint32, DataType.I64: np.int64,
-    DataType.U64: np.uint64, DataType.F16: np.float16, DataType.BF16: np.uint16,
+    DataType.U64: np.uint64, DataType.F16: np.uint16, DataType.BF16: np.uint16,
     DataType.F32: np.float32, DataType.F64: np.float64, DataType.BOOL: np.uint8,
     DataType.F8_E4M3FN: np.uint8, DataType.F8_E5M2: np.uint8, DataType.F8_E8M0: np.uint8,
 }

@@ -1,0 +1,122 @@
+"""GPU parity: iomb_binary against the oracle, bit-exact on physical storage."""
+import numpy as np
+import pytest
+
+from iom_b200.tensor import DataType
+from gpu_support import download, gpu, like, run, upload  # noqa: F401
+from support import (HostTensor, SPECIAL_BF16, SPECIAL_F32, abi, oracle, random_payload)
+
+pytestmark = pytest.mark.gpu
+OPS = {"add": 0, "mul": 1}
+DTYPES = [DataType.I32, DataType.U32, DataType.F32, DataType.BF16]
+
+CASES = [
+    ((2, 17, 33), (2, 17, 33), (2, 17, 33)),
+    ((2, 1, 33), (1, 17, 1), (2, 17, 33)),
+    ((64, 256), (64, 256), (64, 256)),
+    ((4, 32, 48), (4, 32, 48), (4, 32, 48)),
+    ((32, 48), (1, 48), (32, 48)),
+    ((32, 48), (32, 1), (32, 48)),
+    ((1, 1), (3, 20, 35), (3, 20, 35)),
+    ((2, 3, 16, 16), (3, 1, 16), (2, 3, 16, 16)),
+    ((5, 31), (1, 1), (5, 31)),
+    ((1, 15), (1, 15), (1, 15)),
+    ((17, 1), (17, 1), (17, 1)),
+    ((2, 1, 2, 1, 2, 1, 16, 17), (1, 3, 1, 2, 1, 2, 1, 17), (2, 3, 2, 2, 2, 2, 16, 17)),
+]
+
+
+def check(queue, device, op, lhs, rhs, out, lv=None, rv=None, ov=None):
+    lv = lv or lhs.view()
+    rv = rv or rhs.view()
+    ov = ov or out.view()
+    dl, dr, do = upload(device, lhs), upload(device, rhs), upload(device, out)
+    fn = queue.add if op == "add" else queue.mul
+    run(queue, fn(like(lv, dl), like(rv, dr), like(ov, do)))
+    assert oracle().iomo_binary(OPS[op], abi(lv), abi(rv), abi(ov), 0) == 0
+    assert np.array_equal(download(do), out.storage)
+    # inputs untouched
+    assert np.array_equal(download(dl), lhs.storage)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("op", ["add", "mul"])
+@pytest.mark.parametrize("shapes", CASES)
+def test_binary_parity(gpu, dtype, op, shapes):
+    device, queue = gpu
+    rng = np.random.default_rng(abs(hash((int(dtype), op, shapes))) & 0xFFFF)
+    tensors = []
+    for shape in shapes:
+        t = HostTensor(shape, dtype).poison(0xA5)
+        t.view().copy_from_host(random_payload(rng, shape, dtype))
+        tensors.append(t)
+    check(queue, device, op, *tensors)
+
+
+@pytest.mark.parametrize("dtype,specials", [(DataType.F32, SPECIAL_F32), (DataType.BF16, SPECIAL_BF16)])
+@pytest.mark.parametrize("op", ["add", "mul"])
+def test_binary_special_values(gpu, dtype, op, specials):
+    device, queue = gpu
+    n = len(specials)
+    lhs, rhs, out = (HostTensor((n, n), dtype).poison(0x5A) for _ in range(3))
+    lhs.view().copy_from_host(np.repeat(specials, n).reshape(n, n))
+    rhs.view().copy_from_host(np.tile(specials, n).reshape(n, n))
+    check(queue, device, op, lhs, rhs, out)
+
+
+def test_binary_exhaustive_bf16_pairs(gpu):
+    """Every BF16 code against 512 boundary-rich codes, both operations."""
+    device, queue = gpu
+    a = np.arange(65536, dtype=np.uint16)
+    mant = np.array([0, 1, 2, 0x3F, 0x40, 0x41, 0x7E, 0x7F], dtype=np.uint16)
+    exps = np.array([0, 1, 2, 63, 64, 126, 127, 128, 129, 191, 192, 253, 254, 255, 120, 134],
+                    dtype=np.uint16)
+    b = np.array([(s << 15) | (e << 7) | m for s in (0, 1) for e in exps for m in mant],
+                 dtype=np.uint16)
+    b = np.concatenate([b, b])[:512]
+    lhs = HostTensor((65536, 512), DataType.BF16)
+    rhs = HostTensor((65536, 512), DataType.BF16)
+    out = HostTensor((65536, 512), DataType.BF16)
+    lhs.view().copy_from_host(np.repeat(a, 512).reshape(65536, 512))
+    rhs.view().copy_from_host(np.tile(b, 65536).reshape(65536, 512))
+    for op in ("add", "mul"):
+        dl, dr, do = upload(device, lhs), upload(device, rhs), upload(device, out)
+        fn = queue.add if op == "add" else queue.mul
+        run(queue, fn(dl.view(), dr.view(), do.view()))
+        assert oracle().iomo_binary(OPS[op], abi(lhs.view()), abi(rhs.view()), abi(out.view()), 1) == 0
+        assert np.array_equal(download(do), out.storage)
+        for t in (dl, dr, do):
+            t.close()
+
+
+def test_binary_views_and_alias(gpu):
+    device, queue = gpu
+    rng = np.random.default_rng(7)
+    lhs = HostTensor((4, 3, 17, 33), DataType.F32).poison()
+    rhs = HostTensor((3, 4, 17, 33), DataType.F32).poison()
+    out = HostTensor((2, 3, 17, 33), DataType.F32).poison()
+    for t in (lhs, rhs, out):
+        t.view().copy_from_host(random_payload(rng, t.spec.shape, DataType.F32))
+    lv = lhs.view().slice(0, 1, 2, 2)
+    rv = rhs.view().permute([1, 0]).slice(0, 0, 2, 1)
+    check(queue, device, "add", lhs, rhs, out, lv, rv, out.view())
+    # exact in-place alias
+    dl, dr = upload(device, lhs), upload(device, rhs)
+    big = lhs.view().slice(0, 0, 3, 1)
+    run(queue, queue.mul(like(big, dl), like(rhs.view().permute([1, 0]), dr), like(big, dl)))
+    assert oracle().iomo_binary(1, abi(big), abi(rhs.view().permute([1, 0])), abi(big), 0) == 0
+    assert np.array_equal(download(dl), lhs.storage)
+
+
+def test_binary_rejections(gpu):
+    device, queue = gpu
+    a = device.create_tensor(HostTensor((4, 16, 16), DataType.F32).spec)
+    b = device.create_tensor(HostTensor((3, 16, 16), DataType.F32).spec)
+    c = device.create_tensor(HostTensor((4, 16, 16), DataType.BF16).spec)
+    assert queue.add(a.view(), b.view(), a.view()) == -1          # not broadcast compatible
+    assert queue.add(a.view(), a.view(), c.view()) == -1          # dtype mismatch
+    assert queue.add(a.view().slice(0, 0, 2), a.view().slice(0, 1, 2), a.view().slice(0, 0, 2)) == -1
+    f64 = device.create_tensor(HostTensor((16, 16), DataType.F64).spec)
+    assert queue.add(f64.view(), f64.view(), f64.view()) == -2    # leaf not served
+    with pytest.raises(ValueError):
+        queue.wait(12345)

@@ -1,0 +1,162 @@
+"""GPU parity: iomb_rmsnorm / iomb_add_rmsnorm against the oracle.
+
+LANES16 order must be bit-identical to the oracle's order 0 (the reference's
+AVX-512 BF16 build) and SEQUENTIAL to order 1 (the portable build). Across
+orders the BF16 outputs may differ by at most one code and F32 outputs by at
+most 2e-6 relative.
+"""
+import numpy as np
+import pytest
+
+from iom_b200.device import RMS_LANES16, RMS_SEQUENTIAL
+from iom_b200.tensor import DataType
+from gpu_support import download, gpu, like, run, upload  # noqa: F401
+from support import (HostTensor, SPECIAL_BF16, SPECIAL_F32, abi, bf16_bits_to_f32, logical,
+                     oracle, random_payload)
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = [(1, 1), (15, 17), (16, 16), (17, 33), (2, 3, 16, 31), (33, 15), (4, 256),
+          (64, 2048), (40, 8192), (3, 5000), (2, 2, 1, 2, 1, 2, 17, 48)]
+
+
+def seeded(shape, dtype, rng, kind="normal", poison=0xA5):
+    t = HostTensor(shape, dtype).poison(poison)
+    t.view().copy_from_host(random_payload(rng, shape, dtype, kind))
+    return t
+
+
+@pytest.mark.parametrize("dtype", [DataType.BF16, DataType.F32])
+@pytest.mark.parametrize("shape", SHAPES)
+@pytest.mark.parametrize("order", [RMS_LANES16, RMS_SEQUENTIAL])
+def test_rmsnorm_parity(gpu, dtype, shape, order):
+    device, queue = gpu
+    rng = np.random.default_rng(abs(hash((int(dtype), shape))) & 0xFFFF)
+    x = seeded(shape, dtype, rng)
+    w = seeded((1, shape[-1]), dtype, rng)
+    out = seeded(shape, dtype, rng)
+    dx, dw, do = upload(device, x), upload(device, w), upload(device, out)
+    for eps in (1e-5, 0.0):
+        run(queue, queue.rmsnorm(dx.view(), dw.view(), do.view(), eps, order=order))
+        # The oracle's order 0 applies lanes to BF16 only; F32 LANES16 has no
+        # reference counterpart and is checked by tolerance below.
+        if dtype == DataType.BF16 or order == RMS_SEQUENTIAL:
+            assert oracle().iomo_rmsnorm(abi(x.view()), abi(w.view()), abi(out.view()), eps, order) == 0
+            assert np.array_equal(download(do), out.storage)
+        else:
+            assert oracle().iomo_rmsnorm(abi(x.view()), abi(w.view()), abi(out.view()), eps, 1) == 0
+            got = HostTensor(shape, dtype, fill=None)
+            got.storage[:] = download(do)
+            ref = logical(out.view()).astype(np.float64)
+            err = np.abs(logical(got.view()).astype(np.float64) - ref)
+            assert np.all(err <= 2e-6 * np.abs(ref) + 1e-30)
+            # padding and everything outside the logical window stay untouched
+            mask = HostTensor(shape, dtype).poison(0)
+            mask.view().copy_from_host(np.full(shape, 0xFFFFFFFF, dtype=np.uint32))
+            outside = mask.storage == 0
+            assert np.array_equal(got.storage[outside], out.storage[outside])
+    assert np.array_equal(download(dx), x.storage)
+
+
+def test_rmsnorm_orders_within_one_bf16_code(gpu):
+    device, queue = gpu
+    rng = np.random.default_rng(5)
+    x = seeded((256, 2048), DataType.BF16, rng)
+    w = seeded((1, 2048), DataType.BF16, rng)
+    outs = []
+    dx, dw = upload(device, x), upload(device, w)
+    for order in (RMS_LANES16, RMS_SEQUENTIAL):
+        do = device.create_tensor(x.spec)
+        run(queue, queue.rmsnorm(dx.view(), dw.view(), do.view(), 1e-5, order=order))
+        outs.append(download(do).view(np.uint16).astype(np.int32))
+    assert np.max(np.abs(outs[0] - outs[1])) <= 1
+
+
+@pytest.mark.parametrize("dtype,specials", [(DataType.F32, SPECIAL_F32), (DataType.BF16, SPECIAL_BF16)])
+@pytest.mark.parametrize("order", [RMS_LANES16, RMS_SEQUENTIAL])
+def test_rmsnorm_special_rows(gpu, dtype, specials, order):
+    device, queue = gpu
+    rng = np.random.default_rng(3)
+    n = len(specials)
+    base = random_payload(rng, (n + 2, 40), dtype, "normal")
+    raw = base.view(np.uint32 if dtype == DataType.F32 else np.uint16)
+    for i, code in enumerate(specials):
+        raw[i, (3 * i) % 40] = code
+    raw[n, :] = specials[4]
+    raw[n + 1, :] = specials[8]
+    scale = random_payload(rng, (1, 40), dtype, "normal")
+    sraw = scale.view(np.uint32 if dtype == DataType.F32 else np.uint16)
+    sraw[0, 5] = specials[10]
+    sraw[0, 6] = specials[12]
+    x = HostTensor((n + 2, 40), dtype).poison()
+    w = HostTensor((1, 40), dtype).poison()
+    out = HostTensor((n + 2, 40), dtype).poison()
+    x.view().copy_from_host(base)
+    w.view().copy_from_host(scale)
+    dx, dw, do = upload(device, x), upload(device, w), upload(device, out)
+    for eps in (0.0, 1e-5, float(np.finfo(np.float32).max), float(np.finfo(np.float32).smallest_subnormal)):
+        run(queue, queue.rmsnorm(dx.view(), dw.view(), do.view(), eps, order=order))
+        oracle_order = order if dtype == DataType.BF16 else 1
+        assert oracle().iomo_rmsnorm(abi(x.view()), abi(w.view()), abi(out.view()), eps, oracle_order) == 0
+        got = download(do)
+        if dtype == DataType.BF16 or order == RMS_SEQUENTIAL:
+            assert np.array_equal(got, out.storage)
+        else:
+            a = got.view(np.uint32)
+            b = out.storage.view(np.uint32)
+            nan_a = (a & 0x7FFFFFFF) > 0x7F800000
+            nan_b = (b & 0x7FFFFFFF) > 0x7F800000
+            assert np.array_equal(nan_a, nan_b)
+            af, bf = a.view(np.float32).astype(np.float64), b.view(np.float32).astype(np.float64)
+            fin = np.isfinite(bf) & ~nan_b
+            assert np.array_equal(a[~fin], b[~fin])
+            assert np.all(np.abs(af[fin] - bf[fin]) <= 2e-6 * np.abs(bf[fin]) + 1e-44)
+
+
+def test_rmsnorm_rejections(gpu):
+    device, queue = gpu
+    x = device.create_tensor(HostTensor((16, 32), DataType.BF16).spec)
+    w = device.create_tensor(HostTensor((1, 32), DataType.BF16).spec)
+    w2 = device.create_tensor(HostTensor((2, 32), DataType.BF16).spec)
+    o = device.create_tensor(HostTensor((16, 32), DataType.BF16).spec)
+    assert queue.rmsnorm(x.view(), w.view(), x.view(), 1e-5) == -1     # output shares input owner
+    assert queue.rmsnorm(x.view(), w2.view(), o.view(), 1e-5) == -1    # scale not [1,F]
+    for eps in (-1.0, float("inf"), float("nan")):
+        assert queue.rmsnorm(x.view(), w.view(), o.view(), eps) == -1
+    i32 = device.create_tensor(HostTensor((16, 32), DataType.I32).spec)
+    wi = device.create_tensor(HostTensor((1, 32), DataType.I32).spec)
+    oi = device.create_tensor(HostTensor((16, 32), DataType.I32).spec)
+    assert queue.rmsnorm(i32.view(), wi.view(), oi.view(), 1e-5) == -2
+
+
+@pytest.mark.parametrize("dtype", [DataType.BF16, DataType.F32])
+@pytest.mark.parametrize("shape", [(17, 33), (64, 2048), (3, 16, 8192), (2, 3, 5, 100)])
+@pytest.mark.parametrize("order", [RMS_LANES16, RMS_SEQUENTIAL])
+def test_add_rmsnorm_equals_add_then_rmsnorm(gpu, dtype, shape, order):
+    """The fused entry stores the rounded sum and normalises the rounded value."""
+    device, queue = gpu
+    rng = np.random.default_rng(abs(hash((int(dtype), shape, order))) & 0xFFFF)
+    x = seeded(shape, dtype, rng)
+    r = seeded(shape, dtype, rng)
+    w = seeded((1, shape[-1]), dtype, rng)
+    s = seeded(shape, dtype, rng)
+    out = seeded(shape, dtype, rng)
+    dx, dr, dw, ds, do = (upload(device, t) for t in (x, r, w, s, out))
+    run(queue, queue.add_rmsnorm(dx.view(), dr.view(), dw.view(), ds.view(), do.view(), 1e-5, order=order))
+    # unfused on the device: must be bit-identical to the fused result
+    ds2, do2 = upload(device, s), upload(device, out)
+    run(queue, queue.add(dx.view(), dr.view(), ds2.view()))
+    run(queue, queue.rmsnorm(ds2.view(), dw.view(), do2.view(), 1e-5, order=order))
+    assert np.array_equal(download(ds), download(ds2))
+    assert np.array_equal(download(do), download(do2))
+    # and the stored sum equals the oracle's ADD
+    assert oracle().iomo_binary(0, abi(x.view()), abi(r.view()), abi(s.view()), 0) == 0
+    assert np.array_equal(download(ds), s.storage)
+    if dtype == DataType.BF16 or order == RMS_SEQUENTIAL:
+        assert oracle().iomo_rmsnorm(abi(s.view()), abi(w.view()), abi(out.view()), 1e-5, order) == 0
+        assert np.array_equal(download(do), out.storage)
+    # in-place residual update: sum aliases x exactly
+    dx3, do3 = upload(device, x), upload(device, out)
+    run(queue, queue.add_rmsnorm(dx3.view(), dr.view(), dw.view(), dx3.view(), do3.view(), 1e-5, order=order))
+    assert np.array_equal(download(dx3), download(ds))
+    assert np.array_equal(download(do3), download(do))
