@@ -106,35 +106,43 @@ struct BinaryParams {
 constexpr int kTiledThreads = 256;
 constexpr int kTiledWarps = kTiledThreads / 32;
 
-// Loads one operand's 16-byte vector for (tile row tr, tile column tc, slot
-// offset `slot` inside the tile). ELEM is the leaf size in bytes. A broadcast
-// operand replicates its row 0 / column 0 value into the vector.
+// Per-item cursor of one operand for one lane vector: the address of the
+// vector in tile column 0 of the operand's band plus the byte step per tile
+// column (zero for a column-broadcast operand). A broadcast operand reads its
+// row 0 / column 0 instead of the lane's own row / column.
+struct Cursor {
+    const unsigned char* address;
+    uint32_t step;
+    uint32_t scalar;   // column broadcast: replicate one element
+};
+
 template <int ELEM>
-__device__ __forceinline__ uint4 load_operand(
-        const Operand& operand, uint64_t plane, uint32_t tr, uint32_t tc, uint32_t slot) {
+__device__ __forceinline__ Cursor make_cursor(
+        const Operand& operand, uint64_t plane, uint32_t tr, uint32_t slot) {
     constexpr uint32_t kTileBytes = kTileSlots * ELEM;
-    constexpr uint32_t kPerVector = 16 / ELEM;
-    const uint32_t row = slot / kTile;
-    const uint32_t col = slot % kTile;
+    const uint32_t row = operand.bc_rows ? 0u : slot / kTile;
+    const uint32_t col = operand.bc_cols ? 0u : slot % kTile;
     const uint32_t otr = operand.bc_rows ? 0u : tr;
-    const uint32_t otc = operand.bc_cols ? 0u : tc;
-    const unsigned char* tile = operand.base
-            + ((plane * operand.tile_rows + otr) * operand.tile_cols + otc)
-                    * static_cast<uint64_t>(kTileBytes);
-    const uint32_t orow = operand.bc_rows ? 0u : row;
-    if (!operand.bc_cols) {
-        return load_u4(tile + (orow * kTile + col) * ELEM);
-    }
-    // Column broadcast: one scalar per row, replicated.
+    Cursor cursor;
+    cursor.address = operand.base
+            + (plane * operand.tile_rows + otr) * operand.tile_cols
+                    * static_cast<uint64_t>(kTileBytes)
+            + (row * kTile + col) * ELEM;
+    cursor.step = operand.bc_cols ? 0u : kTileBytes;
+    cursor.scalar = operand.bc_cols;
+    return cursor;
+}
+
+template <int ELEM>
+__device__ __forceinline__ uint4 load_cursor(const Cursor& cursor, uint32_t tc) {
+    const unsigned char* address = cursor.address + static_cast<uint64_t>(tc) * cursor.step;
+    if (!cursor.scalar) return load_u4(address);
     if constexpr (ELEM == 4) {
-        const uint32_t value =
-                *reinterpret_cast<const uint32_t*>(tile + orow * kTile * ELEM);
+        const uint32_t value = *reinterpret_cast<const uint32_t*>(address);
         return make_uint4(value, value, value, value);
     } else {
-        const uint32_t half =
-                *reinterpret_cast<const uint16_t*>(tile + orow * kTile * ELEM);
+        const uint32_t half = *reinterpret_cast<const uint16_t*>(address);
         const uint32_t value = half | (half << 16);
-        (void)kPerVector;
         return make_uint4(value, value, value, value);
     }
 }
@@ -184,6 +192,13 @@ binary_tiled_kernel(const BinaryParams p) {
                 + (out_plane * p.out.tile_rows + tr) * p.out.tile_cols
                         * static_cast<uint64_t>(kTileBytes);
         const uint32_t rows_left = p.rows - tr * kTile;   // >= 1
+        Cursor lhs_cursor[kVectorsPerLane], rhs_cursor[kVectorsPerLane];
+#pragma unroll
+        for (uint32_t v = 0; v < kVectorsPerLane; ++v) {
+            const uint32_t slot = (v * 512 + lane * 16) / ELEM;
+            lhs_cursor[v] = make_cursor<ELEM>(p.lhs, lhs_plane, tr, slot);
+            rhs_cursor[v] = make_cursor<ELEM>(p.rhs, rhs_plane, tr, slot);
+        }
         // kBatch tiles per iteration: four 16-byte loads per operand and lane
         // are in flight before the first store.
         constexpr uint32_t kBatch = 4 / kVectorsPerLane;
@@ -195,9 +210,8 @@ binary_tiled_kernel(const BinaryParams p) {
                 if (tc < last) {
 #pragma unroll
                     for (uint32_t v = 0; v < kVectorsPerLane; ++v) {
-                        const uint32_t slot = (v * 512 + lane * 16) / ELEM;
-                        a[k][v] = load_operand<ELEM>(p.lhs, lhs_plane, tr, tc, slot);
-                        b[k][v] = load_operand<ELEM>(p.rhs, rhs_plane, tr, tc, slot);
+                        a[k][v] = load_cursor<ELEM>(lhs_cursor[v], tc);
+                        b[k][v] = load_cursor<ELEM>(rhs_cursor[v], tc);
                     }
                 }
             }

@@ -126,14 +126,17 @@ __device__ __forceinline__ void store_vector_masked(
 }
 
 // Shared memory of one CTA:
-//   [unit : tile_cols * G * 16 * ELEM bytes]  the staged rows, tile by tile
-//   [scale: tile_cols * 16 floats]            row 0 of the scale tiles, widened
-//   [lanes: 16 x 16 floats][inverse: 16 floats][flags: 16 x uint32]
+//   [unit : tile_cols * G * 16 * ELEM bytes]  the staged rows of x, tile by tile
+//   [unit2: same size, fused only]            the staged rows of the residual
+//   [scale: tile_cols * 16 floats, SCALE_SMEM only] row 0 of the scale tiles, widened
+//   [lanes: 16 x 16 floats][inverse: 16 floats][clean: 16 x uint32]
 //
 // G (rows per unit) is a template parameter so that every index split below is a
 // shift. Thread t always owns the same (row, column group) of every tile it
 // touches: vector v = t % (G * ELEM) of tiles t / (G * ELEM) + k * 256 / (G * ELEM).
-template <int ELEM, int G, bool FUSED>
+// Every global read of x (and the residual) is an asynchronous 16-byte copy
+// into shared memory, so a CTA has its whole unit in flight at once.
+template <int ELEM, int G, bool FUSED, bool SCALE_SMEM>
 __global__ void __launch_bounds__(kRmsThreads)
 rmsnorm_kernel(const RmsParams p) {
     extern __shared__ __align__(16) unsigned char smem[];
@@ -144,12 +147,13 @@ rmsnorm_kernel(const RmsParams p) {
     constexpr uint32_t kPieceBytes = G * kRowBytes;          // per tile
     constexpr uint32_t kPieceVectors = G * kVectorsPerRow;   // 2 .. 64, divides 256
     constexpr uint32_t kTilesPerStep = kRmsThreads / kPieceVectors;
+    const size_t unit_bytes = static_cast<size_t>(p.tile_cols) * kPieceBytes;
     unsigned char* unit = smem;
-    float* scale = reinterpret_cast<float*>(unit + static_cast<size_t>(p.tile_cols) * kPieceBytes);
-    float* lanes = scale + static_cast<size_t>(p.tile_cols) * kTile;
+    unsigned char* unit2 = unit + unit_bytes;
+    float* scale = reinterpret_cast<float*>(unit + (FUSED ? 2 : 1) * unit_bytes);
+    float* lanes = scale + (SCALE_SMEM ? static_cast<size_t>(p.tile_cols) * kTile : 0);
     float* inverse = lanes + kTile * kTile;
     uint32_t* clean = reinterpret_cast<uint32_t*>(inverse + kTile);
-    __shared__ uint32_t scale_not_finite;
     const uint32_t tid = threadIdx.x;
     const uint32_t v = tid % kPieceVectors;                  // vector inside a piece
     const uint32_t tile0 = tid / kPieceVectors;
@@ -159,14 +163,15 @@ rmsnorm_kernel(const RmsParams p) {
     const uint32_t full_tiles = p.cols / kTile;
     const uint32_t tail_cols = p.cols % kTile;
 
-    // Widen row 0 of every scale tile once per CTA and note whether every
-    // logical scale value is finite.
+    // Once per CTA: widen row 0 of every scale tile into shared memory (when it
+    // fits) and note whether every logical scale value is finite.
+    __shared__ uint32_t scale_not_finite;
     if (tid == 0) scale_not_finite = 0;
     __syncthreads();
     for (uint32_t c = tid; c < p.tile_cols * kTile; c += kRmsThreads) {
         const float w = decode_element<ELEM>(
                 p.scale_row + static_cast<size_t>(c / kTile) * kTileBytes + (c % kTile) * ELEM);
-        scale[c] = w;
+        if constexpr (SCALE_SMEM) scale[c] = w;
         if (c < p.cols && !(fabsf(w) <= 3.402823466e+38f)) scale_not_finite = 1;
     }
     __syncthreads();
@@ -192,46 +197,39 @@ rmsnorm_kernel(const RmsParams p) {
         // Per-thread cursors: the same vector of successive tiles.
         const unsigned char* x_cursor = band_base(p.x);
         unsigned char* out_cursor = band_base(p.out);
-        unsigned char* unit_cursor = unit + static_cast<size_t>(tile0) * kPieceBytes + v * 16;
 
         // ---- stage the unit ---------------------------------------------
-        if constexpr (!FUSED) {
-            for (uint32_t tile = tile0; tile < p.tile_cols; tile += kTilesPerStep) {
-                cp_async_16(unit + static_cast<size_t>(tile) * kPieceBytes + v * 16,
-                            x_cursor + static_cast<size_t>(tile) * kTileBytes);
-            }
-        } else {
+        for (uint32_t tile = tile0; tile < p.tile_cols; tile += kTilesPerStep) {
+            cp_async_16(unit + static_cast<size_t>(tile) * kPieceBytes + v * 16,
+                        x_cursor + static_cast<size_t>(tile) * kTileBytes);
+        }
+        if constexpr (FUSED) {
             const unsigned char* r_cursor = band_base(p.residual);
-            unsigned char* s_cursor = band_base(p.sum);
-            constexpr uint32_t kBatch = 4;
-            for (uint32_t t0 = tile0; t0 < p.tile_cols; t0 += kTilesPerStep * kBatch) {
-                uint4 a[kBatch], b[kBatch];
-#pragma unroll
-                for (uint32_t k = 0; k < kBatch; ++k) {
-                    const uint32_t tile = t0 + k * kTilesPerStep;
-                    if (tile < p.tile_cols) {
-                        a[k] = load_u4_stream(x_cursor + static_cast<size_t>(tile) * kTileBytes);
-                        b[k] = load_u4_stream(r_cursor + static_cast<size_t>(tile) * kTileBytes);
-                    }
-                }
-#pragma unroll
-                for (uint32_t k = 0; k < kBatch; ++k) {
-                    const uint32_t tile = t0 + k * kTilesPerStep;
-                    if (tile < p.tile_cols) {
-                        const uint4 total = add_vectors<ELEM>(a[k], b[k]);
-                        *reinterpret_cast<uint4*>(
-                                unit + static_cast<size_t>(tile) * kPieceBytes + v * 16) = total;
-                        const uint32_t col = tile * kTile + col_in_tile;
-                        if (row_live && col < p.cols) {
-                            store_vector_masked<ELEM>(
-                                    s_cursor + static_cast<size_t>(tile) * kTileBytes, total,
-                                    min(kPerVector, p.cols - col));
-                        }
-                    }
-                }
+            for (uint32_t tile = tile0; tile < p.tile_cols; tile += kTilesPerStep) {
+                cp_async_16(unit2 + static_cast<size_t>(tile) * kPieceBytes + v * 16,
+                            r_cursor + static_cast<size_t>(tile) * kTileBytes);
             }
         }
         cp_async_wait_all();
+        if constexpr (FUSED) {
+            // Each thread adds the vectors it copied itself: sum = x + residual,
+            // rounded to the leaf, kept in shared memory and stored.
+            unsigned char* s_cursor = band_base(p.sum);
+            for (uint32_t tile = tile0; tile < p.tile_cols; tile += kTilesPerStep) {
+                unsigned char* slot = unit + static_cast<size_t>(tile) * kPieceBytes + v * 16;
+                const uint4 total = add_vectors<ELEM>(
+                        *reinterpret_cast<const uint4*>(slot),
+                        *reinterpret_cast<const uint4*>(
+                                unit2 + static_cast<size_t>(tile) * kPieceBytes + v * 16));
+                *reinterpret_cast<uint4*>(slot) = total;
+                const uint32_t col = tile * kTile + col_in_tile;
+                if (row_live && col < p.cols) {
+                    store_vector_masked<ELEM>(
+                            s_cursor + static_cast<size_t>(tile) * kTileBytes, total,
+                            min(kPerVector, p.cols - col));
+                }
+            }
+        }
         __syncthreads();
 
         // ---- pass 1: row sums of squares ---------------------------------
@@ -291,23 +289,42 @@ rmsnorm_kernel(const RmsParams p) {
         if (row_live) {
             const float inv = inverse[row];
             const bool fast = clean[row] != 0;
-            const float* w_cursor = scale + col_in_tile;
             auto emit = [&](uint32_t tile, uint32_t valid) {
                 const uint4 xv = *reinterpret_cast<const uint4*>(
                         unit + static_cast<size_t>(tile) * kPieceBytes + v * 16);
-                const float* w = w_cursor + tile * kTile;
+                float w[kPerVector];
+                if constexpr (SCALE_SMEM) {
+                    const float* ws = scale + tile * kTile + col_in_tile;
+                    const float4 w0 = *reinterpret_cast<const float4*>(ws);
+                    w[0] = w0.x; w[1] = w0.y; w[2] = w0.z; w[3] = w0.w;
+                    if constexpr (ELEM == 2) {
+                        const float4 w1 = *reinterpret_cast<const float4*>(ws + 4);
+                        w[4] = w1.x; w[5] = w1.y; w[6] = w1.z; w[7] = w1.w;
+                    }
+                } else {
+                    // Large F: the scale row stays in global memory (L1-resident).
+                    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(
+                            p.scale_row + static_cast<size_t>(tile) * kTileBytes + cv * 16));
+                    if constexpr (ELEM == 2) {
+                        w[0] = bf16_lo(raw.x); w[1] = bf16_hi(raw.x);
+                        w[2] = bf16_lo(raw.y); w[3] = bf16_hi(raw.y);
+                        w[4] = bf16_lo(raw.z); w[5] = bf16_hi(raw.z);
+                        w[6] = bf16_lo(raw.w); w[7] = bf16_hi(raw.w);
+                    } else {
+                        w[0] = __uint_as_float(raw.x); w[1] = __uint_as_float(raw.y);
+                        w[2] = __uint_as_float(raw.z); w[3] = __uint_as_float(raw.w);
+                    }
+                }
                 uint4 y;
                 if constexpr (ELEM == 2) {
-                    const float4 w0 = *reinterpret_cast<const float4*>(w);
-                    const float4 w1 = *reinterpret_cast<const float4*>(w + 4);
-                    const float r0 = __fmul_rn(__fmul_rn(bf16_lo(xv.x), inv), w0.x);
-                    const float r1 = __fmul_rn(__fmul_rn(bf16_hi(xv.x), inv), w0.y);
-                    const float r2 = __fmul_rn(__fmul_rn(bf16_lo(xv.y), inv), w0.z);
-                    const float r3 = __fmul_rn(__fmul_rn(bf16_hi(xv.y), inv), w0.w);
-                    const float r4 = __fmul_rn(__fmul_rn(bf16_lo(xv.z), inv), w1.x);
-                    const float r5 = __fmul_rn(__fmul_rn(bf16_hi(xv.z), inv), w1.y);
-                    const float r6 = __fmul_rn(__fmul_rn(bf16_lo(xv.w), inv), w1.z);
-                    const float r7 = __fmul_rn(__fmul_rn(bf16_hi(xv.w), inv), w1.w);
+                    const float r0 = __fmul_rn(__fmul_rn(bf16_lo(xv.x), inv), w[0]);
+                    const float r1 = __fmul_rn(__fmul_rn(bf16_hi(xv.x), inv), w[1]);
+                    const float r2 = __fmul_rn(__fmul_rn(bf16_lo(xv.y), inv), w[2]);
+                    const float r3 = __fmul_rn(__fmul_rn(bf16_hi(xv.y), inv), w[3]);
+                    const float r4 = __fmul_rn(__fmul_rn(bf16_lo(xv.z), inv), w[4]);
+                    const float r5 = __fmul_rn(__fmul_rn(bf16_hi(xv.z), inv), w[5]);
+                    const float r6 = __fmul_rn(__fmul_rn(bf16_lo(xv.w), inv), w[6]);
+                    const float r7 = __fmul_rn(__fmul_rn(bf16_hi(xv.w), inv), w[7]);
                     if (fast) {
                         y = make_uint4(pack_bf16x2(r0, r1), pack_bf16x2(r2, r3),
                                        pack_bf16x2(r4, r5), pack_bf16x2(r6, r7));
@@ -316,11 +333,10 @@ rmsnorm_kernel(const RmsParams p) {
                                        pack_bf16x2_canonical(r4, r5), pack_bf16x2_canonical(r6, r7));
                     }
                 } else {
-                    const float4 w0 = *reinterpret_cast<const float4*>(w);
-                    const float r0 = __fmul_rn(__fmul_rn(__uint_as_float(xv.x), inv), w0.x);
-                    const float r1 = __fmul_rn(__fmul_rn(__uint_as_float(xv.y), inv), w0.y);
-                    const float r2 = __fmul_rn(__fmul_rn(__uint_as_float(xv.z), inv), w0.z);
-                    const float r3 = __fmul_rn(__fmul_rn(__uint_as_float(xv.w), inv), w0.w);
+                    const float r0 = __fmul_rn(__fmul_rn(__uint_as_float(xv.x), inv), w[0]);
+                    const float r1 = __fmul_rn(__fmul_rn(__uint_as_float(xv.y), inv), w[1]);
+                    const float r2 = __fmul_rn(__fmul_rn(__uint_as_float(xv.z), inv), w[2]);
+                    const float r3 = __fmul_rn(__fmul_rn(__uint_as_float(xv.w), inv), w[3]);
                     if (fast) {
                         y = make_uint4(__float_as_uint(r0), __float_as_uint(r1),
                                        __float_as_uint(r2), __float_as_uint(r3));
@@ -338,21 +354,30 @@ rmsnorm_kernel(const RmsParams p) {
                 emit(tile, min(kPerVector, tail_cols - col_in_tile));
             }
         }
-        (void)unit_cursor;
         __syncthreads();   // the unit buffer is reused by the next iteration
     }
     cp_async_wait_all();
 }
 
-template <int ELEM, bool FUSED>
-static auto pick_kernel(uint32_t g) -> void (*)(const RmsParams) {
+using RmsKernel = void (*)(const RmsParams);
+
+template <int ELEM, bool FUSED, bool SCALE_SMEM>
+static RmsKernel pick_kernel(uint32_t g) {
     switch (g) {
-        case 16: return rmsnorm_kernel<ELEM, 16, FUSED>;
-        case 8: return rmsnorm_kernel<ELEM, 8, FUSED>;
-        case 4: return rmsnorm_kernel<ELEM, 4, FUSED>;
-        case 2: return rmsnorm_kernel<ELEM, 2, FUSED>;
-        default: return rmsnorm_kernel<ELEM, 1, FUSED>;
+        case 16: return rmsnorm_kernel<ELEM, 16, FUSED, SCALE_SMEM>;
+        case 8: return rmsnorm_kernel<ELEM, 8, FUSED, SCALE_SMEM>;
+        case 4: return rmsnorm_kernel<ELEM, 4, FUSED, SCALE_SMEM>;
+        case 2: return rmsnorm_kernel<ELEM, 2, FUSED, SCALE_SMEM>;
+        default: return rmsnorm_kernel<ELEM, 1, FUSED, SCALE_SMEM>;
     }
+}
+
+template <int ELEM>
+static RmsKernel pick_kernel(uint32_t g, bool fused, bool scale_smem) {
+    if (fused) {
+        return scale_smem ? pick_kernel<ELEM, true, true>(g) : pick_kernel<ELEM, true, false>(g);
+    }
+    return scale_smem ? pick_kernel<ELEM, false, true>(g) : pick_kernel<ELEM, false, false>(g);
 }
 
 static int rms_dispatch(const iomb_view* x, const iomb_view* residual, const iomb_view* scale,
@@ -411,13 +436,21 @@ static int rms_dispatch(const iomb_view* x, const iomb_view* residual, const iom
     }
     const uint32_t elem = fx.bytes;
     const uint64_t row_bytes = fx.tile_cols * kTile * elem;   // one row of a band
+    // Rows per unit: the staged rows (of x, and of the residual when fused) must
+    // fit kUnitCapBytes. The widened scale row joins them in shared memory when
+    // three CTAs still fit one SM; otherwise it is read through L1.
+    const uint32_t operands = fused ? 2 : 1;
     uint32_t g = kTile;
-    while (g > 1 && g * row_bytes > kUnitCapBytes) g /= 2;
-    const uint64_t smem_bytes = g * row_bytes + fx.tile_cols * kTile * sizeof(float)
-            + (kTile * kTile + 2 * kTile) * sizeof(float);
-    if (smem_bytes > 200 * 1024) {
+    while (g > 1 && operands * g * row_bytes > kUnitCapBytes) g /= 2;
+    if (operands * g * row_bytes > 160 * 1024) {
         return fail(IOMB_ERR_UNSUPPORTED, "rmsnorm: feature extent exceeds the staging capacity");
     }
+    const uint64_t fixed_bytes = (kTile * kTile + 2 * kTile) * sizeof(float);
+    const uint64_t scale_bytes = fx.tile_cols * kTile * sizeof(float);
+    const uint64_t per_cta_budget = (227 * 1024) / 3 - 1024;
+    const bool scale_smem = operands * g * row_bytes + scale_bytes + fixed_bytes <= per_cta_budget;
+    const uint64_t smem_bytes =
+            operands * g * row_bytes + (scale_smem ? scale_bytes : 0) + fixed_bytes;
 
     RmsParams p{};
     const iomb_view* views[4] = {x, out, residual, sum};
@@ -446,15 +479,18 @@ static int rms_dispatch(const iomb_view* x, const iomb_view* residual, const iom
     p.eps = eps;
     p.order = static_cast<uint32_t>(order);
 
-    auto kernel = elem == 2 ? (fused ? pick_kernel<2, true>(g) : pick_kernel<2, false>(g))
-                            : (fused ? pick_kernel<4, true>(g) : pick_kernel<4, false>(g));
+    RmsKernel kernel = elem == 2 ? pick_kernel<2>(g, fused, scale_smem)
+                                 : pick_kernel<4>(g, fused, scale_smem);
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(smem_bytes)) != cudaSuccess) {
         return check_launch("rmsnorm shared-memory attribute");
     }
-    // One unit per CTA in launch order: the hardware scheduler keeps every SM
-    // full and neighbouring CTAs stream neighbouring bands.
-    const unsigned grid = grid_one_shot(p.units);
+    // Persistent CTAs, as many per SM as shared memory allows: the scale row is
+    // staged once per CTA and a CTA's phases overlap with its neighbours'.
+    unsigned per_sm = static_cast<unsigned>((227 * 1024) / (smem_bytes + 1024));
+    if (per_sm < 1) per_sm = 1;
+    if (per_sm > 4) per_sm = 4;
+    const unsigned grid = grid_for(p.units, per_sm);
     kernel<<<grid, kRmsThreads, smem_bytes, static_cast<cudaStream_t>(stream)>>>(p);
     return check_launch("rmsnorm launch");
 }

@@ -49,7 +49,7 @@ __device__ __forceinline__ float fold_block(float value, float* shared) {
 // first 32 threads), 32-bit leaves as 64 vectors of 4 elements. To keep every
 // thread busy a CTA walks 8 (16-bit) or 4 (32-bit) consecutive tiles of its
 // slot at once.
-template <int ELEM>
+template <int ELEM, bool DENSE>
 __global__ void __launch_bounds__(kSumThreads)
 sumsq_kernel(const SumsqParams p) {
     __shared__ float shared[kSumThreads];
@@ -80,19 +80,25 @@ sumsq_kernel(const SumsqParams p) {
                 const uint64_t group = group0 + b;
                 const uint64_t tile = group * kTilesPerStep + sub;
                 if (group >= end || tile >= p.tiles) continue;
-                const uint32_t tc = static_cast<uint32_t>(tile % p.tile_cols);
-                const uint64_t band = tile / p.tile_cols;
-                const uint32_t tr = static_cast<uint32_t>(band % p.tile_rows);
-                const uint64_t index = band / p.tile_rows;
-                const uint32_t rows_left = p.rows - tr * kTile;
-                const uint32_t cols_left = p.cols - tc * kTile;
-                if (row >= rows_left || col >= cols_left) continue;
-                valid[b] = min(kPerVector, cols_left - col);
-                v[b] = load_u4_stream(
-                        p.x.base
-                        + (operand_plane(p.x, p.leading, index) * p.tile_rows * p.tile_cols
-                           + static_cast<uint64_t>(tr) * p.tile_cols + tc) * kTileBytes
-                        + vector * 16);
+                if constexpr (DENSE) {
+                    // Tile-multiple extents and dense planes: tiles are consecutive.
+                    valid[b] = kPerVector;
+                    v[b] = load_u4_stream(p.x.base + tile * kTileBytes + vector * 16);
+                } else {
+                    const uint32_t tc = static_cast<uint32_t>(tile % p.tile_cols);
+                    const uint64_t band = tile / p.tile_cols;
+                    const uint32_t tr = static_cast<uint32_t>(band % p.tile_rows);
+                    const uint64_t index = band / p.tile_rows;
+                    const uint32_t rows_left = p.rows - tr * kTile;
+                    const uint32_t cols_left = p.cols - tc * kTile;
+                    if (row >= rows_left || col >= cols_left) continue;
+                    valid[b] = min(kPerVector, cols_left - col);
+                    v[b] = load_u4_stream(
+                            p.x.base
+                            + (operand_plane(p.x, p.leading, index) * p.tile_rows * p.tile_cols
+                               + static_cast<uint64_t>(tr) * p.tile_cols + tc) * kTileBytes
+                            + vector * 16);
+                }
             }
 #pragma unroll
             for (uint32_t b = 0; b < kBatch; ++b) {
@@ -178,10 +184,14 @@ extern "C" int iomb_sumsq(const iomb_view* x, void* scratch, float* result, void
         return check_launch("sumsq counter reset");
     }
     const unsigned grid = kSlots;
+    const bool dense = p.leading.contiguous && f.rows % kTile == 0 && f.cols % kTile == 0;
+    if (dense) p.x.base += x->plane_offset * f.plane_bytes;
     if (f.bytes == 2) {
-        sumsq_kernel<2><<<grid, kSumThreads, 0, s>>>(p);
+        if (dense) sumsq_kernel<2, true><<<grid, kSumThreads, 0, s>>>(p);
+        else sumsq_kernel<2, false><<<grid, kSumThreads, 0, s>>>(p);
     } else {
-        sumsq_kernel<4><<<grid, kSumThreads, 0, s>>>(p);
+        if (dense) sumsq_kernel<4, true><<<grid, kSumThreads, 0, s>>>(p);
+        else sumsq_kernel<4, false><<<grid, kSumThreads, 0, s>>>(p);
     }
     return check_launch("sumsq launch");
 }
