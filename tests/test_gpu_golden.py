@@ -1,0 +1,72 @@
+"""GPU kernels against the golden vectors recorded from the unmodified
+reference (no oracle in between)."""
+import numpy as np
+import pytest
+
+from iom_b200.device import RMS_LANES16, RMS_SEQUENTIAL
+from iom_b200.tensor import DataType
+from gpu_support import download, gpu, like, run, upload  # noqa: F401
+from test_golden import GOLDEN, host_from, split_shapes, view_from
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("dtype", [DataType.I32, DataType.F32, DataType.BF16])
+@pytest.mark.parametrize("op", ["add", "mul"])
+def test_binary_golden_gpu(gpu, dtype, op):
+    device, queue = gpu
+    for case in range(5):
+        key = f"binary_{op}_{dtype.name}_{case}"
+        ls, rs, os_ = split_shapes(GOLDEN[key + "_shapes"])
+        dl = upload(device, host_from(GOLDEN[key + "_lhs"], ls, dtype))
+        dr = upload(device, host_from(GOLDEN[key + "_rhs"], rs, dtype))
+        do = upload(device, host_from(GOLDEN[key + "_out_before"], os_, dtype))
+        fn = queue.add if op == "add" else queue.mul
+        run(queue, fn(dl.view(), dr.view(), do.view()))
+        assert np.array_equal(download(do), GOLDEN[key + "_out"]), key
+
+
+@pytest.mark.parametrize("build,order", [("portable", RMS_SEQUENTIAL), ("avx512", RMS_LANES16)])
+def test_rmsnorm_golden_gpu(gpu, build, order):
+    device, queue = gpu
+    for dtype in (DataType.BF16, DataType.F32):
+        if dtype == DataType.F32 and order == RMS_LANES16:
+            continue   # the reference has no lane-ordered F32 path
+        for case in range(6):
+            key = f"rmsnorm_{build}_{dtype.name}_{case}"
+            shape = tuple(int(v) for v in GOLDEN[key + "_shape"])
+            dx = upload(device, host_from(GOLDEN[key + "_x"], shape, dtype))
+            dw = upload(device, host_from(GOLDEN[key + "_w"], (1, shape[-1]), dtype))
+            do = upload(device, host_from(GOLDEN[key + "_out_before"], shape, dtype))
+            run(queue, queue.rmsnorm(dx.view(), dw.view(), do.view(), 1e-5, order=order))
+            assert np.array_equal(download(do), GOLDEN[key + "_out"]), key
+
+
+def test_movers_golden_gpu(gpu):
+    device, queue = gpu
+    src = host_from(GOLDEN["copy_src"], (3, 4, 17, 33), DataType.BF16)
+    dst = host_from(GOLDEN["copy_dst_before"], (4, 3, 17, 33), DataType.BF16)
+    ds, dd = upload(device, src), upload(device, dst)
+    run(queue, queue.copy(like(view_from(src, GOLDEN["copy_src_view"], 4), ds),
+                          like(view_from(dst, GOLDEN["copy_dst_view"], 4), dd)))
+    assert np.array_equal(download(dd), GOLDEN["copy_dst"])
+
+    dt = upload(device, host_from(GOLDEN["embedding_table"], (50, 37), DataType.BF16))
+    di = upload(device, host_from(GOLDEN["embedding_ids"], (2, 1, 19), DataType.U32))
+    do = upload(device, host_from(GOLDEN["embedding_out_before"], (2, 19, 37), DataType.BF16))
+    ws = device.create_workspace(32)
+    run(queue, queue.embedding(dt.view(), di.view(), do.view(), ws.view()))
+    assert np.array_equal(download(do), GOLDEN["embedding_out"])
+
+    for a in (0, 5, 29):
+        s = upload(device, host_from(GOLDEN[f"append_{a}_src"], (2, 3, 3, 40), DataType.BF16))
+        d = upload(device, host_from(GOLDEN[f"append_{a}_dst_before"], (2, 3, 32, 40), DataType.BF16))
+        run(queue, queue.cache_append(s.view(), d.view(), a))
+        assert np.array_equal(download(d), GOLDEN[f"append_{a}_dst"])
+
+    host = host_from(GOLDEN["transfer_before"], (3, 2, 17, 35), DataType.F32)
+    dev = upload(device, host)
+    view = like(view_from(host, GOLDEN["transfer_view"], 4), dev)
+    staging = device.create_workspace(GOLDEN["transfer_payload"].nbytes + 32)
+    view.copy_from_host(GOLDEN["transfer_payload"], staging.view())
+    assert np.array_equal(download(dev), GOLDEN["transfer_after"])
