@@ -155,7 +155,7 @@ def run_ours(args) -> dict:
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
-    arena = 5 * PLANES * ROWS * HIDDEN * ELEM + (64 << 20)
+    arena = max(5 * PLANES * ROWS * HIDDEN * ELEM + (64 << 20), 0 if args.no_ops else 5 << 30)
     device = make_b200_device(local_rank, DeviceMemoryConfig(arena // 32 * 32))
     queue = device.create_ops()
     shape = (PLANES, ROWS, HIDDEN)
@@ -225,6 +225,13 @@ def run_ours(args) -> dict:
         torch.cuda.synchronize()
         e2e_ms = (time.perf_counter() - t0) * 1e3
 
+    table = None
+    if world == 1 and not args.no_ops:
+        for t in (x, r, total, out, scale):
+            t.close()
+        staging.close()
+        table = ops_table(device, queue)
+
     times = torch.tensor([elapsed_ms, e2e_ms], dtype=torch.float64, device="cuda")
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
@@ -265,11 +272,181 @@ def run_ours(args) -> dict:
                          "algorithmic_bytes_per_launch": ALGORITHMIC_BYTES},
         }
         result["config"]["pct_of_8TBps"] = 100.0 * achieved / 8000.0
+        if table is not None:
+            result["ops"] = table
     queue.close()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
     return result
+
+
+# ---- per-operation table (supporting numbers beside the headline) ------------------
+
+def ops_table(device, queue, only=None, iters: int = 10) -> dict:
+    """Device-resident GB/s (algorithmic bytes / CUDA-event time) of every operation
+    of the path on HBM-sized inputs, plus single-launch microseconds of the
+    decode-step data movement. Inputs are random bytes reinterpreted per leaf:
+    timing does not depend on the values."""
+    import ctypes
+
+    import torch
+
+    from iom_b200.tensor import DataType, TensorSpec
+
+    lib = device._lib
+    made = []
+
+    def tensor(shape, dtype, kind="normal"):
+        t = device.create_tensor(TensorSpec(shape, dtype))
+        n = t.storage_nbytes
+        if dtype == DataType.BF16 and kind == "normal":
+            t.storage().copy_(torch.randn(n // 2, device=device.torch_device)
+                              .to(torch.bfloat16).view(torch.uint8))
+        elif dtype == DataType.F32 and kind == "normal":
+            t.storage().copy_(torch.randn(n // 4, device=device.torch_device).view(torch.uint8))
+        else:
+            t.storage().copy_(torch.randint(0, 64, (n,), device=device.torch_device,
+                                            dtype=torch.uint8))
+        made.append(t)
+        return t
+
+    def release():
+        while made:
+            made.pop().close()
+
+    def timed(launch, inner=1):
+        """Median CUDA-event time of one launch; `inner` launches share one event
+        pair for microsecond-scale operations (the figure then includes the host's
+        issue rate through this Python layer, as a caller would see it)."""
+        for _ in range(3):
+            token = launch()
+        queue.wait(token)
+        pairs = []
+        for _ in range(iters):
+            a = torch.cuda.Event(enable_timing=True)
+            b = torch.cuda.Event(enable_timing=True)
+            a.record(queue.stream)
+            for _ in range(inner):
+                token = launch()
+            b.record(queue.stream)
+            pairs.append((a, b))
+            queue.wait(token)
+        torch.cuda.synchronize()
+        times = sorted(a.elapsed_time(b) for a, b in pairs)
+        return times[len(times) // 2] / inner
+
+    def ok(token):
+        if token <= 0:
+            raise RuntimeError(f"operation rejected with oid {token}")
+        return token
+
+    results = {}
+
+    def record(name, nbytes, launch, shape, inner=1):
+        if only is not None and name != only:
+            return
+        ms = timed(launch, inner)
+        results[name] = {"GB/s": nbytes / ms / 1e6, "us": ms * 1e3, "bytes": nbytes,
+                         "pct_of_8TBps": nbytes / ms / 1e6 / 80.0, "shape": shape}
+
+    M, N = 131072, 2048          # 2^28 elements: far beyond L2
+    E = M * N
+    for dtype, name, b in ((DataType.BF16, "bf16", 2), (DataType.F32, "f32", 4),
+                           (DataType.I32, "i32", 4)):
+        wanted = [f"{op}_{name}_{form}" for op in ("add", "mul") for form in ("full", "row", "col")]
+        if only is not None and only not in wanted:
+            continue
+        x, y, o = tensor((M, N), dtype), tensor((M, N), dtype), tensor((M, N), dtype)
+        row, col = tensor((1, N), dtype), tensor((M, 1), dtype)
+        fn = queue.mul if dtype == DataType.F32 else queue.add
+        op = "mul" if dtype == DataType.F32 else "add"
+        record(f"{op}_{name}_full", 3 * E * b, lambda: ok(fn(x.view(), y.view(), o.view())),
+               f"[{M},{N}]")
+        record(f"{op}_{name}_row", (2 * E + N) * b, lambda: ok(fn(x.view(), row.view(), o.view())),
+               f"[{M},{N}] op [1,{N}]")
+        record(f"{op}_{name}_col", (2 * E + M) * b, lambda: ok(fn(x.view(), col.view(), o.view())),
+               f"[{M},{N}] op [{M},1]")
+        release()
+    # RMSNorm family, BF16
+    for label, shape, eps in (("tinyllama", (16, 8192, 2048), 1e-5), ("c5shard", (32768, 8192), 1e-6)):
+        names = [f"rmsnorm_{label}", f"add_rmsnorm_{label}", f"rmsnorm_sequential_{label}"]
+        if only is not None and only not in names:
+            continue
+        cols = shape[-1]
+        count = 1
+        for extent in shape:
+            count *= extent
+        x, r, s_, o = (tensor(shape, DataType.BF16) for _ in range(4))
+        w = tensor((1, cols), DataType.BF16)
+        record(names[0], (2 * count + cols) * 2,
+               lambda: ok(queue.rmsnorm(x.view(), w.view(), o.view(), eps)), str(list(shape)))
+        record(names[1], (4 * count + cols) * 2,
+               lambda: ok(queue.add_rmsnorm(x.view(), r.view(), w.view(), s_.view(), o.view(), eps)),
+               str(list(shape)))
+        record(names[2], (2 * count + cols) * 2,
+               lambda: ok(queue.rmsnorm(x.view(), w.view(), o.view(), eps, order=1)),
+               str(list(shape)))
+        release()
+    if only is None or only in ("copy_bf16", "cast_bf16_f32", "cast_f32_bf16", "sumsq_bf16"):
+        x, o = tensor((M, N), DataType.BF16), tensor((M, N), DataType.BF16)
+        f = tensor((M, N), DataType.F32)
+        record("copy_bf16", 2 * E * 2, lambda: ok(queue.copy(x.view(), o.view())), f"[{M},{N}]")
+        record("cast_bf16_f32", 6 * E, lambda: ok(queue.cast(x.view(), f.view())), f"[{M},{N}]")
+        record("cast_f32_bf16", 6 * E, lambda: ok(queue.cast(f.view(), o.view())), f"[{M},{N}]")
+        scratch = device.create_workspace(int(lib.iomb_sumsq_scratch_bytes()))
+        cell = device.create_workspace(32)
+
+        def sumsq():
+            return ok(queue.sumsq(x.view(), scratch.view(), cell.view().address()))
+        record("sumsq_bf16", E * 2, sumsq, f"[{M},{N}]")
+        scratch.close()
+        cell.close()
+        release()
+    if only is None or only in ("embedding_decode", "cache_append_decode_batched",
+                                "cache_append_decode_64calls", "cast_logits"):
+        # Decode-step data movement, TinyLlama geometry (BASELINE config 4): microseconds.
+        table = tensor((32000, 2048), DataType.BF16)
+        ids = device.create_tensor(TensorSpec((1, 64), DataType.U32))
+        made.append(ids)
+        ids.storage().view(torch.int32)[:64].copy_(
+            torch.randint(0, 32000, (64,), device=device.torch_device, dtype=torch.int32))
+        # ids of tile columns 1..3 start at slot 256, 512, 768 of the [1,64] plane
+        raw = ids.storage().view(torch.int32)
+        host_ids = torch.randint(0, 32000, (64,), dtype=torch.int32)
+        for tile in range(4):
+            raw[tile * 256:tile * 256 + 16].copy_(host_ids[tile * 16:(tile + 1) * 16])
+        out = tensor((64, 2048), DataType.BF16)
+        ws = device.create_workspace(32)
+        record("embedding_decode", 2 * 64 * 2048 * 2 + 64 * 4 + 4,
+               lambda: ok(queue.embedding(table.view(), ids.view(), out.view(), ws.view())),
+               "table [32000,2048], 64 ids", inner=12)
+        k = tensor((64, 4, 1, 64), DataType.BF16)
+        cache = tensor((64, 4, 2048, 64), DataType.BF16)
+        positions = torch.randint(0, 2047, (64,), device=device.torch_device, dtype=torch.int32)
+        status = torch.zeros(8, device=device.torch_device, dtype=torch.int32)
+
+        def batched():
+            return ok(queue.cache_append_batched(k.view(), cache.view(), positions.data_ptr(),
+                                                 status.data_ptr()))
+        record("cache_append_decode_batched", 2 * 64 * 4 * 64 * 2, batched,
+               "K [64,4,1,64] -> cache [64,4,2048,64], one call", inner=12)
+        host_positions = positions.cpu().tolist()
+
+        def per_sequence():
+            for b in range(64):
+                token = ok(queue.cache_append(k.view().select(0, b), cache.view().select(0, b),
+                                              host_positions[b]))
+            return token
+        record("cache_append_decode_64calls", 2 * 64 * 4 * 64 * 2, per_sequence,
+               "the contract form: 64 calls on select(0,b) views")
+        logits = tensor((64, 32000), DataType.BF16)
+        wide = tensor((64, 32000), DataType.F32)
+        record("cast_logits", 64 * 32000 * 6, lambda: ok(queue.cast(logits.view(), wide.view())),
+               "[64,32000] BF16 -> F32", inner=12)
+        ws.close()
+        release()
+    return results
 
 
 # ---- CPU side: the reference's own CPU backend (or the oracle port) ---------------
@@ -400,6 +577,11 @@ def main() -> None:
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--no-ops", action="store_true",
+                        help="skip the per-operation table (N=1 only)")
+    parser.add_argument("--op", default=None,
+                        help="run one row of the per-operation table and print it "
+                             "(for profiler captures), e.g. --op rmsnorm_c5shard")
     parser.add_argument("--no-e2e", action="store_true",
                         help="skip the host-buffer leg (used for profiler captures)")
     parser.add_argument("--planes", type=int, default=PLANES,
@@ -408,6 +590,17 @@ def main() -> None:
     args = parser.parse_args()
     configure(args.planes)
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.op is not None:
+        import torch
+
+        from iom_b200.device import DeviceMemoryConfig, make_b200_device
+        torch.cuda.set_device(0)
+        device = make_b200_device(0, DeviceMemoryConfig(5 << 30))
+        queue = device.create_ops()
+        print(json.dumps({"op": args.op, "result": ops_table(device, queue, only=args.op,
+                                                             iters=max(1, args.steps))}))
+        queue.close()
+        return
     if args.impl == "reference":
         result = run_reference(args)
     else:

@@ -356,6 +356,10 @@ class B200Queue:
         self._failures = {}       # sequence -> exception
         self._completed = 0
         self._closed = False
+        # Queue-owned pinned cells for status read-backs, one per in-flight credit
+        # (the reference keeps one pinned cell per queue, src/cuda/device.cpp:165-200).
+        self._status_cells = torch.zeros(device.queue_config.max_in_flight_per_queue,
+                                         dtype=torch.int32).pin_memory()
 
     # -- plumbing -----------------------------------------------------------
     def device(self) -> B200Device:
@@ -410,7 +414,8 @@ class B200Queue:
                 event.record(self._stream)
                 pinned = None
                 if status_cell is not None:
-                    pinned = torch.empty(1, dtype=torch.int32, pin_memory=True)
+                    slot = (self._sequence + 1) % self._status_cells.numel()
+                    pinned = self._status_cells[slot:slot + 1]
                     with torch.cuda.stream(self._stream):
                         pinned.copy_(status_cell, non_blocking=True)
                     event = torch.cuda.Event()
@@ -548,6 +553,36 @@ class B200Queue:
         return self._submit(
             lambda stream: self._lib.iomb_cache_append(ctypes.byref(s), ctypes.byref(d), a, stream),
             (source.owner, destination.owner))
+
+    def cache_append_batched(self, source: TensorView, destination: TensorView,
+                             positions: int, status: int) -> int:
+        """Extension: one row offset per index of the first leading axis.
+        `positions` / `status` are device addresses (uint32[dims[0]] / uint32)."""
+        try:
+            self._check_view(source, "source")
+            self._check_view(destination, "destination")
+            s, d = source.as_abi(), destination.as_abi()
+        except BaseException as error:
+            return _exception_to_oid(error)
+        return self._submit(
+            lambda stream: self._lib.iomb_cache_append_batched(
+                ctypes.byref(s), ctypes.byref(d), positions, status, stream),
+            (source.owner, destination.owner))
+
+    def sumsq(self, x: TensorView, scratch: RawWorkspaceView, result: int) -> int:
+        """Extension: whole-view FP32 sum of squares into the device float at `result`."""
+        try:
+            self._check_view(x, "x")
+            need = int(self._lib.iomb_sumsq_scratch_bytes())
+            if scratch is None or scratch.empty() or scratch.byte_size() < need:
+                raise ValueError("sumsq requires a scratch workspace of iomb_sumsq_scratch_bytes()")
+            view = x.as_abi()
+        except BaseException as error:
+            return _exception_to_oid(error)
+        return self._submit(
+            lambda stream: self._lib.iomb_sumsq(ctypes.byref(view), scratch.address(), result,
+                                                stream),
+            (x.owner, scratch.owner))
 
     # The remaining operations of the contract are not part of this backend.
     def silu(self, *args, **kwargs) -> int:
