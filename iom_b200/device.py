@@ -11,6 +11,7 @@ ABI of libiom_b200.so; torch supplies device memory, streams and events only.
 """
 from __future__ import annotations
 
+import collections
 import ctypes
 import threading
 from dataclasses import dataclass
@@ -103,16 +104,42 @@ def _exception_to_oid(error: BaseException) -> int:
 
 class _Arena:
     """First-fit free list with coalescing over one device allocation
-    (the role of ListAllocator, include/iom/alloc.hpp:52-80)."""
+    (the role of ListAllocator, include/iom/alloc.hpp:52-80).
+
+    `release` may be called from a finalizer, which the garbage collector can
+    run in the middle of `alloc` on the same thread. It therefore never takes
+    the lock: it only queues the range (deque.append is atomic) and the next
+    `alloc` folds the queue into the free list.
+    """
 
     def __init__(self, capacity: int):
         self.capacity = capacity
         self.free = [(0, capacity)]
         self.lock = threading.Lock()
+        self.pending = collections.deque()
+
+    def _drain(self) -> None:
+        changed = False
+        while True:
+            try:
+                self.free.append(self.pending.popleft())
+                changed = True
+            except IndexError:
+                break
+        if changed:
+            self.free.sort()
+            merged = []
+            for start, length in self.free:
+                if merged and merged[-1][0] + merged[-1][1] == start:
+                    merged[-1] = (merged[-1][0], merged[-1][1] + length)
+                else:
+                    merged.append((start, length))
+            self.free = merged
 
     def alloc(self, size: int) -> int:
         size = (size + _ALIGNMENT - 1) // _ALIGNMENT * _ALIGNMENT
         with self.lock:
+            self._drain()
             for i, (offset, length) in enumerate(self.free):
                 if length >= size:
                     if length == size:
@@ -124,16 +151,7 @@ class _Arena:
 
     def release(self, offset: int, size: int) -> None:
         size = (size + _ALIGNMENT - 1) // _ALIGNMENT * _ALIGNMENT
-        with self.lock:
-            self.free.append((offset, size))
-            self.free.sort()
-            merged = []
-            for start, length in self.free:
-                if merged and merged[-1][0] + merged[-1][1] == start:
-                    merged[-1] = (merged[-1][0], merged[-1][1] + length)
-                else:
-                    merged.append((start, length))
-            self.free = merged
+        self.pending.append((offset, size))
 
 
 class RawWorkspaceView:
@@ -306,7 +324,7 @@ class B200Device:
         self._live_queues = 0
         self._next_queue_id = 1
         self._transfer_lock = threading.Lock()
-        self._lock = threading.Lock()
+        self._lock = threading.RLock()   # finalizers may re-enter on the same thread
 
     def backend_kind(self) -> str:
         return "CUDA"
