@@ -205,6 +205,27 @@ uint64_t iomb_sumsq_scratch_bytes(void);
 int iomb_sumsq(const iomb_view* x, void* scratch, float* result, void* stream);
 
 /*
+ * iomb_sumsq for callers that cannot provide scratch memory. It has no
+ * counterpart in the reference. Who needs it: a backend hook whose operation
+ * is admitted with a {0,1} workspace requirement (the caller hands over
+ * nothing) while IOM's contract forbids any native allocation after device
+ * set-up, or any host that calls in while its memory pools are frozen. The
+ * partial sums go to a 16 KiB array built into the library (every GPU that
+ * loads the library keeps it until the process exits); the call itself
+ * allocates and frees nothing.
+ *   - Limit: views of at most IOMB_SUMSQ_STATIC_MAX_ELEMENTS (2^32) elements;
+ *     larger views are rejected with IOMB_ERR_INVALID_ARGUMENT.
+ *   - The first call on each device looks up the array's device address. Make
+ *     that first call during start-up, before any stream capture begins.
+ *   - All calls share the one array and it keeps whatever the previous call
+ *     left; each call resets what it relies on. Two calls that overlap on the
+ *     GPU (different streams, no ordering) race on it: serialise them.
+ * Result and leaves are those of iomb_sumsq.
+ */
+#define IOMB_SUMSQ_STATIC_MAX_ELEMENTS (1ull << 32)
+int iomb_sumsq_static(const iomb_view* x, float* result, void* stream);
+
+/*
  * Host-layout <-> tiled conversion on the device.
  * Replaces scatter_plane_kernel / gather_plane_kernel and their per-plane launch
  * loops (src/shared/standard_tiled_copy.inl:286-441). `staging` is a device

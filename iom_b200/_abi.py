@@ -51,6 +51,7 @@ PROTOTYPES = {
                                                  ctypes.c_void_p]),
     "iomb_sumsq_scratch_bytes": (ctypes.c_uint64, []),
     "iomb_sumsq": (ctypes.c_int, [_VIEW, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
+    "iomb_sumsq_static": (ctypes.c_int, [_VIEW, ctypes.c_void_p, ctypes.c_void_p]),
     "iomb_scatter": (ctypes.c_int, [_VIEW, ctypes.c_void_p, ctypes.c_void_p]),
     "iomb_gather": (ctypes.c_int, [_VIEW, ctypes.c_void_p, ctypes.c_void_p]),
 }

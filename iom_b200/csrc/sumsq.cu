@@ -195,3 +195,72 @@ extern "C" int iomb_sumsq(const iomb_view* x, void* scratch, float* result, void
     }
     return check_launch("sumsq launch");
 }
+
+// ---- sum of squares without caller scratch -----------------------------------
+//
+// Some hosts of this library have no scratch to hand over and are not allowed
+// to create any: IOM's backend contract gives operations such as rmsnorm a
+// workspace requirement of {0, 1} (the caller passes none) and forbids every
+// native allocation once the device is set up, and a hook that runs while a
+// serving loop has frozen its memory pools is in the same position. For them the
+// partial sums live in a fixed array that is part of the library image. Every
+// GPU that loads the library carries the array until the process exits.
+namespace iomb {
+
+constexpr uint64_t kStaticScratchBytes = 16 * 1024;                 // capacity of the array
+constexpr uint64_t kStaticMaxElements = IOMB_SUMSQ_STATIC_MAX_ELEMENTS;   // largest view served
+
+static __device__ __align__(256) unsigned char g_sumsq_static_scratch[kStaticScratchBytes];
+
+// Device address of the array, looked up once per device ordinal. The array's
+// name is only a host-side handle; kernels must be given the looked-up address.
+static void* g_static_scratch_address[64];
+static int static_scratch(void** address) {
+    int device = -1;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) {
+        cudaGetLastError();
+        return fail(IOMB_ERR_DEVICE, "sumsq_static: no current CUDA device");
+    }
+    void* known = __atomic_load_n(&g_static_scratch_address[device], __ATOMIC_ACQUIRE);
+    if (known == nullptr) {
+        void* looked_up = nullptr;
+        const cudaError_t status = cudaGetSymbolAddress(&looked_up, g_sumsq_static_scratch);
+        if (status != cudaSuccess || looked_up == nullptr) {
+            cudaGetLastError();
+            return fail(IOMB_ERR_DEVICE, "sumsq_static: the scratch array's device address is unavailable");
+        }
+        __atomic_store_n(&g_static_scratch_address[device], looked_up, __ATOMIC_RELEASE);
+        known = looked_up;
+    }
+    *address = known;
+    return IOMB_OK;
+}
+
+}  // namespace iomb
+
+extern "C" int iomb_sumsq_static(const iomb_view* x, float* result, void* stream) {
+    using namespace iomb;
+    static_assert(kScratchBytes <= kStaticScratchBytes, "the static array must hold the partials");
+    ViewFacts f{};
+    const int rc = check_view(x, "sumsq_static x", &f);
+    if (rc != IOMB_OK) return rc;
+    // planes * rows * cols cannot overflow here: check_view bounded the storage.
+    const long double elements =
+            static_cast<long double>(f.planes) * static_cast<long double>(f.rows)
+            * static_cast<long double>(f.cols);
+    if (elements > static_cast<long double>(kStaticMaxElements)) {
+        return fail(IOMB_ERR_INVALID_ARGUMENT,
+                    "sumsq_static: the view has more than 2^32 elements; use iomb_sumsq with "
+                    "caller scratch");
+    }
+    if (iomb_sumsq_scratch_bytes() > kStaticScratchBytes) {
+        return fail(IOMB_ERR_INTERNAL, "sumsq_static: partials exceed the static array");
+    }
+    void* scratch = nullptr;
+    const int lookup = static_scratch(&scratch);
+    if (lookup != IOMB_OK) return lookup;
+    // The shared launch path resets the completion counter in stream order and
+    // every partial is overwritten before it is read, so what an earlier call
+    // left in the array never reaches the result.
+    return iomb_sumsq(x, scratch, result, stream);
+}
