@@ -152,6 +152,11 @@ def run_ours(args) -> dict:
     if not torch.cuda.is_available():
         raise RuntimeError("bench.py needs a CUDA device: the B200 backend has no CPU fallback")
     torch.cuda.set_device(local_rank)
+    # Libraries (NCCL's version banner) write to stdout; the one JSON line must be
+    # the only thing there, so fd 1 points at stderr until the result is printed.
+    saved_stdout = os.dup(1)
+    os.dup2(2, 1)
+    args._restore_stdout = lambda: (os.dup2(saved_stdout, 1), os.close(saved_stdout))
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
@@ -225,6 +230,35 @@ def run_ours(args) -> dict:
         torch.cuda.synchronize()
         e2e_ms = (time.perf_counter() - t0) * 1e3
 
+    # ---- whole-tensor sum of squares across ranks (the one exchange step) ----
+    sumsq_info = None
+    if world > 1:
+        from iom_b200.sharding import all_gather_sum
+        scratch = device.create_workspace(int(device._lib.iomb_sumsq_scratch_bytes()))
+        local = torch.zeros(1, dtype=torch.float32, device=device.torch_device)
+
+        def sumsq_step():
+            token = queue.sumsq(total.view(), scratch.view(), local.data_ptr())
+            if token <= 0:
+                raise RuntimeError(f"sumsq rejected with oid {token}")
+            queue.wait(token)
+            return all_gather_sum(local)
+
+        combined = sumsq_step()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(5):
+            combined = sumsq_step()
+        torch.cuda.synchronize()
+        sumsq_ms = (time.perf_counter() - t0) * 1e3 / 5
+        gathered = [torch.empty_like(combined.reshape(1)) for _ in range(world)]
+        dist.all_gather(gathered, combined.reshape(1))
+        sumsq_info = {"value": float(combined), "ms": sumsq_ms,
+                      "identical_on_all_ranks": all(torch.equal(gathered[0], g) for g in gathered),
+                      "bytes_read_per_rank": ELEMENTS * ELEM,
+                      "combine": "all_gather of one FP32 partial per rank, added in rank order"}
+        scratch.close()
+
     table = None
     if world == 1 and not args.no_ops:
         for t in (x, r, total, out, scale):
@@ -274,6 +308,8 @@ def run_ours(args) -> dict:
         result["config"]["pct_of_8TBps"] = 100.0 * achieved / 8000.0
         if table is not None:
             result["ops"] = table
+        if sumsq_info is not None:
+            result["sumsq_across_ranks"] = sumsq_info
     queue.close()
     if world > 1:
         dist.barrier()
@@ -608,6 +644,10 @@ def main() -> None:
         if result is not None and result["n_gpus"] == 1 and not args.no_cpu_baseline:
             cpu = _cpu_arm(1, repeats=3, warmup=1)
             result["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
+    restore = getattr(args, "_restore_stdout", None)
+    if restore is not None:
+        sys.stdout.flush()
+        restore()
     if result is not None:
         print(json.dumps(result), flush=True)
 

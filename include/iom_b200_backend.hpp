@@ -1,0 +1,35 @@
+// C++ host side of the B200 backend: an iom::Device whose tensors live in the
+// standard tiled layout inside one device arena and whose operation queue
+// launches the kernels of libiom_b200.so (include/iom_b200.h).
+//
+// It plugs into the reference's own headers (include/iom/device.hpp,
+// include/iom/iom.hpp): build it with the reference checkout on the include
+// path. The factory mirrors make_cuda_device (include/iom/cuda/device.hpp:22-24).
+#pragma once
+
+#include <cstdint>
+#include <memory>
+
+#include "iom/device.hpp"
+#include "iom/iom.hpp"
+
+namespace iom {
+
+// Rejects a zero or non-multiple-of-32 arena with std::invalid_argument, an
+// unknown ordinal with std::invalid_argument, a failed reservation with
+// std::bad_alloc. Reports BackendKind::CUDA (the enum has no spare value).
+[[nodiscard]] std::unique_ptr<Device> make_b200_device(
+        std::uint32_t ordinal, DeviceMemoryConfig memory_config,
+        QueueConfig queue_config = {});
+
+namespace b200 {
+
+// Extension outside the DeviceOps facade: residual ADD fused into the
+// following RMSNorm (sum = x + residual is stored; out = rmsnorm(sum, scale)).
+// `queue` must have been created by a device from make_b200_device. Returns
+// an oid like the facade operations do.
+oid add_rmsnorm(DeviceOps& queue, const TensorView& x, const TensorView& residual,
+                const TensorView& scale, TensorView& sum, TensorView& out, float eps);
+
+}  // namespace b200
+}  // namespace iom

@@ -32,6 +32,15 @@
 #include "iom/iom.hpp"
 #include "iom/tensor.hpp"
 
+// With IOMREF_WITH_B200 the same shim can also create the B200 backend
+// (iom_b200/backend/b200_backend.cpp) behind the reference's own DeviceOps
+// facade, so one test can drive candidate and reference through identical calls.
+#ifdef IOMREF_WITH_B200
+#include <cuda_runtime_api.h>
+
+#include "iom_b200_backend.hpp"
+#endif
+
 namespace iom::cpu_detail {
 // src/cpu/avx512_bf16.hpp: true when this build and this CPU may enter the
 // isolated AVX-512 BF16 workers.
@@ -56,18 +65,32 @@ public:
 struct DeviceBox {
     AlignedHostAllocator allocator;
     std::unique_ptr<iom::Device> device;
+    bool accelerator = false;
+    // Workspaces handed to operations stay alive until the device goes away.
+    std::vector<std::unique_ptr<iom::RawWorkspace>> workspaces;
+
+    ~DeviceBox() { workspaces.clear(); }
+
+    iom::RawWorkspaceView workspace(const iom::WorkspaceRequirements& need) {
+        if (need.bytes == 0) return {};
+        workspaces.push_back(device->create_workspace(need.bytes));
+        return workspaces.back()->view();
+    }
 };
 
 struct TensorBox {
     std::unique_ptr<iom::Tensor> tensor;
+    DeviceBox* device = nullptr;
 };
 
 struct ViewBox {
     iom::TensorView view;
+    DeviceBox* device = nullptr;
 };
 
 struct QueueBox {
     std::unique_ptr<iom::DeviceOps> ops;
+    DeviceBox* device = nullptr;
 };
 
 // Exception class → small positive code (0 is success).
@@ -154,8 +177,8 @@ void* iomref_tensor_create(
                 iom::TensorShape{std::move(shape)},
                 static_cast<iom::DataType>(data_type)};
         auto box = std::make_unique<TensorBox>();
-        box->tensor =
-                static_cast<DeviceBox*>(device)->device->create_tensor(spec);
+        box->device = static_cast<DeviceBox*>(device);
+        box->tensor = box->device->device->create_tensor(spec);
         return box.release();
     });
 }
@@ -177,7 +200,8 @@ std::uint64_t iomref_tensor_storage_nbytes(void* tensor) {
 
 void* iomref_view_full(void* tensor) {
     return guarded_pointer([&]() -> void* {
-        return new ViewBox{static_cast<TensorBox*>(tensor)->tensor->view()};
+        auto* owner = static_cast<TensorBox*>(tensor);
+        return new ViewBox{owner->tensor->view(), owner->device};
     });
 }
 
@@ -185,13 +209,13 @@ void* iomref_view_slice(
         void* view, std::uint64_t dim, std::uint64_t first,
         std::uint64_t count, std::uint64_t step) {
     return guarded_pointer([&]() -> void* {
-        return new ViewBox{view_of(view).slice(dim, first, count, step)};
+        return new ViewBox{view_of(view).slice(dim, first, count, step), static_cast<ViewBox*>(view)->device};
     });
 }
 
 void* iomref_view_select(void* view, std::uint64_t dim, std::uint64_t index) {
     return guarded_pointer([&]() -> void* {
-        return new ViewBox{view_of(view).select(dim, index)};
+        return new ViewBox{view_of(view).select(dim, index), static_cast<ViewBox*>(view)->device};
     });
 }
 
@@ -199,7 +223,7 @@ void* iomref_view_permute(
         void* view, const std::uint64_t* order, std::uint32_t count) {
     return guarded_pointer([&]() -> void* {
         std::vector<std::size_t> leading(order, order + count);
-        return new ViewBox{view_of(view).permute(leading)};
+        return new ViewBox{view_of(view).permute(leading), static_cast<ViewBox*>(view)->device};
     });
 }
 
@@ -207,7 +231,7 @@ void* iomref_view_reshape_leading(
         void* view, const std::uint64_t* dims, std::uint32_t count) {
     return guarded_pointer([&]() -> void* {
         std::vector<std::size_t> leading(dims, dims + count);
-        return new ViewBox{view_of(view).reshape_leading(leading)};
+        return new ViewBox{view_of(view).reshape_leading(leading), static_cast<ViewBox*>(view)->device};
     });
 }
 
@@ -244,22 +268,29 @@ std::uint64_t iomref_view_logical_nbytes(void* view) {
 
 int iomref_view_from_host(void* view, const void* bytes, std::uint64_t count) {
     return guarded_status([&] {
-        view_of(view).copy_from_host(std::span<const std::byte>(
-                static_cast<const std::byte*>(bytes), count));
+        iom::TensorView& target = view_of(view);
+        target.copy_from_host(
+                std::span<const std::byte>(static_cast<const std::byte*>(bytes), count),
+                static_cast<ViewBox*>(view)->device->workspace(
+                        target.copy_from_host_workspace_requirements()));
     });
 }
 
 int iomref_view_to_host(void* view, void* bytes, std::uint64_t count) {
     return guarded_status([&] {
-        view_of(view).copy_to_host(
-                std::span<std::byte>(static_cast<std::byte*>(bytes), count));
+        iom::TensorView& source = view_of(view);
+        source.copy_to_host(
+                std::span<std::byte>(static_cast<std::byte*>(bytes), count),
+                static_cast<ViewBox*>(view)->device->workspace(
+                        source.copy_to_host_workspace_requirements()));
     });
 }
 
 void* iomref_queue_create(void* device) {
     return guarded_pointer([&]() -> void* {
         auto box = std::make_unique<QueueBox>();
-        box->ops = static_cast<DeviceBox*>(device)->device->create_ops();
+        box->device = static_cast<DeviceBox*>(device);
+        box->ops = box->device->device->create_ops();
         return box.release();
     });
 }
@@ -292,8 +323,16 @@ std::int64_t iomref_copy(void* queue, void* source, void* destination) {
 
 std::int64_t iomref_embedding(
         void* queue, void* table, void* indices, void* out) {
-    return ops_of(queue).embedding(
-            view_of(table), view_of(indices), view_of(out));
+    auto* box = static_cast<QueueBox*>(queue);
+    try {
+        const iom::WorkspaceRequirements need = box->ops->embedding_workspace_requirements(
+                view_of(table), view_of(indices), view_of(out));
+        return box->ops->embedding(view_of(table), view_of(indices), view_of(out),
+                                   box->device->workspace(need));
+    } catch (...) {
+        // The query throws what the facade would map; let the facade report it.
+        return box->ops->embedding(view_of(table), view_of(indices), view_of(out));
+    }
 }
 
 std::int64_t iomref_cache_append(
@@ -307,5 +346,46 @@ std::int64_t iomref_cache_append(
 int iomref_wait(void* queue, std::int64_t token) {
     return guarded_status([&] { ops_of(queue).wait(token); });
 }
+
+#ifdef IOMREF_WITH_B200
+void* iomref_device_create_b200(std::uint32_t ordinal, std::uint64_t arena_bytes) {
+    return guarded_pointer([&]() -> void* {
+        auto box = std::make_unique<DeviceBox>();
+        box->accelerator = true;
+        box->device = iom::make_b200_device(ordinal, iom::DeviceMemoryConfig{arena_bytes});
+        return box.release();
+    });
+}
+
+// Whole-owner physical storage transfers through an independent native path
+// (plain cudaMemcpy on the default stream), as the reference's CUDA storage
+// oracle does (test/cuda/test_cuda_conformance.cpp:180-208).
+int iomref_tensor_upload(void* tensor, const void* bytes, std::uint64_t count) {
+    auto* box = static_cast<TensorBox*>(tensor);
+    if (cudaMemcpy(box->tensor->view().native_handle(), bytes, count, cudaMemcpyHostToDevice)
+            != cudaSuccess) {
+        g_last_error = "cudaMemcpy H2D failed";
+        return 5;
+    }
+    return 0;
+}
+
+int iomref_tensor_download(void* tensor, void* bytes, std::uint64_t count) {
+    auto* box = static_cast<TensorBox*>(tensor);
+    if (cudaDeviceSynchronize() != cudaSuccess
+            || cudaMemcpy(bytes, box->tensor->view().native_handle(), count,
+                          cudaMemcpyDeviceToHost) != cudaSuccess) {
+        g_last_error = "cudaMemcpy D2H failed";
+        return 5;
+    }
+    return 0;
+}
+
+std::int64_t iomref_add_rmsnorm(void* queue, void* x, void* residual, void* scale, void* sum,
+                                void* out, float epsilon) {
+    return iom::b200::add_rmsnorm(ops_of(queue), view_of(x), view_of(residual), view_of(scale),
+                                  view_of(sum), view_of(out), epsilon);
+}
+#endif
 
 }  // extern "C"

@@ -21,6 +21,8 @@ ORACLE_LIB = ORACLE_DIR / "libiom_oracle.so"
 REF_LIBS = {
     "portable": ORACLE_DIR / "_ref" / "libiomref_portable.so",
     "avx512": ORACLE_DIR / "_ref" / "libiomref_avx512.so",
+    # reference CPU backend + the C++ B200 backend behind the same facade
+    "b200": ORACLE_DIR / "_ref" / "libiomref_b200.so",
 }
 
 _VIEW = ctypes.POINTER(IombView)
@@ -157,7 +159,7 @@ def abi(view: TensorView):
 class Reference:
     """ctypes access to oracle/_ref/libiomref_<kind>.so (see oracle/ref_driver.cpp)."""
 
-    def __init__(self, kind: str):
+    def __init__(self, kind: str, accelerator: bool = False, arena_bytes: int = 1 << 30):
         path = REF_LIBS[kind]
         if not path.exists():
             raise FileNotFoundError(path)
@@ -193,13 +195,22 @@ class Reference:
             "iomref_cache_append": (ctypes.c_int64, [vp, vp, vp, u64]),
             "iomref_wait": (ctypes.c_int, [vp, ctypes.c_int64]),
         }
+        if kind == "b200":
+            spec.update({
+                "iomref_device_create_b200": (vp, [u32, u64]),
+                "iomref_tensor_upload": (ctypes.c_int, [vp, vp, u64]),
+                "iomref_tensor_download": (ctypes.c_int, [vp, vp, u64]),
+                "iomref_add_rmsnorm": (ctypes.c_int64, [vp, vp, vp, vp, vp, vp, ctypes.c_float]),
+            })
         for name, (restype, argtypes) in spec.items():
             fn = getattr(lib, name)
             fn.restype = restype
             fn.argtypes = argtypes
         self.lib = lib
         self.kind = kind
-        self.device = lib.iomref_device_create()
+        self.accelerator = accelerator
+        self.device = (lib.iomref_device_create_b200(0, arena_bytes) if accelerator
+                       else lib.iomref_device_create())
         assert self.device, self.error()
         self.queue = lib.iomref_queue_create(self.device)
         assert self.queue, self.error()
@@ -288,9 +299,31 @@ class RefTensor:
         self.handle = ref.lib.iomref_tensor_create(ref.device, dims, len(shape), int(data_type))
         assert self.handle, ref.error()
         self.nbytes = ref.lib.iomref_tensor_storage_nbytes(self.handle)
-        address = ref.lib.iomref_tensor_storage(self.handle)
-        self.storage = np.ctypeslib.as_array(
-            ctypes.cast(address, ctypes.POINTER(ctypes.c_uint8)), shape=(self.nbytes,))
+        if ref.accelerator:
+            self.storage = None     # device memory: use write() / read()
+        else:
+            address = ref.lib.iomref_tensor_storage(self.handle)
+            self.storage = np.ctypeslib.as_array(
+                ctypes.cast(address, ctypes.POINTER(ctypes.c_uint8)), shape=(self.nbytes,))
+
+    def write(self, raw) -> None:
+        """Sets the owner's complete physical storage."""
+        data = np.ascontiguousarray(raw, dtype=np.uint8).reshape(-1)
+        assert data.size == self.nbytes
+        if self.ref.accelerator:
+            rc = self.ref.lib.iomref_tensor_upload(self.handle, data.ctypes.data, data.size)
+            assert rc == 0, self.ref.error()
+        else:
+            self.storage[:] = data
+
+    def read(self) -> np.ndarray:
+        """The owner's complete physical storage."""
+        if self.ref.accelerator:
+            out = np.empty(self.nbytes, dtype=np.uint8)
+            rc = self.ref.lib.iomref_tensor_download(self.handle, out.ctypes.data, out.size)
+            assert rc == 0, self.ref.error()
+            return out
+        return self.storage.copy()
 
     def view(self) -> RefView:
         return RefView(self.ref, self.ref.lib.iomref_view_full(self.handle))

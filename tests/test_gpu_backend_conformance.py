@@ -1,0 +1,216 @@
+"""The C++ B200 backend behind the reference's own DeviceOps facade, side by
+side with the reference CPU backend: identical calls, identical physical bytes.
+
+Both devices live in oracle/_ref/libiomref_b200.so (reference common + CPU
+sources compiled unmodified, iom_b200/backend/b200_backend.cpp, the shim). The
+candidate's storage is seeded and observed with plain cudaMemcpy, independent
+of the code under test, as the reference's CUDA storage oracle does.
+"""
+import numpy as np
+import pytest
+
+from iom_b200.tensor import DataType
+from support import NUMPY_OF, REF_LIBS, Reference, SPECIAL_BF16, SPECIAL_F32, random_payload
+
+pytestmark = pytest.mark.gpu
+POISON = 0xA5
+
+
+@pytest.fixture(scope="module")
+def pair():
+    if not REF_LIBS["b200"].exists():
+        pytest.skip("libiomref_b200.so is not built (make -C oracle b200)")
+    cpu = Reference("b200")
+    gpu = Reference("b200", accelerator=True, arena_bytes=1 << 30)
+    yield cpu, gpu
+    gpu.close()
+    cpu.close()
+
+
+def both(pair, shape, dtype, rng, payload=None, kind="uniform"):
+    """The same poisoned owner with the same logical payload on both devices."""
+    if payload is None:
+        payload = random_payload(rng, shape, dtype, kind)
+    owners = []
+    for ref in pair:
+        tensor = ref.tensor(shape, dtype)
+        tensor.write(np.full(tensor.nbytes, POISON, dtype=np.uint8))
+        tensor.view().from_host(payload)
+        owners.append(tensor)
+    # the candidate's host transfer must produce the reference's physical bytes
+    assert np.array_equal(owners[0].read(), owners[1].read()), "copy_from_host differs"
+    return owners
+
+
+def views(owners, steps=()):
+    result = []
+    for owner in owners:
+        view = owner.view()
+        for name, args in steps:
+            view = getattr(view, name)(*args)
+        result.append(view)
+    return result
+
+
+def same(owners):
+    assert np.array_equal(owners[0].read(), owners[1].read())
+
+
+@pytest.mark.parametrize("dtype", [DataType.I32, DataType.U32, DataType.F32, DataType.BF16])
+@pytest.mark.parametrize("op", [0, 1])
+@pytest.mark.parametrize("shapes", [
+    ((2, 17, 33), (2, 17, 33), (2, 17, 33)), ((2, 1, 33), (1, 17, 1), (2, 17, 33)),
+    ((64, 256), (1, 256), (64, 256)), ((32, 48), (32, 1), (32, 48)), ((1, 1), (3, 20, 35), (3, 20, 35)),
+])
+def test_binary(pair, dtype, op, shapes):
+    rng = np.random.default_rng(5)
+    lhs, rhs, out = (both(pair, s, dtype, rng) for s in shapes)
+    for i, ref in enumerate(pair):
+        token = ref.lib.iomref_binary(ref.queue, op, lhs[i].view().handle, rhs[i].view().handle,
+                                      out[i].view().handle)
+        assert ref.run(token) == 0, ref.error()
+    same(out)
+    same(lhs)
+
+
+def test_binary_views_alias_and_rejections(pair):
+    rng = np.random.default_rng(6)
+    lhs = both(pair, (4, 3, 17, 33), DataType.F32, rng)
+    rhs = both(pair, (3, 4, 17, 33), DataType.F32, rng)
+    out = both(pair, (2, 3, 17, 33), DataType.F32, rng)
+    lv = views(lhs, [("slice", (0, 1, 2, 2))])
+    rv = views(rhs, [("permute", ([1, 0],)), ("slice", (0, 0, 2, 1))])
+    ov = views(out)
+    other = views(lhs, [("slice", (0, 0, 2, 2))])   # same owner as lv, another window
+    for i, ref in enumerate(pair):
+        assert ref.run(ref.lib.iomref_binary(ref.queue, 0, lv[i].handle, rv[i].handle, ov[i].handle)) == 0
+        # exact in-place alias
+        assert ref.run(ref.lib.iomref_binary(ref.queue, 1, ov[i].handle, rv[i].handle, ov[i].handle)) == 0
+        # the facade's own rejections arrive unchanged through the new backend
+        assert ref.lib.iomref_binary(ref.queue, 0, ov[i].handle, other[i].handle, lv[i].handle) == -1
+    same(out)
+    # SUB/DIV are not served by this backend: explicit Unsupported, never a fallback
+    cpu, gpu = pair
+    assert gpu.lib.iomref_binary(gpu.queue, 2, ov[1].handle, rv[1].handle, ov[1].handle) == -2
+    f64 = gpu.tensor((16, 16), DataType.F64)
+    assert gpu.lib.iomref_binary(gpu.queue, 0, f64.view().handle, f64.view().handle,
+                                 f64.view().handle) == -2
+    # a view of the other device is rejected by device identity
+    foreign = cpu.tensor((2, 3, 17, 33), DataType.F32)
+    assert gpu.lib.iomref_binary(gpu.queue, 0, foreign.view().handle, rv[1].handle, ov[1].handle) == -1
+
+
+@pytest.mark.parametrize("dtype", [DataType.BF16, DataType.F32])
+@pytest.mark.parametrize("shape", [(15, 17), (17, 33), (2, 3, 16, 31), (64, 2048)])
+def test_rmsnorm_within_contract_tolerance(pair, dtype, shape):
+    """Through the facade the candidate runs the lane order (bit-identical to the
+    reference's AVX-512 BF16 build); against this portable CPU build the contract
+    allows one BF16 code / 2e-6 relative."""
+    rng = np.random.default_rng(8)
+    x = both(pair, shape, dtype, rng, kind="normal")
+    w = both(pair, (1, shape[-1]), dtype, rng, kind="normal")
+    out = both(pair, shape, dtype, rng)
+    for i, ref in enumerate(pair):
+        token = ref.lib.iomref_rmsnorm(ref.queue, x[i].view().handle, w[i].view().handle,
+                                       out[i].view().handle, 1e-5)
+        assert ref.run(token) == 0, ref.error()
+        assert ref.lib.iomref_rmsnorm(ref.queue, x[i].view().handle, w[i].view().handle,
+                                      x[i].view().handle, 1e-5) == -1   # output shares input
+    a, b = out[0].read(), out[1].read()
+    if dtype == DataType.BF16:
+        assert np.max(np.abs(a.view(np.uint16).astype(np.int32) - b.view(np.uint16).astype(np.int32))) <= 1
+    else:
+        fa, fb = a.view(np.float32).astype(np.float64), b.view(np.float32).astype(np.float64)
+        logical = np.abs(fa) < 1e30          # poisoned padding (0xA5A5A5A5) is identical anyway
+        assert np.array_equal(a.view(np.uint32)[~logical], b.view(np.uint32)[~logical])
+        assert np.all(np.abs(fa[logical] - fb[logical]) <= 2e-6 * np.abs(fa[logical]) + 1e-30)
+
+
+def test_copy_embedding_cache_append(pair):
+    rng = np.random.default_rng(9)
+    src = both(pair, (3, 4, 17, 33), DataType.BF16, rng)
+    dst = both(pair, (4, 3, 17, 33), DataType.BF16, rng)
+    sv = views(src, [("slice", (1, 0, 2, 2))])
+    dv = views(dst, [("permute", ([1, 0],)), ("slice", (1, 1, 2, 2))])
+    for i, ref in enumerate(pair):
+        assert ref.run(ref.lib.iomref_copy(ref.queue, sv[i].handle, dv[i].handle)) == 0
+    same(dst)
+
+    table = both(pair, (50, 37), DataType.BF16, rng)
+    ids = rng.integers(0, 50, size=(2, 1, 19)).astype(np.uint32)
+    idx = both(pair, (2, 1, 19), DataType.U32, rng, payload=ids)
+    out = both(pair, (2, 19, 37), DataType.BF16, rng)
+    for i, ref in enumerate(pair):
+        token = ref.lib.iomref_embedding(ref.queue, table[i].view().handle, idx[i].view().handle,
+                                         out[i].view().handle)
+        assert ref.run(token) == 0, ref.error()
+    same(out)
+    bad = ids.copy()
+    bad[1, 0, 3] = 50
+    for i, ref in enumerate(pair):
+        idx[i].view().from_host(bad)
+        token = ref.lib.iomref_embedding(ref.queue, table[i].view().handle, idx[i].view().handle,
+                                         out[i].view().handle)
+        assert token > 0
+        assert ref.run(token) == 1          # retained invalid_argument on wait
+        assert ref.run(token) == 1          # ... on every wait
+
+    for a in (0, 5, 29):
+        s = both(pair, (2, 3, 3, 40), DataType.BF16, rng)
+        d = both(pair, (2, 3, 32, 40), DataType.BF16, rng)
+        for i, ref in enumerate(pair):
+            assert ref.run(ref.lib.iomref_cache_append(ref.queue, s[i].view().handle,
+                                                       d[i].view().handle, a)) == 0
+            assert ref.lib.iomref_cache_append(ref.queue, s[i].view().handle, d[i].view().handle, 30) == -1
+        same(d)
+
+
+def test_host_transfers_and_fused_extension(pair):
+    cpu, gpu = pair
+    rng = np.random.default_rng(10)
+    for dtype in (DataType.BF16, DataType.F32, DataType.U8, DataType.I64):
+        owners = both(pair, (3, 2, 17, 35), dtype, rng)
+        tv = views(owners, [("permute", ([1, 0],)), ("slice", (1, 1, 2, 1))])
+        assert np.array_equal(tv[0].to_host(), tv[1].to_host())
+        payload = random_payload(rng, (2, 2, 17, 35), dtype)
+        for v in tv:
+            v.from_host(payload)
+        same(owners)
+    # fused residual ADD + RMSNorm equals add then rmsnorm on the candidate itself
+    shape = (40, 2048)
+    x = gpu.tensor(shape, DataType.BF16)
+    r = gpu.tensor(shape, DataType.BF16)
+    w = gpu.tensor((1, 2048), DataType.BF16)
+    s1, s2, n1, n2 = (gpu.tensor(shape, DataType.BF16) for _ in range(4))
+    x.view().from_host(random_payload(rng, shape, DataType.BF16, "normal"))
+    r.view().from_host(random_payload(rng, shape, DataType.BF16, "normal"))
+    w.view().from_host(random_payload(rng, (1, 2048), DataType.BF16, "normal"))
+    token = gpu.lib.iomref_add_rmsnorm(gpu.queue, x.view().handle, r.view().handle, w.view().handle,
+                                       s1.view().handle, n1.view().handle, 1e-5)
+    assert gpu.run(token) == 0, gpu.error()
+    assert gpu.run(gpu.lib.iomref_binary(gpu.queue, 0, x.view().handle, r.view().handle, s2.view().handle)) == 0
+    assert gpu.run(gpu.lib.iomref_rmsnorm(gpu.queue, s2.view().handle, w.view().handle, n2.view().handle, 1e-5)) == 0
+    assert np.array_equal(s1.read(), s2.read())
+    assert np.array_equal(n1.read(), n2.read())
+    # the CPU reference computes the same stored sum
+    cx = cpu.tensor(shape, DataType.BF16)
+    cr = cpu.tensor(shape, DataType.BF16)
+    cs = cpu.tensor(shape, DataType.BF16)
+    cx.view().from_host(x.view().to_host())
+    cr.view().from_host(r.view().to_host())
+    assert cpu.run(cpu.lib.iomref_binary(cpu.queue, 0, cx.view().handle, cr.view().handle, cs.view().handle)) == 0
+    assert np.array_equal(cs.read(), s1.read())
+
+
+def test_queue_limits_and_tokens(pair):
+    _, gpu = pair
+    queues = []
+    for _ in range(3):                       # one queue already exists: four is the cap
+        handle = gpu.lib.iomref_queue_create(gpu.device)
+        assert handle, gpu.error()
+        queues.append(handle)
+    assert not gpu.lib.iomref_queue_create(gpu.device)      # the fifth is bad_alloc
+    for handle in queues:
+        gpu.lib.iomref_queue_destroy(handle)
+    assert gpu.lib.iomref_wait(gpu.queue, 12345) == 1       # foreign / never submitted token
+    assert gpu.lib.iomref_wait(gpu.queue, -1) == 1
