@@ -39,9 +39,9 @@ METRIC = "achieved HBM GB/s, fused residual ADD + RMSNorm (BF16, TinyLlama prefi
 WORKLOAD = (f"C2 x{PLANES}: BF16 [{PLANES},{ROWS},{HIDDEN}] residual ADD + RMSNorm, eps 1e-5, "
             "x,r ~ N(0,1), w ~ N(1,0.02)")
 # dram__bytes_read.sum + dram__bytes_write.sum of one rmsnorm_kernel launch, from
-# the ncu capture summarised in profiles/ (a [2,8192,2048] case scaled by 8:
-# traffic is proportional to the rows processed). None until a capture exists.
-NCU_TRAFFIC_BYTES = None
+# the ncu capture summarised in profiles/ (taken on a [2,8192,2048] case; traffic
+# is proportional to the rows processed, so it is scaled by the plane count).
+NCU_TRAFFIC_BYTES_PER_PLANE = 211.63e6 / 2     # profiles/add_rmsnorm_bf16_tinyllama.md
 
 
 def configure(planes: int) -> None:
@@ -301,7 +301,7 @@ def run_ours(args) -> dict:
                     "path": "copy_from_host(x), copy_from_host(r), add_rmsnorm, copy_to_host(out)"},
             "gpu_launches": args.steps,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES,
+                         "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES_PER_PLANE * PLANES,
                          "peak_source": f"of {peak_kind}", "kernel": "rmsnorm_kernel<2,16,true>",
                          "algorithmic_bytes_per_launch": ALGORITHMIC_BYTES},
         }
