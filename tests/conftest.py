@@ -19,7 +19,7 @@ def pytest_sessionstart(session):
     period = os.environ.get("IOMB_TRACE_SLOW")
     if period:
         import faulthandler
-        path = os.environ.get("IOMB_TRACE_FILE", "gpurun_out/slow_trace.log")
+        path = os.environ.get("IOMB_TRACE_FILE", "slow_trace.log")
         session.config._iomb_trace_file = open(path, "w")
         faulthandler.dump_traceback_later(float(period), repeat=True,
                                           file=session.config._iomb_trace_file)
