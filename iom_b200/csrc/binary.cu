@@ -1,8 +1,11 @@
 // Elementwise ADD / MUL with right-aligned broadcasting on tiled storage.
 //
 // Replaces grid_stride_binary_kernel / alias_safe_binary_kernel of the
-// reference (src/shared/standard_tiled_add.inl:206-464). Two kernels:
+// reference (src/shared/standard_tiled_add.inl:206-464). Three kernels:
 //
+//   binary_stream_bc_kernel  one dense full-shape operand against a single [1,N]
+//                         or [M,1] plane (bias add, per-row scale): the big
+//                         operand is a linear stream, the small one comes from L1.
 //   binary_linear_kernel  every operand has the result's shape, tile-multiple
 //                         extents and dense planes: the three storages are
 //                         walked as one linear stream of 16-byte vectors.
@@ -85,6 +88,100 @@ binary_linear_kernel(const uint4* __restrict__ lhs, const uint4* __restrict__ rh
             }
         }
     }
+}
+
+// ---- linear stream against one broadcast row / column --------------------------
+//
+// `big` has the result's shape (dense planes, tile-multiple extents) and is
+// streamed exactly like binary_linear_kernel; `small` is a single [1,N] or [M,1]
+// plane that every leading index shares. For vector i of the stream the tile is
+// i / (vectors per tile); a [1,N] operand contributes row 0 of tile column
+// (tile % tile_cols), an [M,1] operand column 0 of band (tile / tile_cols) %
+// tile_rows. The small operand stays in L1/L2; HBM sees the big stream only.
+struct StreamBcParams {
+    const uint4* big;
+    const unsigned char* small;
+    uint4* out;
+    uint64_t vectors;
+    uint32_t tile_rows;
+    uint32_t tile_cols;
+    uint32_t cols_shift;    // log2(tile_cols) when it is a power of two, else 32
+    uint32_t single_plane;  // the stream is one plane: band index needs no modulo
+};
+
+template <Leaf L, int OP, bool COLUMN, bool SMALL_IS_LHS>
+__global__ void __launch_bounds__(kLinearThreads)
+binary_stream_bc_kernel(const StreamBcParams p) {
+    constexpr int ELEM = L == Leaf::BF16 ? 2 : 4;
+    constexpr uint32_t kTileVectors = kTileSlots * ELEM / 16;     // 32 or 64
+    constexpr uint32_t kVectorsPerRow = kTile * ELEM / 16;        // 2 or 4
+    constexpr uint64_t kChunk = static_cast<uint64_t>(kLinearThreads) * kLinearUnroll;
+    const uint64_t chunks = (p.vectors + kChunk - 1) / kChunk;
+    for (uint64_t chunk = blockIdx.x; chunk < chunks; chunk += gridDim.x) {
+        const uint64_t base = chunk * kChunk + threadIdx.x;
+        uint4 a[kLinearUnroll], b[kLinearUnroll];
+#pragma unroll
+        for (int u = 0; u < kLinearUnroll; ++u) {
+            const uint64_t index = base + u * kLinearThreads;
+            if (index < p.vectors) {
+                a[u] = load_u4_stream(p.big + index);
+                const uint32_t tile = static_cast<uint32_t>(index / kTileVectors);
+                const uint32_t in_tile = static_cast<uint32_t>(index % kTileVectors);
+                if constexpr (!COLUMN) {
+                    const uint32_t tc = p.cols_shift < 32 ? tile & ((1u << p.cols_shift) - 1u)
+                                                          : tile % p.tile_cols;
+                    b[u] = __ldg(reinterpret_cast<const uint4*>(
+                            p.small + static_cast<size_t>(tc) * kTileSlots * ELEM
+                            + (in_tile % kVectorsPerRow) * 16));
+                } else {
+                    uint32_t band = p.cols_shift < 32 ? tile >> p.cols_shift : tile / p.tile_cols;
+                    if (!p.single_plane) band %= p.tile_rows;
+                    const unsigned char* cell = p.small
+                            + static_cast<size_t>(band) * kTileSlots * ELEM
+                            + (in_tile / kVectorsPerRow) * kTile * ELEM;
+                    uint32_t value;
+                    if constexpr (ELEM == 4) {
+                        value = __ldg(reinterpret_cast<const uint32_t*>(cell));
+                    } else {
+                        const uint32_t half = __ldg(reinterpret_cast<const uint16_t*>(cell));
+                        value = half | (half << 16);
+                    }
+                    b[u] = make_uint4(value, value, value, value);
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kLinearUnroll; ++u) {
+            const uint64_t index = base + u * kLinearThreads;
+            if (index < p.vectors) {
+                store_u4_stream(p.out + index,
+                                SMALL_IS_LHS ? apply_vector<L, OP>(b[u], a[u])
+                                             : apply_vector<L, OP>(a[u], b[u]));
+            }
+        }
+    }
+}
+
+template <Leaf L, int OP>
+static int launch_stream_bc(const StreamBcParams& params, bool column, bool small_is_lhs,
+                            cudaStream_t stream) {
+    const uint64_t per_cta = static_cast<uint64_t>(kLinearThreads) * kLinearUnroll;
+    const unsigned grid = grid_one_shot((params.vectors + per_cta - 1) / per_cta);
+    if (column) {
+        if (small_is_lhs) binary_stream_bc_kernel<L, OP, true, true><<<grid, kLinearThreads, 0, stream>>>(params);
+        else binary_stream_bc_kernel<L, OP, true, false><<<grid, kLinearThreads, 0, stream>>>(params);
+    } else {
+        if (small_is_lhs) binary_stream_bc_kernel<L, OP, false, true><<<grid, kLinearThreads, 0, stream>>>(params);
+        else binary_stream_bc_kernel<L, OP, false, false><<<grid, kLinearThreads, 0, stream>>>(params);
+    }
+    return check_launch("binary launch");
+}
+
+template <Leaf L>
+static int launch_stream_bc_op(int op, const StreamBcParams& params, bool column,
+                               bool small_is_lhs, cudaStream_t stream) {
+    return op == IOMB_ADD ? launch_stream_bc<L, IOMB_ADD>(params, column, small_is_lhs, stream)
+                          : launch_stream_bc<L, IOMB_MUL>(params, column, small_is_lhs, stream);
 }
 
 // ---- tiled general kernel --------------------------------------------------
@@ -372,6 +469,57 @@ extern "C" int iomb_binary(int op, const iomb_view* lhs, const iomb_view* rhs,
         linear_vectors = params.leading.planes * fo.plane_bytes / 16;
     }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // One dense full-shape operand against a single broadcast row or column plane.
+    if (!linear && tile_multiple && broadcasts[0] != broadcasts[1]
+            && fo.tile_rows * fo.tile_cols * params.leading.planes < 0xFFFFFFFFull) {
+        const int small_index = broadcasts[0] ? 0 : 1;
+        const int big_index = 1 - small_index;
+        const iomb_view* small_view = small_index == 0 ? lhs : rhs;
+        const iomb_view* big_view = big_index == 0 ? lhs : rhs;
+        const ViewFacts& fs = small_index == 0 ? fl : fr;
+        const ViewFacts& fb = big_index == 0 ? fl : fr;
+        const bool row_form = fs.rows == 1 && fs.cols == fo.cols && fo.rows != 1;
+        const bool col_form = fs.cols == 1 && fs.rows == fo.rows && fo.cols != 1;
+        bool small_single = true;       // every leading axis of the small operand broadcasts
+        bool dense = true;              // big and out advance one plane per logical plane
+        const Operand& small_operand = small_index == 0 ? params.lhs : params.rhs;
+        const Operand& big_operand = big_index == 0 ? params.lhs : params.rhs;
+        for (uint32_t axis = 0; axis < params.leading.count; ++axis) {
+            if (small_operand.stride[axis] != 0) small_single = false;
+        }
+        if (params.leading.count > 1) dense = false;
+        if (params.leading.count == 1
+                && (big_operand.stride[0] != 1 || params.out.stride[0] != 1)) {
+            dense = false;
+        }
+        if ((row_form || col_form) && small_single && dense) {
+            StreamBcParams stream_params{};
+            stream_params.big = reinterpret_cast<const uint4*>(
+                    static_cast<unsigned char*>(big_view->base) + big_view->plane_offset * fb.plane_bytes);
+            stream_params.small = static_cast<const unsigned char*>(small_view->base)
+                    + small_view->plane_offset * fs.plane_bytes;
+            stream_params.out = reinterpret_cast<uint4*>(
+                    static_cast<unsigned char*>(out->base) + out->plane_offset * fo.plane_bytes);
+            stream_params.vectors = params.leading.planes * fo.plane_bytes / 16;
+            stream_params.tile_rows = static_cast<uint32_t>(fo.tile_rows);
+            stream_params.tile_cols = static_cast<uint32_t>(fo.tile_cols);
+            stream_params.cols_shift = 32;
+            if ((fo.tile_cols & (fo.tile_cols - 1)) == 0) {
+                uint32_t shift = 0;
+                while ((1ull << shift) < fo.tile_cols) ++shift;
+                stream_params.cols_shift = shift;
+            }
+            stream_params.single_plane = params.leading.planes == 1 ? 1u : 0u;
+            switch (leaf) {
+                case Leaf::I32:
+                    return launch_stream_bc_op<Leaf::I32>(op, stream_params, col_form, small_index == 0, s);
+                case Leaf::F32:
+                    return launch_stream_bc_op<Leaf::F32>(op, stream_params, col_form, small_index == 0, s);
+                default:
+                    return launch_stream_bc_op<Leaf::BF16>(op, stream_params, col_form, small_index == 0, s);
+            }
+        }
+    }
     switch (leaf) {
         case Leaf::I32: return launch_op<Leaf::I32>(op, params, linear, linear_vectors, s);
         case Leaf::F32: return launch_op<Leaf::F32>(op, params, linear, linear_vectors, s);

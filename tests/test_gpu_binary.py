@@ -23,6 +23,20 @@ CASES = [
     ((1, 15), (1, 15), (1, 15)),
     ((17, 1), (17, 1), (17, 1)),
     ((2, 1, 2, 1, 2, 1, 16, 17), (1, 3, 1, 2, 1, 2, 1, 17), (2, 3, 2, 2, 2, 2, 16, 17)),
+    # tile-multiple extents with one broadcast row / column plane: the linear-stream
+    # broadcast kernel (power-of-two and other tile-column counts, either operand
+    # small, several result planes, chunk tails).
+    ((64, 128), (1, 128), (64, 128)),
+    ((64, 128), (64, 1), (64, 128)),
+    ((1, 48), (160, 48), (160, 48)),
+    ((160, 1), (160, 48), (160, 48)),
+    ((3, 48, 80), (1, 80), (3, 48, 80)),
+    ((3, 48, 80), (48, 1), (3, 48, 80)),
+    ((1, 1, 256), (5, 32, 256), (5, 32, 256)),
+    ((1, 32, 1), (5, 32, 256), (5, 32, 256)),
+    ((2, 2, 32, 32), (1, 32), (2, 2, 32, 32)),
+    ((528, 512), (1, 512), (528, 512)),
+    ((528, 512), (528, 1), (528, 512)),
 ]
 
 
@@ -106,6 +120,32 @@ def test_binary_views_and_alias(gpu):
     run(queue, queue.mul(like(big, dl), like(rhs.view().permute([1, 0]), dr), like(big, dl)))
     assert oracle().iomo_binary(1, abi(big), abi(rhs.view().permute([1, 0])), abi(big), 0) == 0
     assert np.array_equal(download(dl), lhs.storage)
+
+
+@pytest.mark.parametrize("dtype", [DataType.F32, DataType.BF16])
+def test_binary_broadcast_stream_views(gpu, dtype):
+    """Bias add / per-row scale over windows: a dense plane range (offset, unit
+    stride) streams linearly, a strided one does not; both must match, and the
+    in-place form must leave every plane outside the window untouched."""
+    device, queue = gpu
+    rng = np.random.default_rng(11 + int(dtype))
+    big = HostTensor((6, 32, 64), dtype).poison()
+    out = HostTensor((6, 32, 64), dtype).poison()
+    row = HostTensor((2, 1, 64), dtype).poison()
+    col = HostTensor((32, 1), dtype).poison()
+    for t in (big, out, row, col):
+        t.view().copy_from_host(random_payload(rng, t.spec.shape, dtype))
+    window = big.view().slice(0, 2, 3, 1)
+    strided = big.view().slice(0, 0, 3, 2)
+    one_row = row.view().slice(0, 1, 1, 1)
+    check(queue, device, "add", big, row, out, window, one_row, out.view().slice(0, 1, 3, 1))
+    check(queue, device, "mul", col, big, out, col.view(), window, out.view().slice(0, 3, 3, 1))
+    check(queue, device, "add", big, row, out, strided, one_row, out.view().slice(0, 0, 3, 2))
+    # in place: out is the big operand's own window
+    db, dr = upload(device, big), upload(device, row)
+    run(queue, queue.add(like(window, db), like(one_row, dr), like(window, db)))
+    assert oracle().iomo_binary(0, abi(window), abi(one_row), abi(window), 0) == 0
+    assert np.array_equal(download(db), big.storage)
 
 
 def test_binary_rejections(gpu):
