@@ -60,7 +60,9 @@ typedef enum iomb_dtype {
 /* DeviceOps::BinaryOperation (include/iom/iom.hpp:381). */
 typedef enum iomb_binary_op {
     IOMB_ADD = 0,
-    IOMB_MUL = 1
+    IOMB_MUL = 1,
+    IOMB_SUB = 2,
+    IOMB_DIV = 3
 } iomb_binary_op;
 
 /*
@@ -109,13 +111,14 @@ uint64_t iomb_plane_slot(uint64_t rows, uint64_t columns, uint64_t plane,
                          uint64_t row, uint64_t column); /* detail::standard_plane_slot, src/tensor.cpp:136-164 */
 
 /*
- * out = lhs (+|*) rhs with right-aligned broadcasting.
+ * out = lhs (+|*|-|/) rhs with right-aligned broadcasting.
  * Replaces GpuQueue::binary_impl + grid_stride_binary_kernel / alias_safe_binary_kernel
  * (src/shared/gpu_queue_operations.inl:65-124,756-818; src/shared/standard_tiled_add.inl:206-464);
  * admission rules of DeviceOps::validate_binary (src/device_ops_binary.cpp:102-181).
- * Leaves: I32/U32 (wrap), F32, BF16. Arithmetic equals the scalar codec
- * (src/shared/scalar_binary_codec.hpp:120-178): IEEE binary32 op, one RNE encode,
- * every NaN result is the positive quiet NaN (0x7FC00000 / 0x7FC0).
+ * Leaves: I32/U32 (wrap; no division, as src/device_ops_binary.cpp:46-57), F32, BF16.
+ * Arithmetic equals the scalar codec (src/shared/scalar_binary_codec.hpp:120-178):
+ * IEEE binary32 op (division correctly rounded), one RNE encode, every NaN result is
+ * the positive quiet NaN (0x7FC00000 / 0x7FC0).
  * Exact in-place alias (out is the same view as an input) is allowed.
  */
 int iomb_binary(int op, const iomb_view* lhs, const iomb_view* rhs,

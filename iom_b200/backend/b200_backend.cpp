@@ -423,10 +423,13 @@ protected:
                 });
     }
 
+    static_assert(static_cast<int>(BinaryOperation::Add) == IOMB_ADD
+                          && static_cast<int>(BinaryOperation::Mul) == IOMB_MUL
+                          && static_cast<int>(BinaryOperation::Sub) == IOMB_SUB
+                          && static_cast<int>(BinaryOperation::Div) == IOMB_DIV,
+                  "BinaryOperation and iomb_binary_op must share their ordinals");
+
     oid binary_impl(const BinaryRequest& request) override {
-        if (request.operation != BinaryOperation::Add && request.operation != BinaryOperation::Mul) {
-            throw detail::UnsupportedOperation();
-        }
         switch (request.out.spec.data_type) {
             case DataType::I32: case DataType::U32: case DataType::F32: case DataType::BF16: break;
             default: throw detail::UnsupportedOperation();
@@ -439,9 +442,9 @@ protected:
                     launch_three_owner(sequence, entries, captured.workspace_lease, [&] {
                         const iomb_view lhs = to_view(captured.lhs), rhs = to_view(captured.rhs),
                                         out = to_view(captured.out);
-                        check_status(iomb_binary(
-                                captured.operation == BinaryOperation::Add ? IOMB_ADD : IOMB_MUL,
-                                &lhs, &rhs, &out, stream_));
+                        // BinaryOperation and iomb_binary_op share their ordinals.
+                        check_status(iomb_binary(static_cast<int>(captured.operation), &lhs, &rhs,
+                                                 &out, stream_));
                     });
                 });
     }

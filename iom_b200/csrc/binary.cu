@@ -1,4 +1,4 @@
-// Elementwise ADD / MUL with right-aligned broadcasting on tiled storage.
+// Elementwise ADD / MUL / SUB / DIV with right-aligned broadcasting on tiled storage.
 //
 // Replaces grid_stride_binary_kernel / alias_safe_binary_kernel of the
 // reference (src/shared/standard_tiled_add.inl:206-464). Three kernels:
@@ -15,9 +15,10 @@
 //                         logical bounds mask the stores so padding is never
 //                         written.
 //
-// Arithmetic: IEEE binary32 add/mul without contraction, one RNE encode for
-// BF16, canonical positive quiet NaN (src/shared/scalar_binary_codec.hpp:120-178).
-// Integers wrap. Each lane reads its inputs before it stores the same slots, so
+// Arithmetic: one IEEE binary32 operation without contraction (division correctly
+// rounded), one RNE encode for BF16, canonical positive quiet NaN
+// (src/shared/scalar_binary_codec.hpp:120-178). Integers wrap and have no division
+// (src/device_ops_binary.cpp:46-57). Each lane reads its inputs before it stores the same slots, so
 // the exact in-place alias the reference handles with a shared-memory snapshot
 // needs no special path here.
 #include "host.hpp"
@@ -26,20 +27,26 @@ namespace iomb {
 
 enum class Leaf : int { I32 = 0, F32 = 1, BF16 = 2 };
 
+// One IEEE binary32 operation, rounded once (never contracted); division is the
+// correctly rounded quotient.
+template <int OP>
+__device__ __forceinline__ float apply_f32(float x, float y) {
+    if constexpr (OP == IOMB_ADD) return __fadd_rn(x, y);
+    if constexpr (OP == IOMB_MUL) return __fmul_rn(x, y);
+    if constexpr (OP == IOMB_SUB) return __fsub_rn(x, y);
+    return __fdiv_rn(x, y);
+}
+
 template <Leaf L, int OP>
 __device__ __forceinline__ uint32_t apply_word(uint32_t a, uint32_t b) {
     if constexpr (L == Leaf::I32) {
-        return OP == IOMB_ADD ? a + b : a * b;
+        // Integers wrap; the reference admits no integer division.
+        return OP == IOMB_ADD ? a + b : OP == IOMB_MUL ? a * b : a - b;
     } else if constexpr (L == Leaf::F32) {
-        const float x = __uint_as_float(a), y = __uint_as_float(b);
-        const float r = OP == IOMB_ADD ? __fadd_rn(x, y) : __fmul_rn(x, y);
-        return f32_canonical_bits(r);
+        return f32_canonical_bits(apply_f32<OP>(__uint_as_float(a), __uint_as_float(b)));
     } else {
-        const float lo = OP == IOMB_ADD ? __fadd_rn(bf16_lo(a), bf16_lo(b))
-                                        : __fmul_rn(bf16_lo(a), bf16_lo(b));
-        const float hi = OP == IOMB_ADD ? __fadd_rn(bf16_hi(a), bf16_hi(b))
-                                        : __fmul_rn(bf16_hi(a), bf16_hi(b));
-        return pack_bf16x2_canonical(lo, hi);
+        return pack_bf16x2_canonical(apply_f32<OP>(bf16_lo(a), bf16_lo(b)),
+                                     apply_f32<OP>(bf16_hi(a), bf16_hi(b)));
     }
 }
 
@@ -180,8 +187,17 @@ static int launch_stream_bc(const StreamBcParams& params, bool column, bool smal
 template <Leaf L>
 static int launch_stream_bc_op(int op, const StreamBcParams& params, bool column,
                                bool small_is_lhs, cudaStream_t stream) {
-    return op == IOMB_ADD ? launch_stream_bc<L, IOMB_ADD>(params, column, small_is_lhs, stream)
-                          : launch_stream_bc<L, IOMB_MUL>(params, column, small_is_lhs, stream);
+    switch (op) {
+        case IOMB_ADD: return launch_stream_bc<L, IOMB_ADD>(params, column, small_is_lhs, stream);
+        case IOMB_MUL: return launch_stream_bc<L, IOMB_MUL>(params, column, small_is_lhs, stream);
+        case IOMB_SUB: return launch_stream_bc<L, IOMB_SUB>(params, column, small_is_lhs, stream);
+        default:
+            if constexpr (L == Leaf::I32) {
+                return fail(IOMB_ERR_UNSUPPORTED, "binary: integer division is not admitted");
+            } else {
+                return launch_stream_bc<L, IOMB_DIV>(params, column, small_is_lhs, stream);
+            }
+    }
 }
 
 // ---- tiled general kernel --------------------------------------------------
@@ -356,8 +372,17 @@ static int launch(const BinaryParams& params, bool linear, uint64_t linear_vecto
 template <Leaf L>
 static int launch_op(int op, const BinaryParams& params, bool linear,
                      uint64_t linear_vectors, cudaStream_t stream) {
-    return op == IOMB_ADD ? launch<L, IOMB_ADD>(params, linear, linear_vectors, stream)
-                          : launch<L, IOMB_MUL>(params, linear, linear_vectors, stream);
+    switch (op) {
+        case IOMB_ADD: return launch<L, IOMB_ADD>(params, linear, linear_vectors, stream);
+        case IOMB_MUL: return launch<L, IOMB_MUL>(params, linear, linear_vectors, stream);
+        case IOMB_SUB: return launch<L, IOMB_SUB>(params, linear, linear_vectors, stream);
+        default:
+            if constexpr (L == Leaf::I32) {
+                return fail(IOMB_ERR_UNSUPPORTED, "binary: integer division is not admitted");
+            } else {
+                return launch<L, IOMB_DIV>(params, linear, linear_vectors, stream);
+            }
+    }
 }
 
 }  // namespace iomb
@@ -365,8 +390,8 @@ static int launch_op(int op, const BinaryParams& params, bool linear,
 extern "C" int iomb_binary(int op, const iomb_view* lhs, const iomb_view* rhs,
                            const iomb_view* out, void* stream) {
     using namespace iomb;
-    if (op != IOMB_ADD && op != IOMB_MUL) {
-        return fail(IOMB_ERR_UNSUPPORTED, "binary: only ADD and MUL are implemented");
+    if (op < IOMB_ADD || op > IOMB_DIV) {
+        return fail(IOMB_ERR_INVALID_ARGUMENT, "binary: unknown operation");
     }
     ViewFacts fl{}, fr{}, fo{};
     int status = check_view(lhs, "binary lhs", &fl);

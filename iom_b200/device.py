@@ -31,7 +31,7 @@ OID_RESOURCE_EXHAUSTED = -4
 OID_DEVICE_ERROR = -5
 OID_INTERNAL_ERROR = -6
 
-ADD, MUL = 0, 1
+ADD, MUL, SUB, DIV = 0, 1, 2, 3
 RMS_LANES16, RMS_SEQUENTIAL = 0, 1
 
 _ALIGNMENT = 256          # arena suballocation granularity (the contract needs 32)
@@ -475,11 +475,11 @@ class B200Queue:
     def mul(self, lhs: TensorView, rhs: TensorView, out: TensorView, workspace=None) -> int:
         return self._binary(MUL, lhs, rhs, out)
 
-    def sub(self, lhs, rhs, out, workspace=None) -> int:
-        return OID_UNSUPPORTED
+    def sub(self, lhs: TensorView, rhs: TensorView, out: TensorView, workspace=None) -> int:
+        return self._binary(SUB, lhs, rhs, out)
 
-    def div(self, lhs, rhs, out, workspace=None) -> int:
-        return OID_UNSUPPORTED
+    def div(self, lhs: TensorView, rhs: TensorView, out: TensorView, workspace=None) -> int:
+        return self._binary(DIV, lhs, rhs, out)
 
     def rmsnorm(self, x: TensorView, scale: TensorView, out: TensorView, eps: float,
                 workspace: Optional[RawWorkspaceView] = None, order: int = RMS_LANES16) -> int:

@@ -258,16 +258,18 @@ static uint32_t float_to_bf16_rne(float value) {
     return (bits + 0x7FFFu + ((bits >> 16) & 1u)) >> 16;
 }
 
-/* The arithmetic the kernels implement: IEEE binary32 add/mul (rounded once),
- * then one RNE encode for BF16, every NaN result canonical. Equal to
- * iomo_scalar_binary for I32/U32/F32/BF16 add/mul because rounding a binary32
+/* The arithmetic the kernels implement: one IEEE binary32 add/mul/sub/div
+ * (rounded once), then one RNE encode for BF16, every NaN result canonical.
+ * Equal to iomo_scalar_binary for I32/U32/F32/BF16 because rounding a binary32
  * (or x87) result again to a format with fewer than half its significand bits
- * is innocuous; tests/test_oracle_codec.py proves the equality exhaustively
- * for BF16 and on boundary-rich samples for F32. */
+ * is innocuous for all four operations; tests/test_layout_and_codec.py proves
+ * the equality exhaustively for BF16 and on boundary-rich samples for F32.
+ * Integer division does not exist (the codec answers 0, admission rejects it). */
 uint64_t iomo_scalar_binary_ieee(int op, uint32_t dtype, uint64_t a, uint64_t b) {
     if (dtype == DT_I32 || dtype == DT_U32) {
         const uint32_t x = (uint32_t)a, y = (uint32_t)b;
-        return op == 0 ? (uint32_t)(x + y) : (uint32_t)(x * y);
+        if (op == 3) return 0;
+        return op == 0 ? (uint32_t)(x + y) : op == 1 ? (uint32_t)(x * y) : (uint32_t)(x - y);
     }
     float x, y;
     if (dtype == DT_BF16) {
@@ -277,7 +279,7 @@ uint64_t iomo_scalar_binary_ieee(int op, uint32_t dtype, uint64_t a, uint64_t b)
         x = bits_to_float((uint32_t)a);
         y = bits_to_float((uint32_t)b);
     }
-    volatile float r = op == 0 ? x + y : x * y;
+    volatile float r = op == 0 ? x + y : op == 1 ? x * y : op == 2 ? x - y : x / y;
     const float result = r;
     if (dtype == DT_BF16) return float_to_bf16_rne(result);
     return isnan(result) ? 0x7FC00000u : float_to_bits(result);

@@ -49,7 +49,9 @@ def binary_cases(ref, out):
               ((32, 48), (1, 48), (32, 48)), ((32, 48), (32, 1), (32, 48)),
               ((5, 31), (1, 1), (5, 31))]
     for dtype in (DataType.I32, DataType.F32, DataType.BF16):
-        for op, code in (("add", 0), ("mul", 1)):
+        for op, code in (("add", 0), ("mul", 1), ("sub", 2), ("div", 3)):
+            if op == "div" and dtype == DataType.I32:
+                continue      # the reference admits no integer division
             for i, (ls, rs, os_) in enumerate(shapes):
                 rng = np.random.default_rng(1000 + 10 * int(dtype) + i)
                 lhs = owner(ref, ls, dtype, random_payload(rng, ls, dtype))
@@ -67,7 +69,7 @@ def binary_cases(ref, out):
                 out[key + "_shapes"] = np.array([len(ls), *ls, len(rs), *rs, len(os_), *os_])
     for dtype, specials in ((DataType.F32, SPECIAL_F32), (DataType.BF16, SPECIAL_BF16)):
         n = len(specials)
-        for op, code in (("add", 0), ("mul", 1)):
+        for op, code in (("add", 0), ("mul", 1), ("sub", 2), ("div", 3)):
             lhs = owner(ref, (n, n), dtype, np.repeat(specials, n).reshape(n, n))
             rhs = owner(ref, (n, n), dtype, np.tile(specials, n).reshape(n, n))
             res = owner(ref, (n, n), dtype, np.zeros((n, n), dtype=specials.dtype))

@@ -71,7 +71,7 @@ def test_admission_rejects_before_any_device_work():
     assert lib.iomb_binary(0, ctypes.byref(va), ctypes.byref(vb), ctypes.byref(va), None) == 1
     assert "broadcast" in _abi.last_error()
     assert lib.iomb_binary(0, ctypes.byref(va), ctypes.byref(va), ctypes.byref(vc), None) == 1
-    assert lib.iomb_binary(7, ctypes.byref(va), ctypes.byref(va), ctypes.byref(va), None) == 2
+    assert lib.iomb_binary(7, ctypes.byref(va), ctypes.byref(va), ctypes.byref(va), None) == 1   # unknown operation
     assert lib.iomb_binary(0, None, ctypes.byref(va), ctypes.byref(va), None) == 1
     bad = a.view().as_abi()
     bad.storage_bytes = 100                       # view exceeds its owner

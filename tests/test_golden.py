@@ -37,23 +37,28 @@ def view_from(tensor, described, rank):
     return TensorView(tensor, TensorSpec(dims, tensor.spec.data_type), offset, strides)
 
 
+OP_CODES = {"add": 0, "mul": 1, "sub": 2, "div": 3}
+
+
 @pytest.mark.parametrize("dtype", [DataType.I32, DataType.F32, DataType.BF16])
-@pytest.mark.parametrize("op", ["add", "mul"])
+@pytest.mark.parametrize("op", ["add", "mul", "sub", "div"])
 @pytest.mark.parametrize("case", range(BINARY_SHAPES))
 @pytest.mark.parametrize("ieee", [0, 1])
 def test_binary_golden(dtype, op, case, ieee):
+    if op == "div" and dtype == DataType.I32:
+        pytest.skip("the reference admits no integer division")
     key = f"binary_{op}_{dtype.name}_{case}"
     ls, rs, os_ = split_shapes(GOLDEN[key + "_shapes"])
     lhs = host_from(GOLDEN[key + "_lhs"], ls, dtype)
     rhs = host_from(GOLDEN[key + "_rhs"], rs, dtype)
     out = host_from(GOLDEN[key + "_out_before"], os_, dtype)
-    assert oracle().iomo_binary(0 if op == "add" else 1, abi(lhs.view()), abi(rhs.view()),
+    assert oracle().iomo_binary(OP_CODES[op], abi(lhs.view()), abi(rhs.view()),
                                 abi(out.view()), ieee) == 0
     assert np.array_equal(out.storage, GOLDEN[key + "_out"])
 
 
 @pytest.mark.parametrize("dtype", [DataType.F32, DataType.BF16])
-@pytest.mark.parametrize("op", ["add", "mul"])
+@pytest.mark.parametrize("op", ["add", "mul", "sub", "div"])
 def test_special_values_golden(dtype, op):
     key = f"special_{op}_{dtype.name}"
     n = int(round((GOLDEN[key + "_out"].size / (4 if dtype == DataType.F32 else 2)) ** 0.5))
@@ -63,7 +68,7 @@ def test_special_values_golden(dtype, op):
     for ieee in (0, 1):
         out = HostTensor((n, n), dtype).poison(0xA5)
         out.view().copy_from_host(np.zeros((n, n), dtype=np.uint32 if dtype == DataType.F32 else np.uint16))
-        assert oracle().iomo_binary(0 if op == "add" else 1, abi(lhs.view()), abi(rhs.view()),
+        assert oracle().iomo_binary(OP_CODES[op], abi(lhs.view()), abi(rhs.view()),
                                     abi(out.view()), ieee) == 0
         assert np.array_equal(out.storage, GOLDEN[key + "_out"])
 

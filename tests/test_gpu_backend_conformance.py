@@ -57,7 +57,7 @@ def same(owners):
 
 
 @pytest.mark.parametrize("dtype", [DataType.I32, DataType.U32, DataType.F32, DataType.BF16])
-@pytest.mark.parametrize("op", [0, 1])
+@pytest.mark.parametrize("op", [0, 1, 2, 3])
 @pytest.mark.parametrize("shapes", [
     ((2, 17, 33), (2, 17, 33), (2, 17, 33)), ((2, 1, 33), (1, 17, 1), (2, 17, 33)),
     ((64, 256), (1, 256), (64, 256)), ((32, 48), (32, 1), (32, 48)), ((1, 1), (3, 20, 35), (3, 20, 35)),
@@ -65,9 +65,13 @@ def same(owners):
 def test_binary(pair, dtype, op, shapes):
     rng = np.random.default_rng(5)
     lhs, rhs, out = (both(pair, s, dtype, rng) for s in shapes)
+    integer_division = op == 3 and dtype in (DataType.I32, DataType.U32)
     for i, ref in enumerate(pair):
         token = ref.lib.iomref_binary(ref.queue, op, lhs[i].view().handle, rhs[i].view().handle,
                                       out[i].view().handle)
+        if integer_division:
+            assert token == -2          # both backends: UnsupportedOperation at admission
+            continue
         assert ref.run(token) == 0, ref.error()
     same(out)
     same(lhs)
@@ -89,9 +93,8 @@ def test_binary_views_alias_and_rejections(pair):
         # the facade's own rejections arrive unchanged through the new backend
         assert ref.lib.iomref_binary(ref.queue, 0, ov[i].handle, other[i].handle, lv[i].handle) == -1
     same(out)
-    # SUB/DIV are not served by this backend: explicit Unsupported, never a fallback
+    # leaves this backend does not serve: explicit Unsupported, never a fallback
     cpu, gpu = pair
-    assert gpu.lib.iomref_binary(gpu.queue, 2, ov[1].handle, rv[1].handle, ov[1].handle) == -2
     f64 = gpu.tensor((16, 16), DataType.F64)
     assert gpu.lib.iomref_binary(gpu.queue, 0, f64.view().handle, f64.view().handle,
                                  f64.view().handle) == -2

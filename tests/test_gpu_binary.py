@@ -7,7 +7,7 @@ from gpu_support import download, gpu, like, run, upload  # noqa: F401
 from support import (HostTensor, SPECIAL_BF16, SPECIAL_F32, abi, oracle, random_payload)
 
 pytestmark = pytest.mark.gpu
-OPS = {"add": 0, "mul": 1}
+OPS = {"add": 0, "mul": 1, "sub": 2, "div": 3}
 DTYPES = [DataType.I32, DataType.U32, DataType.F32, DataType.BF16]
 
 CASES = [
@@ -45,8 +45,7 @@ def check(queue, device, op, lhs, rhs, out, lv=None, rv=None, ov=None):
     rv = rv or rhs.view()
     ov = ov or out.view()
     dl, dr, do = upload(device, lhs), upload(device, rhs), upload(device, out)
-    fn = queue.add if op == "add" else queue.mul
-    run(queue, fn(like(lv, dl), like(rv, dr), like(ov, do)))
+    run(queue, getattr(queue, op)(like(lv, dl), like(rv, dr), like(ov, do)))
     assert oracle().iomo_binary(OPS[op], abi(lv), abi(rv), abi(ov), 0) == 0
     assert np.array_equal(download(do), out.storage)
     # inputs untouched
@@ -54,10 +53,12 @@ def check(queue, device, op, lhs, rhs, out, lv=None, rv=None, ov=None):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("op", ["add", "mul"])
+@pytest.mark.parametrize("op", ["add", "mul", "sub", "div"])
 @pytest.mark.parametrize("shapes", CASES)
 def test_binary_parity(gpu, dtype, op, shapes):
     device, queue = gpu
+    if op == "div" and dtype in (DataType.I32, DataType.U32):
+        pytest.skip("integer division is rejected (test_binary_rejections)")
     rng = np.random.default_rng(abs(hash((int(dtype), op, shapes))) & 0xFFFF)
     tensors = []
     for shape in shapes:
@@ -68,7 +69,7 @@ def test_binary_parity(gpu, dtype, op, shapes):
 
 
 @pytest.mark.parametrize("dtype,specials", [(DataType.F32, SPECIAL_F32), (DataType.BF16, SPECIAL_BF16)])
-@pytest.mark.parametrize("op", ["add", "mul"])
+@pytest.mark.parametrize("op", ["add", "mul", "sub", "div"])
 def test_binary_special_values(gpu, dtype, op, specials):
     device, queue = gpu
     n = len(specials)
@@ -79,7 +80,7 @@ def test_binary_special_values(gpu, dtype, op, specials):
 
 
 def test_binary_exhaustive_bf16_pairs(gpu):
-    """Every BF16 code against 512 boundary-rich codes, both operations."""
+    """Every BF16 code against 512 boundary-rich codes, all four operations."""
     device, queue = gpu
     a = np.arange(65536, dtype=np.uint16)
     mant = np.array([0, 1, 2, 0x3F, 0x40, 0x41, 0x7E, 0x7F], dtype=np.uint16)
@@ -93,10 +94,9 @@ def test_binary_exhaustive_bf16_pairs(gpu):
     out = HostTensor((65536, 512), DataType.BF16)
     lhs.view().copy_from_host(np.repeat(a, 512).reshape(65536, 512))
     rhs.view().copy_from_host(np.tile(b, 65536).reshape(65536, 512))
-    for op in ("add", "mul"):
+    for op in ("add", "mul", "sub", "div"):
         dl, dr, do = upload(device, lhs), upload(device, rhs), upload(device, out)
-        fn = queue.add if op == "add" else queue.mul
-        run(queue, fn(dl.view(), dr.view(), do.view()))
+        run(queue, getattr(queue, op)(dl.view(), dr.view(), do.view()))
         assert oracle().iomo_binary(OPS[op], abi(lhs.view()), abi(rhs.view()), abi(out.view()), 1) == 0
         assert np.array_equal(download(do), out.storage)
         for t in (dl, dr, do):
@@ -158,5 +158,8 @@ def test_binary_rejections(gpu):
     assert queue.add(a.view().slice(0, 0, 2), a.view().slice(0, 1, 2), a.view().slice(0, 0, 2)) == -1
     f64 = device.create_tensor(HostTensor((16, 16), DataType.F64).spec)
     assert queue.add(f64.view(), f64.view(), f64.view()) == -2    # leaf not served
+    i32 = device.create_tensor(HostTensor((16, 16), DataType.I32).spec)
+    assert queue.div(i32.view(), i32.view(), i32.view()) == -2    # no integer division
+    assert queue.sub(i32.view(), i32.view(), i32.view()) > 0
     with pytest.raises(ValueError):
         queue.wait(12345)

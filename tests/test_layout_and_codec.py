@@ -97,7 +97,7 @@ def boundary_bf16():
     return np.array(codes, dtype=np.uint16)
 
 
-@pytest.mark.parametrize("op", [ADD, MUL])
+@pytest.mark.parametrize("op", [ADD, MUL, SUB, DIV])
 def test_ieee_form_equals_codec_bf16(op):
     """Every BF16 code against a boundary-rich set: the arithmetic the kernels
     implement (binary32 op, RNE, canonical NaN) equals the reference codec."""
@@ -108,7 +108,7 @@ def test_ieee_form_equals_codec_bf16(op):
     assert mismatches == 0
 
 
-@pytest.mark.parametrize("op", [ADD, MUL])
+@pytest.mark.parametrize("op", [ADD, MUL, SUB, DIV])
 def test_ieee_form_equals_codec_f32(op):
     rng = np.random.default_rng(9)
     exps = np.array([0, 1, 2, 23, 24, 25, 100, 126, 127, 128, 149, 150, 151, 230, 253, 254, 255],
