@@ -439,6 +439,27 @@ def ops_table(device, queue, only=None, iters: int = 10) -> dict:
         scratch.close()
         cell.close()
         release()
+    if only is None or only in ("silu_bf16", "silu_mul_bf16", "silu_then_mul_bf16", "silu_f32"):
+        # Decoder MLP gate, TinyLlama geometry (intermediate 5632), 32768 rows: 369 MB per tensor.
+        rows, inter = 32768, 5632
+        count = rows * inter
+        g, u, a, o = (tensor((rows, inter), DataType.BF16) for _ in range(4))
+        record("silu_bf16", 2 * count * 2, lambda: ok(queue.silu(g.view(), a.view())),
+               f"[{rows},{inter}]")
+        record("silu_mul_bf16", 3 * count * 2,
+               lambda: ok(queue.silu_mul(g.view(), u.view(), o.view())), f"[{rows},{inter}]")
+
+        def silu_then_mul():
+            ok(queue.silu(g.view(), a.view()))
+            return ok(queue.mul(a.view(), u.view(), o.view()))
+        # The unfused pair moves 5 tensors; its figure counts the fused op's 3 so that
+        # the two lines compare the same useful work.
+        record("silu_then_mul_bf16", 3 * count * 2, silu_then_mul, f"[{rows},{inter}] two launches")
+        release()
+        gf, af = tensor((rows // 2, inter), DataType.F32), tensor((rows // 2, inter), DataType.F32)
+        record("silu_f32", 2 * (count // 2) * 4, lambda: ok(queue.silu(gf.view(), af.view())),
+               f"[{rows // 2},{inter}]")
+        release()
     if only is None or only in ("embedding_decode", "cache_append_decode_batched",
                                 "cache_append_decode_64calls", "cast_logits"):
         # Decode-step data movement, TinyLlama geometry (BASELINE config 4): microseconds.

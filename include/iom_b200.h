@@ -165,6 +165,31 @@ int iomb_copy(const iomb_view* source, const iomb_view* destination, void* strea
 int iomb_cast(const iomb_view* source, const iomb_view* destination, void* stream);
 
 /*
+ * out = x * sigmoid(x), elementwise, between views of identical shape and leaf.
+ * Replaces GpuQueue::silu_impl + silu_kernel (src/cuda/copy.cu:452-596); admission
+ * rules of validate_silu (src/device_ops_neural.cpp:362-434: equal shapes and
+ * specifications, the output shares neither an owner nor a byte with the input).
+ * Arithmetic is scalar_silu on the FP64 carrier of the reference's GPU backends
+ * (src/shared/scalar_silu.hpp:66-101, src/cuda/copy.cu:498-503): decode, evaluate
+ * the stable form, one RNE encode, canonical NaN. Leaves: BF16, F32. For BF16 the
+ * result equals the reference CPU backend's FP32 evaluation for every one of the
+ * 65 536 codes. The first BF16 call on a device builds a 128 KiB table inside the
+ * library and waits for it once: make it before any stream capture.
+ */
+int iomb_silu(const iomb_view* x, const iomb_view* out, void* stream);
+
+/*
+ * out = silu(x) * up; `activated` (may be NULL) receives silu(x) when given.
+ * The decoder MLP's SiLU(gate) followed by the multiply with the up projection
+ * (src/session.cpp:2020-2030) in one pass. Results equal iomb_silu followed by
+ * iomb_binary(IOMB_MUL) bit for bit (the activated value is rounded to the leaf
+ * before the product). Written views share no owner and no byte with any other
+ * operand.
+ */
+int iomb_silu_mul(const iomb_view* x, const iomb_view* up, const iomb_view* activated,
+                  const iomb_view* out, void* stream);
+
+/*
  * out[b, r, f] = table[indices[b, 0, r], f] (raw bits).
  * Replaces GpuQueue::embedding_impl + embedding_word_kernel and its status protocol
  * (src/shared/standard_tiled_embedding.inl:117-199; src/shared/gpu_queue_operations.inl:870-919;

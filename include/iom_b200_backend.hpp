@@ -31,5 +31,11 @@ namespace b200 {
 oid add_rmsnorm(DeviceOps& queue, const TensorView& x, const TensorView& residual,
                 const TensorView& scale, TensorView& sum, TensorView& out, float eps);
 
+// Extension outside the DeviceOps facade: out = silu(x) * up in one pass, the
+// decoder MLP's SiLU(gate) followed by the multiply with the up projection.
+// `activated` (may be null) receives silu(x). Results equal silu then mul.
+oid silu_mul(DeviceOps& queue, const TensorView& x, const TensorView& up, TensorView* activated,
+             TensorView& out);
+
 }  // namespace b200
 }  // namespace iom

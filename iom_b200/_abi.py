@@ -45,6 +45,8 @@ PROTOTYPES = {
                                         ctypes.c_int, ctypes.c_void_p]),
     "iomb_copy": (ctypes.c_int, [_VIEW, _VIEW, ctypes.c_void_p]),
     "iomb_cast": (ctypes.c_int, [_VIEW, _VIEW, ctypes.c_void_p]),
+    "iomb_silu": (ctypes.c_int, [_VIEW, _VIEW, ctypes.c_void_p]),
+    "iomb_silu_mul": (ctypes.c_int, [_VIEW, _VIEW, _VIEW, _VIEW, ctypes.c_void_p]),
     "iomb_embedding": (ctypes.c_int, [_VIEW, _VIEW, _VIEW, ctypes.c_void_p, ctypes.c_void_p]),
     "iomb_cache_append": (ctypes.c_int, [_VIEW, _VIEW, ctypes.c_uint64, ctypes.c_void_p]),
     "iomb_cache_append_batched": (ctypes.c_int, [_VIEW, _VIEW, ctypes.c_void_p, ctypes.c_void_p,

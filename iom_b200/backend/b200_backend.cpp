@@ -393,6 +393,34 @@ public:
         }
     }
 
+    // Extension entry (see iom_b200_backend.hpp). `activated` may be null.
+    oid silu_mul(const TensorView& x, const TensorView& up, TensorView* activated, TensorView& out) {
+        try {
+            if (activated != nullptr) {
+                validate_views(queue_device(), {&x, &up, activated, &out});
+            } else {
+                validate_views(queue_device(), {&x, &up, &out});
+            }
+            const iomb_view vx = to_view(x), vu = to_view(up), vo = to_view(out);
+            const bool stores_activated = activated != nullptr;
+            const iomb_view va = stores_activated ? to_view(*activated) : iomb_view{};
+            std::lock_guard<std::mutex> order(submission_order_mutex_);
+            return submit([this, vx, vu, va, vo, stores_activated](std::uint64_t sequence) {
+                device_->activate();
+                check_status(iomb_silu_mul(&vx, &vu, stores_activated ? &va : nullptr, &vo, stream_));
+                retire(sequence, [] {}, nullptr);
+            });
+        } catch (const std::invalid_argument&) {
+            return to_oid(OidError::InvalidArgument);
+        } catch (const detail::UnsupportedOperation&) {
+            return to_oid(OidError::Unsupported);
+        } catch (const std::bad_alloc&) {
+            return to_oid(OidError::ResourceExhausted);
+        } catch (...) {
+            return to_oid(OidError::DeviceError);
+        }
+    }
+
 protected:
     [[nodiscard]] std::string_view backend_label() const noexcept override { return "B200"; }
 
@@ -522,6 +550,27 @@ protected:
                         const iomb_view src = to_view_fixed(captured.source),
                                         dst = to_view_fixed(captured.destination);
                         check_status(iomb_cache_append(&src, &dst, captured.a, stream_));
+                    });
+                });
+    }
+
+    [[nodiscard]] WorkspaceRequirements silu_workspace_requirements_impl(
+            const SiLURequest& request) override {
+        if (request.x.data_type != DataType::BF16 && request.x.data_type != DataType::F32) {
+            throw detail::UnsupportedOperation();
+        }
+        return {0, 1};
+    }
+
+    oid silu_impl(const SiLURequest& request) override {
+        std::lock_guard<std::mutex> order(submission_order_mutex_);
+        return submit_silu(
+                request, device_->registry_state(), registry_queue_id_, fence(),
+                [this](std::uint64_t sequence, const SiLURequest& captured,
+                       detail::BinaryEntryRegistration entries) {
+                    launch_three_owner(sequence, entries, {}, [&] {
+                        const iomb_view x = to_view_fixed(captured.x), y = to_view_fixed(captured.y);
+                        check_status(iomb_silu(&x, &y, stream_));
                     });
                 });
     }
@@ -657,6 +706,13 @@ oid add_rmsnorm(DeviceOps& queue, const TensorView& x, const TensorView& residua
     auto* native = dynamic_cast<B200Queue*>(&queue);
     if (native == nullptr) return to_oid(OidError::InvalidArgument);
     return native->add_rmsnorm(x, residual, scale, sum, out, eps);
+}
+
+oid silu_mul(DeviceOps& queue, const TensorView& x, const TensorView& up, TensorView* activated,
+             TensorView& out) {
+    auto* native = dynamic_cast<B200Queue*>(&queue);
+    if (native == nullptr) return to_oid(OidError::InvalidArgument);
+    return native->silu_mul(x, up, activated, out);
 }
 
 }  // namespace b200

@@ -603,8 +603,36 @@ class B200Queue:
             (x.owner, scratch.owner))
 
     # The remaining operations of the contract are not part of this backend.
-    def silu(self, *args, **kwargs) -> int:
-        return OID_UNSUPPORTED
+    def silu_workspace_requirements(self, x, y) -> WorkspaceRequirements:
+        return WorkspaceRequirements(0, 1)
+
+    def silu(self, x: TensorView, y: TensorView, workspace=None) -> int:
+        try:
+            self._check_view(x, "x")
+            self._check_view(y, "y")
+            a, b = x.as_abi(), y.as_abi()
+        except BaseException as error:
+            return _exception_to_oid(error)
+        return self._submit(
+            lambda stream: self._lib.iomb_silu(ctypes.byref(a), ctypes.byref(b), stream),
+            (x.owner, y.owner))
+
+    def silu_mul(self, x: TensorView, up: TensorView, out: TensorView,
+                 activated: Optional[TensorView] = None) -> int:
+        """Extension: out = silu(x) * up in one pass; `activated` receives silu(x) when given."""
+        try:
+            views = [x, up, out] + ([activated] if activated is not None else [])
+            for view in views:
+                self._check_view(view, "silu_mul")
+            a, b, c = x.as_abi(), up.as_abi(), out.as_abi()
+            d = activated.as_abi() if activated is not None else None
+        except BaseException as error:
+            return _exception_to_oid(error)
+        return self._submit(
+            lambda stream: self._lib.iomb_silu_mul(
+                ctypes.byref(a), ctypes.byref(b), ctypes.byref(d) if d is not None else None,
+                ctypes.byref(c), stream),
+            tuple(view.owner for view in views))
 
     def linear(self, *args, **kwargs) -> int:
         return OID_UNSUPPORTED

@@ -576,6 +576,87 @@ int iomo_cast(const iomo_view* source, const iomo_view* destination) {
     return 0;
 }
 
+/* ---- SiLU: src/shared/scalar_silu.hpp:66-101 ------------------------------- */
+
+/* scalar_silu_detail::evaluate on the FP32 carrier, the evaluation domain the CPU
+ * backend selects for every leaf below F64 (src/cpu/queue.cpp:1770-1774,1863-1868;
+ * the AVX-512 BF16 source runs the same FP32 operations, src/cpu/avx512_bf16_silu.cpp:147-176).
+ * exp is the C library's expf, as std::exp(float) is there. Every operation is
+ * rounded separately (this file is built with -ffp-contract=off). */
+static float silu_evaluate_f32(float x) {
+    if (isnan(x)) return NAN;
+    if (isinf(x)) return signbit(x) ? -0.0f : INFINITY;
+    if (x == 0.0f) return x;
+    if (x >= 0.0f) {
+        const float weight = expf(-x);
+        const float denominator = 1.0f + weight;
+        return x / denominator;
+    }
+    const float t = expf(x * 0.5f);
+    const float first = x * t;
+    const float numerator = first * t;
+    const float square = t * t;
+    const float denominator = 1.0f + square;
+    return numerator / denominator;
+}
+
+/* The same evaluator on the FP64 carrier of the reference's GPU backends
+ * (SiluFp64Traits, src/cuda/copy.cu:498-503). */
+static double silu_evaluate_f64(double x) {
+    if (isnan(x)) return NAN;
+    if (isinf(x)) return signbit(x) ? -0.0 : INFINITY;
+    if (x == 0.0) return x;
+    if (x >= 0.0) {
+        const double weight = exp(-x);
+        const double denominator = 1.0 + weight;
+        return x / denominator;
+    }
+    const double t = exp(x * 0.5);
+    const double first = x * t;
+    const double numerator = first * t;
+    const double square = t * t;
+    const double denominator = 1.0 + square;
+    return numerator / denominator;
+}
+
+/* scalar_silu: decode the leaf, evaluate on the carrier, one RNE encode.
+ * carrier 0: FP32 (CPU backend), 1: FP64 (GPU backends). */
+uint64_t iomo_scalar_silu(uint32_t dtype, uint64_t raw, int carrier) {
+    const format_t f = format_of(dtype);
+    if (!f.bits) return 0;
+    const long double value = codec_decode(raw, f);
+    if (carrier == 0) {
+        return codec_encode((long double)silu_evaluate_f32((float)value), f);
+    }
+    return codec_encode((long double)silu_evaluate_f64((double)value), f);
+}
+
+int iomo_silu(const iomo_view* x, const iomo_view* y, int carrier) {
+    geometry_t gx, gy;
+    if (geometry_of(x, &gx) || geometry_of(y, &gy)) return 1;
+    if (x->dtype != y->dtype || x->rank != y->rank) return 1;
+    for (uint32_t i = 0; i < x->rank; ++i) {
+        if (x->dims[i] != y->dims[i]) return 1;
+    }
+    if (x->base == y->base) return 1;                /* src/device_ops_neural.cpp:362-368 */
+    if (!format_of(x->dtype).bits) return 2;
+    if (carrier != 0 && carrier != 1) return 1;
+    const uint64_t planes = leading_count(x);
+    for (uint64_t index = 0; index < planes; ++index) {
+        const uint64_t xp = view_plane(x, index);
+        const uint64_t yp = view_plane(y, index);
+        for (uint64_t row = 0; row < gx.rows; ++row) {
+            for (uint64_t column = 0; column < gx.columns; ++column) {
+                const uint64_t raw = load_bits((const unsigned char*)x->base,
+                                               element_bit(x, &gx, xp, row, column), gx.bits);
+                store_bits((unsigned char*)y->base, element_bit(y, &gy, yp, row, column), gy.bits,
+                           iomo_scalar_silu(x->dtype, raw, carrier));
+            }
+        }
+    }
+    return 0;
+}
+
 /* ---- embedding: src/cpu/queue.cpp:941-1038 -------------------------------- */
 
 int iomo_embedding(const iomo_view* table, const iomo_view* indices,

@@ -52,6 +52,11 @@ int iomo_binary(int op, const iomo_view* lhs, const iomo_view* rhs,
  * (the reference's AVX-512 BF16 build); order 1: sequential recurrence. */
 int iomo_rmsnorm(const iomo_view* x, const iomo_view* scale, const iomo_view* out,
                  float eps, int order);
+/* SiLU (src/shared/scalar_silu.hpp:66-101). carrier 0: FP32 evaluation with the C
+ * library's expf (the reference CPU backend); carrier 1: FP64 evaluation (the
+ * reference's GPU backends, src/cuda/copy.cu:498-503). */
+uint64_t iomo_scalar_silu(uint32_t dtype, uint64_t raw, int carrier);
+int iomo_silu(const iomo_view* x, const iomo_view* y, int carrier);
 int iomo_copy(const iomo_view* source, const iomo_view* destination);
 int iomo_cast(const iomo_view* source, const iomo_view* destination);
 /* *status = 1 and nothing is written when any index is negative or >= V. */

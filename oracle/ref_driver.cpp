@@ -317,6 +317,10 @@ std::int64_t iomref_rmsnorm(
             view_of(x), view_of(scale), view_of(out), epsilon);
 }
 
+std::int64_t iomref_silu(void* queue, void* x, void* y) {
+    return ops_of(queue).silu(view_of(x), view_of(y));
+}
+
 std::int64_t iomref_copy(void* queue, void* source, void* destination) {
     return ops_of(queue).copy(view_of(source), view_of(destination));
 }
@@ -385,6 +389,11 @@ std::int64_t iomref_add_rmsnorm(void* queue, void* x, void* residual, void* scal
                                 void* out, float epsilon) {
     return iom::b200::add_rmsnorm(ops_of(queue), view_of(x), view_of(residual), view_of(scale),
                                   view_of(sum), view_of(out), epsilon);
+}
+
+std::int64_t iomref_silu_mul(void* queue, void* x, void* up, void* activated, void* out) {
+    return iom::b200::silu_mul(ops_of(queue), view_of(x), view_of(up),
+                               activated != nullptr ? &view_of(activated) : nullptr, view_of(out));
 }
 #endif
 

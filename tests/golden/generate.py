@@ -144,16 +144,38 @@ def mover_cases(ref, out):
     out["transfer_view"] = describe(view)
 
 
+def silu_cases(ref, out, tag):
+    """SiLU through the reference CPU backend (FP32 evaluation, expf of this host's
+    C library): every BF16 code, and a ragged multi-plane F32 case with specials."""
+    codes = np.arange(65536, dtype=np.uint16).reshape(256, 256)
+    x = owner(ref, (256, 256), DataType.BF16, codes)
+    y = owner(ref, (256, 256), DataType.BF16, np.zeros((256, 256), dtype=np.uint16))
+    assert ref.run(ref.lib.iomref_silu(ref.queue, x.view().handle, y.view().handle)) == 0, ref.error()
+    out[f"silu_{tag}_BF16_out"] = y.storage.copy()
+    rng = np.random.default_rng(4000)
+    payload = (random_payload(rng, (2, 17, 35), DataType.F32, "normal") * np.float32(6.0)).astype(np.float32)
+    flat = payload.reshape(-1).view(np.uint32)
+    flat[:SPECIAL_F32.size] = SPECIAL_F32
+    xf = owner(ref, (2, 17, 35), DataType.F32, payload)
+    yf = owner(ref, (2, 17, 35), DataType.F32, random_payload(rng, (2, 17, 35), DataType.F32))
+    out[f"silu_{tag}_F32_out_before"] = yf.storage.copy()
+    assert ref.run(ref.lib.iomref_silu(ref.queue, xf.view().handle, yf.view().handle)) == 0, ref.error()
+    out[f"silu_{tag}_F32_x"] = xf.storage.copy()
+    out[f"silu_{tag}_F32_out"] = yf.storage.copy()
+
+
 def main():
     fixtures = {}
     portable = Reference("portable")
     binary_cases(portable, fixtures)
     rmsnorm_cases(portable, fixtures, "portable")
     mover_cases(portable, fixtures)
+    silu_cases(portable, fixtures, "portable")
     portable.close()
     avx = Reference("avx512")
     assert avx.lib.iomref_avx512_bf16_active() == 1, "this host cannot run the AVX-512 BF16 build"
     rmsnorm_cases(avx, fixtures, "avx512")
+    silu_cases(avx, fixtures, "avx512")
     avx.close()
     np.savez_compressed(HERE / "reference_vectors.npz", **fixtures)
     print(f"wrote {len(fixtures)} arrays, "

@@ -58,6 +58,10 @@ def oracle() -> ctypes.CDLL:
         lib.iomo_rmsnorm.argtypes = [_VIEW, _VIEW, _VIEW, ctypes.c_float, ctypes.c_int]
         lib.iomo_copy.restype = ctypes.c_int
         lib.iomo_copy.argtypes = [_VIEW, _VIEW]
+        lib.iomo_silu.restype = ctypes.c_int
+        lib.iomo_silu.argtypes = [_VIEW, _VIEW, ctypes.c_int]
+        lib.iomo_scalar_silu.restype = ctypes.c_uint64
+        lib.iomo_scalar_silu.argtypes = [ctypes.c_uint32, ctypes.c_uint64, ctypes.c_int]
         lib.iomo_cast.restype = ctypes.c_int
         lib.iomo_cast.argtypes = [_VIEW, _VIEW]
         lib.iomo_embedding.restype = ctypes.c_int
@@ -191,6 +195,7 @@ class Reference:
             "iomref_binary": (ctypes.c_int64, [vp, ctypes.c_int, vp, vp, vp]),
             "iomref_rmsnorm": (ctypes.c_int64, [vp, vp, vp, vp, ctypes.c_float]),
             "iomref_copy": (ctypes.c_int64, [vp, vp, vp]),
+            "iomref_silu": (ctypes.c_int64, [vp, vp, vp]),
             "iomref_embedding": (ctypes.c_int64, [vp, vp, vp, vp]),
             "iomref_cache_append": (ctypes.c_int64, [vp, vp, vp, u64]),
             "iomref_wait": (ctypes.c_int, [vp, ctypes.c_int64]),
@@ -201,6 +206,7 @@ class Reference:
                 "iomref_tensor_upload": (ctypes.c_int, [vp, vp, u64]),
                 "iomref_tensor_download": (ctypes.c_int, [vp, vp, u64]),
                 "iomref_add_rmsnorm": (ctypes.c_int64, [vp, vp, vp, vp, vp, vp, ctypes.c_float]),
+                "iomref_silu_mul": (ctypes.c_int64, [vp, vp, vp, vp, vp]),
             })
         for name, (restype, argtypes) in spec.items():
             fn = getattr(lib, name)

@@ -119,3 +119,23 @@ def test_host_transfer_golden():
     view = view_from(host, GOLDEN["transfer_view"], 4)
     view.copy_from_host(GOLDEN["transfer_payload"])
     assert np.array_equal(host.storage, GOLDEN["transfer_after"])
+
+
+@pytest.mark.parametrize("build", ["portable", "avx512"])
+def test_silu_golden(build):
+    """Oracle (FP32 carrier) against the reference CPU backend's stored outputs:
+    every BF16 code, and a ragged F32 case with special values."""
+    codes = np.arange(65536, dtype=np.uint16).reshape(256, 256)
+    x = HostTensor((256, 256), DataType.BF16).poison(0xA5)
+    x.view().copy_from_host(codes)
+    y = HostTensor((256, 256), DataType.BF16).poison(0xA5)
+    y.view().copy_from_host(np.zeros((256, 256), dtype=np.uint16))
+    assert oracle().iomo_silu(abi(x.view()), abi(y.view()), 0) == 0
+    assert np.array_equal(y.storage, GOLDEN[f"silu_{build}_BF16_out"])
+    # the FP64 carrier of the reference's GPU backends agrees on every BF16 code
+    assert oracle().iomo_silu(abi(x.view()), abi(y.view()), 1) == 0
+    assert np.array_equal(y.storage, GOLDEN[f"silu_{build}_BF16_out"])
+    xf = host_from(GOLDEN[f"silu_{build}_F32_x"], (2, 17, 35), DataType.F32)
+    yf = host_from(GOLDEN[f"silu_{build}_F32_out_before"], (2, 17, 35), DataType.F32)
+    assert oracle().iomo_silu(abi(xf.view()), abi(yf.view()), 0) == 0
+    assert np.array_equal(yf.storage, GOLDEN[f"silu_{build}_F32_out"])

@@ -168,6 +168,46 @@ def test_copy_embedding_cache_append(pair):
         same(d)
 
 
+def test_silu_and_fused_gate(pair):
+    """SiLU behind the facade: BF16 equals the reference CPU backend on every code;
+    F32 stays within 4 ulp (FP64 against FP32 evaluation, as between the reference's
+    own GPU and CPU backends). The fused gate extension equals silu then mul."""
+    rng = np.random.default_rng(31)
+    codes = np.arange(65536, dtype=np.uint16).reshape(256, 256)
+    x = both(pair, (256, 256), DataType.BF16, rng, payload=codes)
+    y = both(pair, (256, 256), DataType.BF16, rng)
+    for i, ref in enumerate(pair):
+        assert ref.run(ref.lib.iomref_silu(ref.queue, x[i].view().handle, y[i].view().handle)) == 0, ref.error()
+    same(y)
+    xf = both(pair, (3, 17, 33), DataType.F32, rng, kind="normal")
+    yf = both(pair, (3, 17, 33), DataType.F32, rng)
+    for i, ref in enumerate(pair):
+        assert ref.run(ref.lib.iomref_silu(ref.queue, xf[i].view().handle, yf[i].view().handle)) == 0, ref.error()
+    a, b = (o.read().view(np.uint32).astype(np.int64) for o in yf)
+    assert np.abs(a - b).max() <= 4
+    cpu, gpu = pair
+    # rejections arrive unchanged: in place, and a leaf outside the SiLU set
+    assert gpu.lib.iomref_silu(gpu.queue, x[1].view().handle, x[1].view().handle) == -1
+    i32 = gpu.tensor((16, 16), DataType.I32)
+    j32 = gpu.tensor((16, 16), DataType.I32)
+    assert gpu.lib.iomref_silu(gpu.queue, i32.view().handle, j32.view().handle) == -2
+    # fused gate on the candidate equals its own silu followed by mul
+    up = gpu.tensor((256, 256), DataType.BF16)
+    up.view().from_host(random_payload(rng, (256, 256), DataType.BF16, "normal"))
+    act, out, out2 = (gpu.tensor((256, 256), DataType.BF16) for _ in range(3))
+    token = gpu.lib.iomref_silu_mul(gpu.queue, x[1].view().handle, up.view().handle,
+                                    act.view().handle, out.view().handle)
+    assert gpu.run(token) == 0, gpu.error()
+    assert gpu.run(gpu.lib.iomref_binary(gpu.queue, 1, y[1].view().handle, up.view().handle,
+                                         out2.view().handle)) == 0
+    assert np.array_equal(act.read(), y[1].read())
+    assert np.array_equal(out.read(), out2.read())
+    token = gpu.lib.iomref_silu_mul(gpu.queue, x[1].view().handle, up.view().handle, None,
+                                    out.view().handle)
+    assert gpu.run(token) == 0, gpu.error()
+    assert np.array_equal(out.read(), out2.read())
+
+
 def test_host_transfers_and_fused_extension(pair):
     cpu, gpu = pair
     rng = np.random.default_rng(10)

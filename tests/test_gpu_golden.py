@@ -6,6 +6,7 @@ import pytest
 from iom_b200.device import RMS_LANES16, RMS_SEQUENTIAL
 from iom_b200.tensor import DataType
 from gpu_support import download, gpu, like, run, upload  # noqa: F401
+from support import HostTensor
 from test_golden import GOLDEN, host_from, split_shapes, view_from
 
 pytestmark = pytest.mark.gpu
@@ -71,3 +72,28 @@ def test_movers_golden_gpu(gpu):
     staging = device.create_workspace(GOLDEN["transfer_payload"].nbytes + 32)
     view.copy_from_host(GOLDEN["transfer_payload"], staging.view())
     assert np.array_equal(download(dev), GOLDEN["transfer_after"])
+
+
+def test_silu_golden_gpu(gpu):
+    """The CUDA path against the reference CPU backend's stored outputs: BF16 bit for
+    bit on every code; F32 within 4 ulp (the kernel evaluates on the FP64 carrier of
+    the reference's GPU backends, the stored outputs come from its FP32 CPU carrier)."""
+    device, queue = gpu
+    codes = np.arange(65536, dtype=np.uint16).reshape(256, 256)
+    x = HostTensor((256, 256), DataType.BF16).poison(0xA5)
+    x.view().copy_from_host(codes)
+    y = HostTensor((256, 256), DataType.BF16).poison(0xA5)
+    y.view().copy_from_host(np.zeros((256, 256), dtype=np.uint16))
+    dx, dy = upload(device, x), upload(device, y)
+    run(queue, queue.silu(dx.view(), dy.view()))
+    assert np.array_equal(download(dy), GOLDEN["silu_portable_BF16_out"])
+    assert np.array_equal(download(dy), GOLDEN["silu_avx512_BF16_out"])
+    xf = upload(device, host_from(GOLDEN["silu_portable_F32_x"], (2, 17, 35), DataType.F32))
+    yf = upload(device, host_from(GOLDEN["silu_portable_F32_out_before"], (2, 17, 35), DataType.F32))
+    run(queue, queue.silu(xf.view(), yf.view()))
+    got = download(yf).view(np.uint32).astype(np.int64)
+    want = GOLDEN["silu_portable_F32_out"].view(np.uint32).astype(np.int64)
+    assert np.abs(got - want).max() <= 4
+    before = GOLDEN["silu_portable_F32_out_before"].view(np.uint32).astype(np.int64)
+    untouched = want == before        # padding and nothing else (payloads are random)
+    assert np.array_equal(got[untouched], want[untouched])

@@ -174,6 +174,39 @@ def test_copy_matches_reference(ref, dtype):
     assert np.array_equal(dst.storage, rdst.storage)
 
 
+def test_silu_every_bf16_code_matches_reference(ref):
+    """All 65 536 BF16 codes through the reference CPU backend's SiLU (portable and
+    AVX-512 builds run the same FP32 evaluation) against the oracle's FP32 carrier."""
+    codes = np.arange(65536, dtype=np.uint16).reshape(256, 256)
+    x, rx = mirror(ref, (256, 256), DataType.BF16, np.random.default_rng(1), payload=codes)
+    y, ry = mirror(ref, (256, 256), DataType.BF16, np.random.default_rng(2))
+    assert ref.run(ref.lib.iomref_silu(ref.queue, rx.view().handle, ry.view().handle)) == 0, ref.error()
+    assert oracle().iomo_silu(abi(x.view()), abi(y.view()), 0) == 0
+    assert np.array_equal(y.storage, ry.storage)
+
+
+@pytest.mark.parametrize("dtype", [DataType.F32, DataType.BF16, DataType.F16])
+def test_silu_views_and_ragged_extents_match_reference(ref, dtype):
+    rng = np.random.default_rng(21)
+    payload = random_payload(rng, (3, 2, 17, 33), dtype, "normal") if dtype != DataType.F16 \
+        else rng.integers(0, 1 << 16, size=(3, 2, 17, 33), dtype=np.uint16)
+    if dtype == DataType.F32:
+        payload = (payload * np.float32(6.0)).astype(np.float32)
+        flat = payload.reshape(-1).view(np.uint32)
+        flat[:SPECIAL_F32.size] = SPECIAL_F32
+        flat[100:104] = np.array([-90.0, -104.0, 88.0, -0.0], dtype=np.float32).view(np.uint32)
+    x, rx = mirror(ref, (3, 2, 17, 33), dtype, rng, payload=payload)
+    y, ry = mirror(ref, (2, 3, 17, 33), dtype, rng)
+    xv, rxv = apply(x.view(), rx.view(), [("permute", ([1, 0],))])
+    yv, ryv = y.view(), ry.view()
+    assert ref.run(ref.lib.iomref_silu(ref.queue, rxv.handle, ryv.handle)) == 0, ref.error()
+    assert oracle().iomo_silu(abi(xv), abi(yv), 0) == 0
+    assert np.array_equal(y.storage, ry.storage)
+    # in-place and cross-shape requests are rejected by the reference; the oracle agrees
+    assert ref.lib.iomref_silu(ref.queue, rx.view().handle, rx.view().handle) == -1
+    assert oracle().iomo_silu(abi(x.view()), abi(x.view()), 0) == 1
+
+
 @pytest.mark.parametrize("index_dtype", [DataType.U32, DataType.I64, DataType.U8, DataType.I16])
 def test_embedding_matches_reference(ref, index_dtype):
     rng = np.random.default_rng(13)
