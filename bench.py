@@ -503,6 +503,56 @@ def ops_table(device, queue, only=None, iters: int = 10) -> dict:
                "[64,32000] BF16 -> F32", inner=12)
         ws.close()
         release()
+    if only is None or only in ("decode_step_eager", "decode_step_graph"):
+        # One decode step's tensor-op traffic, TinyLlama geometry, 64 sequences, 22 layers:
+        # embedding, then per layer norm / K,V appends / residual add + norm / gate / residual
+        # add, then the final norm: 156 launches of microsecond-scale kernels. Eager: one
+        # submission per launch through the host layer; graph: the whole step recorded once
+        # (B200Queue.capture) and replayed as a single CUDA graph launch.
+        batch, hidden, inter, layers, heads = 64, 2048, 5632, 22, 4
+        table = tensor((32000, hidden), DataType.BF16)
+        ids = device.create_tensor(TensorSpec((1, batch), DataType.U32))
+        made.append(ids)
+        ids.storage().zero_()
+        h, normed, attn, total = (tensor((batch, hidden), DataType.BF16) for _ in range(4))
+        w = tensor((1, hidden), DataType.BF16)
+        gate, up, prod = (tensor((batch, inter), DataType.BF16) for _ in range(3))
+        k, v = tensor((batch, heads, 1, 64), DataType.BF16), tensor((batch, heads, 1, 64), DataType.BF16)
+        k_cache = tensor((batch, heads, 512, 64), DataType.BF16)
+        v_cache = tensor((batch, heads, 512, 64), DataType.BF16)
+        positions = torch.randint(0, 511, (batch,), device=device.torch_device, dtype=torch.int32)
+        status = torch.zeros(8, device=device.torch_device, dtype=torch.int32)
+        ws = device.create_workspace(32)
+
+        def step():
+            token = ok(queue.embedding(table.view(), ids.view(), h.view(), ws.view()))
+            for _ in range(layers):
+                queue.rmsnorm(h.view(), w.view(), normed.view(), 1e-5)
+                queue.cache_append_batched(k.view(), k_cache.view(), positions.data_ptr(),
+                                           status.data_ptr())
+                queue.cache_append_batched(v.view(), v_cache.view(), positions.data_ptr(),
+                                           status.data_ptr())
+                queue.add_rmsnorm(h.view(), attn.view(), w.view(), total.view(), normed.view(), 1e-5)
+                queue.silu_mul(gate.view(), up.view(), prod.view())
+                token = queue.add(total.view(), attn.view(), h.view())
+            if token != OID_CAPTURED:
+                ok(token)
+            return queue.rmsnorm(h.view(), w.view(), normed.view(), 1e-5)
+
+        from iom_b200.device import OID_CAPTURED
+        launches = 2 + layers * 6
+        moved = (2 * batch * hidden * 2) + layers * (
+            2 * batch * hidden * 2 + 2 * 2 * batch * heads * 64 * 2 + 4 * batch * hidden * 2
+            + 3 * batch * inter * 2 + 3 * batch * hidden * 2) + 2 * batch * hidden * 2
+        record("decode_step_eager", moved, lambda: ok(step()), f"{launches} launches, one submission each")
+        if only is None or only == "decode_step_graph":
+            queue.wait(ok(step()))
+            with queue.capture() as recorded:
+                step()
+            record("decode_step_graph", moved, lambda: ok(recorded.replay()),
+                   f"{launches} launches, one graph replay")
+        ws.close()
+        release()
     return results
 
 

@@ -46,6 +46,9 @@ Operand make_operand(const iomb_view& view, const ViewFacts& facts,
                      const uint64_t* aligned_strides, const Leading& leading,
                      bool bc_rows, bool bc_cols);
 
+// Streaming multiprocessors of the current device (0 when it cannot be read).
+int sm_count();
+
 // Grid size for grid-stride kernels: enough CTAs to fill every SM
 // `ctas_per_sm` times, never more than `work_items`.
 unsigned grid_for(uint64_t work_items, unsigned ctas_per_sm);

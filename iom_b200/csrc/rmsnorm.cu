@@ -506,6 +506,13 @@ static int rms_dispatch(const iomb_view* x, const iomb_view* residual, const iom
     const uint32_t operands = fused ? 2 : 1;
     uint32_t g = kTile;
     while (g > 1 && static_cast<uint64_t>(operands) * g * row_bytes > kUnitCapBytes) g /= 2;
+    // Few rows (decode steps): smaller groups spread the bands over more CTAs; the
+    // per-row work is the same, the per-CTA copy shrinks.
+    {
+        const uint64_t bands = fx.tile_rows * fx.planes;
+        const uint64_t wanted = 2 * static_cast<uint64_t>(sm_count() > 0 ? sm_count() : 148);
+        while (g > 1 && bands * (kTile / g) < wanted) g /= 2;
+    }
     const uint64_t staged_bytes = static_cast<uint64_t>(operands) * g * row_bytes;
     if (staged_bytes > 160 * 1024) {
         return fail(IOMB_ERR_UNSUPPORTED, "rmsnorm: feature extent exceeds the staging capacity");

@@ -37,6 +37,9 @@ RMS_LANES16, RMS_SEQUENTIAL = 0, 1
 _ALIGNMENT = 256          # arena suballocation granularity (the contract needs 32)
 _MAX_QUEUES = 4           # src/device_ops.cpp:210-218
 _SEQUENCE_BITS = 55       # token = (queue_id << 55) | sequence
+# Returned by operations issued while a queue records a CapturedSequence: accepted,
+# but completed (and waited for) only through the replay's own token.
+OID_CAPTURED = (1 << 62) - 1
 
 
 class UnsupportedOperation(Exception):
@@ -361,6 +364,105 @@ def make_b200_device(ordinal: int, memory: DeviceMemoryConfig,
     return B200Device(ordinal, memory, queue_config)
 
 
+class CapturedSequence:
+    """A run of queue operations recorded once and replayed as one CUDA graph launch:
+    the launch-bound inner loop of a decode step (embedding, norms, cache appends,
+    gate) costs one submission instead of one per kernel.
+
+        with queue.capture() as step:
+            queue.embedding(...); queue.rmsnorm(...); queue.cache_append_batched(...)
+        token = step.replay()        # an ordinary token of the queue
+        queue.wait(token)
+    """
+
+    def __init__(self, queue: "B200Queue"):
+        self._queue = queue
+        self._graph = torch.cuda.CUDAGraph()
+        self._context = None
+        self._owners = []
+        self._status_cells = []
+        self._rejected = []
+        self._operations = 0
+        self._ready = False
+        # Pinned status cells are reserved before the capture starts (pinning memory
+        # is not a capturable call): one per status-bearing operation.
+        self._cell_pool = torch.zeros(self.MAX_STATUS_OPERATIONS, dtype=torch.int32).pin_memory()
+        # The queue keeps every sequence alive until close(): a graph or pinned cell
+        # released by the garbage collector while another sequence is being recorded
+        # would invalidate that capture.
+        queue._sequences.append(self)
+
+    MAX_STATUS_OPERATIONS = 64
+
+    def _take_cell(self):
+        index = len(self._status_cells)
+        if index >= self.MAX_STATUS_OPERATIONS:
+            raise ValueError("a captured sequence holds at most 64 status-bearing operations")
+        cell = self._cell_pool[index:index + 1]
+        self._status_cells.append(cell)
+        return cell
+
+    def __enter__(self) -> "CapturedSequence":
+        queue = self._queue
+        queue._stream.synchronize()
+        queue._capture = self
+        # Only this thread's unsafe calls invalidate the capture (other threads may
+        # allocate freely meanwhile).
+        self._context = torch.cuda.graph(self._graph, stream=queue._stream,
+                                         capture_error_mode="thread_local")
+        try:
+            self._context.__enter__()
+        except BaseException:
+            queue._capture = None
+            raise
+        return self
+
+    def __exit__(self, kind, value, trace) -> bool:
+        queue = self._queue
+        try:
+            self._context.__exit__(kind, value, trace)
+        finally:
+            queue._capture = None
+        if kind is None:
+            if self._rejected:
+                raise self._rejected[0]
+            self._ready = True
+        return False
+
+    @property
+    def operations(self) -> int:
+        return self._operations
+
+    def close(self) -> None:
+        """Releases the graph; not while the queue is recording."""
+        queue = self._queue
+        if queue._capture is not None:
+            raise RuntimeError("a sequence cannot be released while the queue records another")
+        queue._stream.synchronize()
+        self._ready = False
+        if self in queue._sequences:
+            queue._sequences.remove(self)
+
+    def replay(self) -> int:
+        """Launches the recorded graph on the queue's stream; returns a token."""
+        if not self._ready:
+            raise RuntimeError("the sequence was not recorded successfully")
+        queue = self._queue
+        if queue._capture is not None:
+            raise RuntimeError("a sequence cannot be replayed while the queue records another")
+
+        def launch(_stream):
+            with torch.cuda.stream(queue._stream):
+                self._graph.replay()
+            return 0
+        token = queue._submit(launch, tuple(self._owners))
+        if token > 0 and self._status_cells:
+            sequence = token & ((1 << _SEQUENCE_BITS) - 1)
+            event, owners, _ = queue._records[sequence]
+            queue._records[sequence] = (event, owners, self._status_cells)
+        return token
+
+
 class B200Queue:
     """DeviceOps: one in-order asynchronous queue = one CUDA stream."""
 
@@ -374,6 +476,8 @@ class B200Queue:
         self._failures = {}       # sequence -> exception
         self._completed = 0
         self._closed = False
+        self._capture = None      # the CapturedSequence being recorded, if any
+        self._sequences = []      # every recorded sequence, kept alive until closed
         # Queue-owned pinned cells for status read-backs, one per in-flight credit
         # (the reference keeps one pinned cell per queue, src/cuda/device.cpp:165-200).
         self._status_cells = torch.zeros(device.queue_config.max_in_flight_per_queue,
@@ -392,6 +496,7 @@ class B200Queue:
             self._closed = True
             self._stream.synchronize()
             self._records.clear()
+            self._sequences.clear()
             with self._device._lock:
                 self._device._live_queues -= 1
 
@@ -418,10 +523,14 @@ class B200Queue:
             return
         event, _owners, status_cell = record
         event.synchronize()
-        if status_cell is not None and int(status_cell.item()) != 0:
+        cells = status_cell if isinstance(status_cell, list) else \
+            ([] if status_cell is None else [status_cell])
+        if any(int(cell.item()) != 0 for cell in cells):
             self._failures[sequence] = ValueError("embedding index is negative or out of range")
 
     def _submit(self, launch, owners, status_cell=None) -> int:
+        if self._capture is not None:
+            return self._submit_captured(launch, owners, status_cell)
         try:
             self._retire(self._device.queue_config.max_in_flight_per_queue)
             with torch.cuda.device(self._device.torch_device):
@@ -444,8 +553,41 @@ class B200Queue:
         except BaseException as error:  # the facade is noexcept: map to an oid
             return _exception_to_oid(error)
 
+    # -- CUDA graph capture ---------------------------------------------------
+    def _submit_captured(self, launch, owners, status_cell) -> int:
+        """One operation inside capture(): the launch is recorded into the graph; no
+        event, no sequence number. Status words are copied to a pinned cell of the
+        sequence by a captured copy and checked after every replay."""
+        try:
+            with torch.cuda.device(self._device.torch_device):
+                status = launch(self._stream.cuda_stream)
+                if status != 0:
+                    raise _status_to_exception(status)
+                if status_cell is not None:
+                    pinned = self._capture._take_cell()
+                    pinned.copy_(status_cell, non_blocking=True)
+            self._capture._owners.extend(owners)
+            self._capture._operations += 1
+            return OID_CAPTURED
+        except BaseException as error:
+            self._capture._rejected.append(error)
+            return _exception_to_oid(error)
+
+    def capture(self) -> "CapturedSequence":
+        """Context manager: records the operations issued on this queue inside the
+        block into one CUDA graph instead of running them. The C ABI entry points
+        neither allocate nor synchronise, so they are capture-safe as they are;
+        run the same sequence once eagerly first (one-time set-up such as the SiLU
+        table build does synchronise). The views' storage is baked into the graph:
+        replays read whatever the same tensors hold at that time."""
+        if self._capture is not None:
+            raise RuntimeError("this queue is already recording a sequence")
+        return CapturedSequence(self)
+
     def wait(self, token: int) -> None:
         """DeviceOps::wait (src/device_ops.cpp:536-568)."""
+        if token == OID_CAPTURED:
+            raise ValueError("a captured operation completes with its sequence's replay token")
         if token <= 0 or (token >> _SEQUENCE_BITS) != self._queue_id:
             raise ValueError("wait token is not an accepted token of this queue")
         sequence = token & ((1 << _SEQUENCE_BITS) - 1)
