@@ -252,11 +252,32 @@ rmsnorm_kernel(const RmsParams p) {
     // fits) and note whether every logical scale value is finite.
     if (tid == 0) scale_not_finite = 0;
     __syncthreads();
-    for (uint32_t c = tid; c < p.tile_cols * kTile; c += kRmsThreads) {
-        const float w = decode_element<ELEM>(
-                p.scale_row + static_cast<size_t>(c / kTile) * kTileBytes + (c % kTile) * ELEM);
-        if constexpr (SCALE_SMEM) scale[c] = w;
-        if (c < p.cols && !(fabsf(w) <= 3.402823466e+38f)) scale_not_finite = 1;
+    // One 16-byte vector of row 0 of a scale tile per step (2 or 4 vectors per tile).
+    for (uint32_t k = tid; k < p.tile_cols * kVectorsPerRow; k += kRmsThreads) {
+        const uint32_t tile = k / kVectorsPerRow, part = k % kVectorsPerRow;
+        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(
+                p.scale_row + static_cast<size_t>(tile) * kTileBytes + part * 16));
+        float w[kPerVector];
+        if constexpr (ELEM == 2) {
+            w[0] = bf16_lo(raw.x); w[1] = bf16_hi(raw.x); w[2] = bf16_lo(raw.y); w[3] = bf16_hi(raw.y);
+            w[4] = bf16_lo(raw.z); w[5] = bf16_hi(raw.z); w[6] = bf16_lo(raw.w); w[7] = bf16_hi(raw.w);
+        } else {
+            w[0] = __uint_as_float(raw.x); w[1] = __uint_as_float(raw.y);
+            w[2] = __uint_as_float(raw.z); w[3] = __uint_as_float(raw.w);
+        }
+        const uint32_t first = tile * kTile + part * kPerVector;
+        bool finite = true;
+#pragma unroll
+        for (uint32_t e = 0; e < kPerVector; ++e) {
+            // Padding columns of the last tile are not part of the scale.
+            if (first + e < p.cols && !(fabsf(w[e]) <= 3.402823466e+38f)) finite = false;
+        }
+        if constexpr (SCALE_SMEM) {
+            float4* target = reinterpret_cast<float4*>(scale + first);
+            target[0] = make_float4(w[0], w[1], w[2], w[3]);
+            if constexpr (ELEM == 2) target[1] = make_float4(w[4], w[5], w[6], w[7]);
+        }
+        if (!finite) scale_not_finite = 1;
     }
     __syncthreads();
     const bool scale_finite = scale_not_finite == 0;
