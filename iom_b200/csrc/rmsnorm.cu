@@ -208,12 +208,22 @@ rmsnorm_kernel(const RmsParams p) {
         uint64_t index;
         bool valid;
     };
+    // 16 / G groups per band is a power of two; the band arithmetic is 32-bit
+    // whenever the band count allows (64-bit division costs a hundred instructions
+    // on every CTA's critical path).
+    constexpr uint32_t kGroupsPerBand = kTile / G;
     auto locate = [&](uint64_t u) {
         Unit unit_at;
-        const uint32_t group = static_cast<uint32_t>(u % p.groups_per_band);
-        const uint64_t band = u / p.groups_per_band;
-        unit_at.tr = static_cast<uint32_t>(band % p.tile_rows);
-        unit_at.index = band / p.tile_rows;
+        const uint32_t group = static_cast<uint32_t>(u % kGroupsPerBand);
+        const uint64_t band = u / kGroupsPerBand;
+        if (band <= 0xFFFFFFFFull) {
+            const uint32_t band32 = static_cast<uint32_t>(band);
+            unit_at.tr = band32 % p.tile_rows;
+            unit_at.index = band32 / p.tile_rows;
+        } else {
+            unit_at.tr = static_cast<uint32_t>(band % p.tile_rows);
+            unit_at.index = band / p.tile_rows;
+        }
         unit_at.row0 = group * G;
         unit_at.rows_in_band = min(kTile, p.rows - unit_at.tr * kTile);
         unit_at.valid = unit_at.row0 < unit_at.rows_in_band;     // uniform per CTA
