@@ -160,7 +160,8 @@ def run_ours(args) -> dict:
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
-    arena = max(5 * PLANES * ROWS * HIDDEN * ELEM + (64 << 20), 0 if args.no_ops else 5 << 30)
+    arena = max(5 * PLANES * ROWS * HIDDEN * ELEM + 7 * ROWS * HIDDEN * ELEM + (64 << 20),
+                0 if args.no_ops else 5 << 30)
     device = make_b200_device(local_rank, DeviceMemoryConfig(arena // 32 * 32))
     queue = device.create_ops()
     shape = (PLANES, ROWS, HIDDEN)
@@ -220,13 +221,52 @@ def run_ours(args) -> dict:
         queue.wait(step())
         out.view().copy_to_host(out_host.numpy(), staging.view())
 
+    # The same step with the asynchronous transfer operations: the batch goes plane by
+    # plane through two queues (streams), so that one queue's device-to-host copy
+    # runs while the other's host-to-device copies do (both PCIe directions busy).
+    plane_bytes = ROWS * HIDDEN * ELEM
+    lanes = []
+
+    def e2e_pipelined_step():
+        if not lanes:
+            for q in (queue, device.create_ops()):
+                lanes.append((q, [device.create_workspace(plane_bytes + 64) for _ in range(3)]))
+        tokens = [None, None]
+        for plane in range(PLANES):
+            q, (sx, sr, so) = lanes[plane % 2]
+            chunk = slice(plane * ROWS * HIDDEN, (plane + 1) * ROWS * HIDDEN)
+            xv, rv = x.view().select(0, plane), r.view().select(0, plane)
+            tv, ov = total.view().select(0, plane), out.view().select(0, plane)
+            for token in (q.upload(xv, pinned["x"].numpy()[chunk], sx.view()),
+                          q.upload(rv, pinned["r"].numpy()[chunk], sr.view()),
+                          q.add_rmsnorm(xv, rv, scale.view(), tv, ov, EPS)):
+                if token <= 0:
+                    raise RuntimeError(f"pipelined step rejected with oid {token}")
+            tokens[plane % 2] = q.download(ov, out_host.numpy()[chunk], so.view())
+            if tokens[plane % 2] <= 0:
+                raise RuntimeError(f"download rejected with oid {tokens[plane % 2]}")
+        for (q, _), token in zip(lanes, tokens):
+            q.wait(token)
+
     e2e_ms = float("nan")
+    e2e_sync_ms = float("nan")
     if not args.no_e2e:
         e2e_step()
         barrier()
         t0 = time.perf_counter()
         for _ in range(e2e_steps):
             e2e_step()
+        torch.cuda.synchronize()
+        e2e_sync_ms = (time.perf_counter() - t0) * 1e3
+        reference_out = out_host.clone()
+        out_host.zero_()
+        e2e_pipelined_step()
+        barrier()
+        if not torch.equal(reference_out, out_host):
+            raise RuntimeError("pipelined end-to-end step and synchronous step disagree")
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            e2e_pipelined_step()
         torch.cuda.synchronize()
         e2e_ms = (time.perf_counter() - t0) * 1e3
 
@@ -298,7 +338,11 @@ def run_ours(args) -> dict:
             "e2e": {"value": world * ALGORITHMIC_BYTES * e2e_steps / e2e_ms / 1e6, "unit": "GB/s",
                     "h2d_bytes_per_step": 2 * logical_bytes, "d2h_bytes_per_step": logical_bytes,
                     "steps": e2e_steps,
-                    "path": "copy_from_host(x), copy_from_host(r), add_rmsnorm, copy_to_host(out)"},
+                    "path": "per plane, alternating over two queues: upload(x), upload(r), "
+                            "add_rmsnorm, download(out); pinned host buffers in the logical layout",
+                    "synchronous_value": world * ALGORITHMIC_BYTES * e2e_steps / e2e_sync_ms / 1e6,
+                    "synchronous_path": "copy_from_host(x), copy_from_host(r), add_rmsnorm, "
+                                        "copy_to_host(out)"},
             "gpu_launches": args.steps,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES_PER_PLANE * PLANES,
@@ -459,6 +503,15 @@ def ops_table(device, queue, only=None, iters: int = 10) -> dict:
         gf, af = tensor((rows // 2, inter), DataType.F32), tensor((rows // 2, inter), DataType.F32)
         record("silu_f32", 2 * (count // 2) * 4, lambda: ok(queue.silu(gf.view(), af.view())),
                f"[{rows // 2},{inter}]")
+        release()
+    if only is None or only in ("rope_bf16",):
+        # Rotary embedding of Q at prefill, TinyLlama geometry: 32 heads x 64, 8192 positions,
+        # 16 sequences: 537 MB per tensor; the 2 MiB angle table stays in L2.
+        shape = (16, 32, 8192, 64)
+        count = 16 * 32 * 8192 * 64
+        q_in, q_out = tensor(shape, DataType.BF16), tensor(shape, DataType.BF16)
+        record("rope_bf16", 2 * count * 2, lambda: ok(queue.rope(q_in.view(), q_out.view(), 0, 10000.0)),
+               str(list(shape)))
         release()
     if only is None or only in ("embedding_decode", "cache_append_decode_batched",
                                 "cache_append_decode_64calls", "cast_logits"):

@@ -190,6 +190,33 @@ int iomb_silu_mul(const iomb_view* x, const iomb_view* up, const iomb_view* acti
                   const iomb_view* out, void* stream);
 
 /*
+ * Fills the rotary angle table on the HOST: for r in [0, rows) and c in [0, width/2),
+ * cos_sin[(r * width/2 + c) * 2 + {0,1}] = {cos, sin} of
+ * float(first_position + r) * powf(float(theta), float(-2c / width)),
+ * the expression of rope_angle (src/cpu/queue.cpp:1356-1367) with the C library's
+ * powf / sinf / cosf, which is what fixes the reference CPU backend's bits. No device
+ * work. The caller keeps the table in device memory (a rotary cache) for iomb_rope.
+ */
+int iomb_rope_angles(float* cos_sin, uint64_t first_position, uint64_t rows, uint64_t width,
+                     double theta);
+
+/*
+ * Split-half rotary embedding: x, out are [..., H, R, W] (rank 3..8, W even); row r sits
+ * at position a + r; (out[c], out[c + W/2]) = rotation of (x[c], x[c + W/2]) by the
+ * angle of (position, c); a row at position 0 is copied raw.
+ * Replaces GpuQueue::rope_impl + src/shared/standard_tiled_rope.inl:83-624; admission rules
+ * of validate_rope (src/device_ops_neural.cpp:169-197,241-360: equal shapes, even width,
+ * a + R - 1 < 2^24, the output shares neither an owner nor a byte with the input);
+ * arithmetic of rope_pair (src/cpu/queue.cpp:1369-1411): four separately rounded FP32
+ * products, one subtraction, one addition, one RNE encode each, canonical NaN.
+ * `cos_sin` is the DEVICE copy of iomb_rope_angles(first_position = a, rows >= R, W, theta)
+ * (or a pointer to row a of a longer table). Leaves: BF16, F32. With the table built on
+ * the same host, results are bit-identical to the reference CPU backend.
+ */
+int iomb_rope(const iomb_view* x, const iomb_view* out, uint64_t a, const float* cos_sin,
+              void* stream);
+
+/*
  * out[b, r, f] = table[indices[b, 0, r], f] (raw bits).
  * Replaces GpuQueue::embedding_impl + embedding_word_kernel and its status protocol
  * (src/shared/standard_tiled_embedding.inl:117-199; src/shared/gpu_queue_operations.inl:870-919;

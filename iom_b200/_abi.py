@@ -45,6 +45,9 @@ PROTOTYPES = {
                                         ctypes.c_int, ctypes.c_void_p]),
     "iomb_copy": (ctypes.c_int, [_VIEW, _VIEW, ctypes.c_void_p]),
     "iomb_cast": (ctypes.c_int, [_VIEW, _VIEW, ctypes.c_void_p]),
+    "iomb_rope_angles": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_uint64, ctypes.c_uint64,
+                                        ctypes.c_uint64, ctypes.c_double]),
+    "iomb_rope": (ctypes.c_int, [_VIEW, _VIEW, ctypes.c_uint64, ctypes.c_void_p, ctypes.c_void_p]),
     "iomb_silu": (ctypes.c_int, [_VIEW, _VIEW, ctypes.c_void_p]),
     "iomb_silu_mul": (ctypes.c_int, [_VIEW, _VIEW, _VIEW, _VIEW, ctypes.c_void_p]),
     "iomb_embedding": (ctypes.c_int, [_VIEW, _VIEW, _VIEW, ctypes.c_void_p, ctypes.c_void_p]),

@@ -161,6 +161,7 @@ public:
 
     ~B200Device() override {
         if (transfer_stream_ != nullptr) (void)cudaStreamDestroy(transfer_stream_);
+        for (const RopeTable& table : rope_tables_) (void)cudaFree(table.device);
         allocator_.reset();
         if (arena_ != nullptr) (void)cudaFree(arena_);
     }
@@ -191,6 +192,39 @@ public:
     [[nodiscard]] cudaStream_t transfer_stream() const noexcept { return transfer_stream_; }
     [[nodiscard]] std::mutex& transfer_mutex() noexcept { return transfer_mutex_; }
 
+    // Rotary cache: device table of (cos, sin) for positions 0 .. rows-1 of one
+    // (theta, width), built on the host by iomb_rope_angles and grown by doubling.
+    // Tables live outside the tensor arena and until the device goes away, because
+    // queued work may still read a table that a longer one has replaced.
+    [[nodiscard]] const float* rope_table(double theta, std::size_t width, std::size_t positions) {
+        std::lock_guard<std::mutex> lock(rope_mutex_);
+        const float narrowed = static_cast<float>(theta);
+        std::uint32_t theta_bits = 0;
+        std::memcpy(&theta_bits, &narrowed, sizeof theta_bits);
+        for (const RopeTable& table : rope_tables_) {
+            if (table.theta_bits == theta_bits && table.width == width && table.rows >= positions) {
+                return table.device;
+            }
+        }
+        std::size_t rows = 256;
+        while (rows < positions) rows *= 2;
+        const std::size_t count = rows * (width / 2) * 2;
+        std::vector<float> host(count);
+        check_status(iomb_rope_angles(host.data(), 0, rows, width, theta));
+        activate();
+        void* allocation = nullptr;
+        check_cuda("cudaMalloc(rope table)", cudaMalloc(&allocation, count * sizeof(float)));
+        float* device = static_cast<float*>(allocation);
+        const cudaError_t copied = cudaMemcpy(device, host.data(), count * sizeof(float),
+                                              cudaMemcpyHostToDevice);
+        if (copied != cudaSuccess) {
+            (void)cudaFree(device);
+            check_cuda("cudaMemcpy(rope table)", copied);
+        }
+        rope_tables_.push_back(RopeTable{theta_bits, width, rows, device});
+        return device;
+    }
+
     [[nodiscard]] std::unique_ptr<Tensor> create_tensor(const TensorSpec& spec) override;
     [[nodiscard]] std::unique_ptr<RawWorkspace> create_workspace(std::size_t bytes) override {
         if (bytes == 0) return std::make_unique<B200Workspace>(*this, nullptr, 0);
@@ -213,6 +247,14 @@ private:
     cudaStream_t transfer_stream_ = nullptr;
     std::mutex transfer_mutex_;
     detail::RegistryState registry_state_;
+    struct RopeTable {
+        std::uint32_t theta_bits;
+        std::size_t width;
+        std::size_t rows;
+        float* device;
+    };
+    std::vector<RopeTable> rope_tables_;
+    std::mutex rope_mutex_;
 };
 
 B200Workspace::B200Workspace(B200Device& device, void* address, std::size_t bytes)
@@ -571,6 +613,32 @@ protected:
                     launch_three_owner(sequence, entries, {}, [&] {
                         const iomb_view x = to_view_fixed(captured.x), y = to_view_fixed(captured.y);
                         check_status(iomb_silu(&x, &y, stream_));
+                    });
+                });
+    }
+
+    [[nodiscard]] WorkspaceRequirements rope_workspace_requirements(
+            const RopeRequest& request) override {
+        if (request.x.data_type != DataType::BF16 && request.x.data_type != DataType::F32) {
+            throw detail::UnsupportedOperation();
+        }
+        return {0, 1};
+    }
+
+    oid rope_impl(const RopeRequest& request) override {
+        // The table covers positions 0 .. a + R - 1; row a is where this request starts.
+        const std::size_t rows = request.x.dimensions[request.x.rank - 2];
+        const std::size_t width = request.x.dimensions[request.x.rank - 1];
+        const float* table = device_->rope_table(request.theta, width, request.a + rows);
+        const float* first = table + request.a * (width / 2) * 2;
+        std::lock_guard<std::mutex> order(submission_order_mutex_);
+        return submit_rope(
+                request, device_->registry_state(), registry_queue_id_, fence(),
+                [this, first](std::uint64_t sequence, const RopeRequest& captured,
+                              detail::BinaryEntryRegistration entries) {
+                    launch_three_owner(sequence, entries, {}, [&] {
+                        const iomb_view x = to_view_fixed(captured.x), out = to_view_fixed(captured.out);
+                        check_status(iomb_rope(&x, &out, captured.a, first, stream_));
                     });
                 });
     }

@@ -328,6 +328,11 @@ class B200Device:
         self._next_queue_id = 1
         self._transfer_lock = threading.Lock()
         self._lock = threading.RLock()   # finalizers may re-enter on the same thread
+        # Rotary caches: (theta as binary32 bits, width) -> device table of (cos, sin)
+        # for positions 0 .. rows-1, grown by doubling; replaced tables stay alive
+        # because work already queued may still read them.
+        self._rope_tables = {}
+        self._rope_retired = []
 
     def backend_kind(self) -> str:
         return "CUDA"
@@ -347,6 +352,29 @@ class B200Device:
 
     def owns_workspace(self, workspace: RawWorkspace) -> bool:
         return workspace in self._live_workspaces
+
+    def rope_table(self, theta: float, width: int, positions: int) -> torch.Tensor:
+        """Device table [rows, width/2, 2] of (cos, sin) covering at least `positions`
+        positions from 0. The angles are computed on the host by iomb_rope_angles (the
+        reference CPU backend's expression with this host's powf / sinf / cosf)."""
+        import struct
+        key = (struct.unpack("<I", struct.pack("<f", theta))[0], width)
+        with self._lock:
+            table = self._rope_tables.get(key)
+            if table is not None and table.shape[0] >= positions:
+                return table
+            rows = 256
+            while rows < positions:
+                rows *= 2
+            host = torch.empty((rows, width // 2, 2), dtype=torch.float32).pin_memory()
+            status = self._lib.iomb_rope_angles(host.data_ptr(), 0, rows, width, float(theta))
+            if status != 0:
+                raise _status_to_exception(status)
+            if table is not None:
+                self._rope_retired.append(table)
+            table = host.to(self.torch_device)
+            self._rope_tables[key] = table
+            return table
 
     def create_ops(self) -> "B200Queue":
         with self._lock:
@@ -729,6 +757,55 @@ class B200Queue:
                 ctypes.byref(s), ctypes.byref(d), positions, status, stream),
             (source.owner, destination.owner))
 
+    def upload(self, view: TensorView, source, workspace: RawWorkspaceView) -> int:
+        """Extension: the host-to-device transfer of Tensor::region_from_host as an
+        asynchronous operation of this queue. `source` holds the view's logical bytes
+        (row-major) in pinned host memory and must stay untouched until the returned
+        token completes; `workspace` is the {logical bytes, 32} staging range, private
+        to this queue while the token is pending. Two queues uploading and downloading
+        alternate slices keep both PCIe directions busy."""
+        try:
+            self._check_view(view, "view")
+            payload = np.ascontiguousarray(source).view(np.uint8).reshape(-1)
+            if payload.size != view.spec.logical_nbytes():
+                raise ValueError("host source must hold exactly logical_nbytes bytes")
+            staging = view.owner._staging(view, workspace)
+            host = torch.from_numpy(payload)
+            target = staging.owner.tensor()[staging.offset:staging.offset + payload.size]
+            abi_view = view.as_abi()
+        except BaseException as error:
+            return _exception_to_oid(error)
+
+        def launch(stream):
+            with torch.cuda.stream(self._stream):
+                target.copy_(host, non_blocking=True)
+            return self._lib.iomb_scatter(ctypes.byref(abi_view), staging.address(), stream)
+        return self._submit(launch, (view.owner, staging.owner, host))
+
+    def download(self, view: TensorView, destination, workspace: RawWorkspaceView) -> int:
+        """Extension: Tensor::region_to_host as an asynchronous operation of this queue;
+        `destination` (pinned host memory, logical_nbytes bytes) is valid once the
+        returned token completes."""
+        try:
+            self._check_view(view, "view")
+            out = np.asarray(destination).view(np.uint8).reshape(-1)
+            if out.size != view.spec.logical_nbytes() or not out.flags.writeable:
+                raise ValueError("host destination must hold exactly logical_nbytes writable bytes")
+            staging = view.owner._staging(view, workspace)
+            host = torch.from_numpy(out)
+            source = staging.owner.tensor()[staging.offset:staging.offset + out.size]
+            abi_view = view.as_abi()
+        except BaseException as error:
+            return _exception_to_oid(error)
+
+        def launch(stream):
+            status = self._lib.iomb_gather(ctypes.byref(abi_view), staging.address(), stream)
+            if status == 0:
+                with torch.cuda.stream(self._stream):
+                    host.copy_(source, non_blocking=True)
+            return status
+        return self._submit(launch, (view.owner, staging.owner, host))
+
     def sumsq(self, x: TensorView, scratch: RawWorkspaceView, result: int) -> int:
         """Extension: whole-view FP32 sum of squares into the device float at `result`."""
         try:
@@ -779,8 +856,30 @@ class B200Queue:
     def linear(self, *args, **kwargs) -> int:
         return OID_UNSUPPORTED
 
-    def rope(self, *args, **kwargs) -> int:
-        return OID_UNSUPPORTED
+    def rope_workspace_requirements(self, x, out, a, theta) -> WorkspaceRequirements:
+        return WorkspaceRequirements(0, 1)
+
+    def rope(self, x: TensorView, out: TensorView, a: int, theta: float, workspace=None) -> int:
+        """DeviceOps::rope (include/iom/iom.hpp): split-half rotary embedding of
+        [..., H, R, W] with row r at position a + r."""
+        try:
+            self._check_view(x, "x")
+            self._check_view(out, "out")
+            if a < 0 or a >= 1 << 64:
+                raise ValueError("rope position offset is out of range")
+            xv, ov = x.as_abi(), out.as_abi()
+            rows, width = x.spec.shape[-2], x.spec.shape[-1]
+            if x.spec.rank < 3 or width % 2 != 0 or a + rows - 1 >= 1 << 24:
+                raise ValueError("rope requires rank >= 3, an even width and positions below 2^24")
+            if not (1.0 <= theta <= 3.4028234663852886e38):
+                raise ValueError("rope theta must be finite in [1,float_max]")
+            table = self._device.rope_table(theta, width, a + rows)
+            first = table.data_ptr() + a * (width // 2) * 8
+        except BaseException as error:
+            return _exception_to_oid(error)
+        return self._submit(
+            lambda stream: self._lib.iomb_rope(ctypes.byref(xv), ctypes.byref(ov), a, first, stream),
+            (x.owner, out.owner, table))
 
     def sdpa(self, *args, **kwargs) -> int:
         return OID_UNSUPPORTED

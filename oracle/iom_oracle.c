@@ -657,6 +657,76 @@ int iomo_silu(const iomo_view* x, const iomo_view* y, int carrier) {
     return 0;
 }
 
+/* ---- RoPE: src/cpu/queue.cpp:1338-1592 ---------------------------------------- */
+
+/* rope_angle on the FP32 carrier (src/cpu/queue.cpp:1356-1367): the exponent is
+ * formed in FP64 and narrowed, powf / sinf / cosf are the C library's. */
+void iomo_rope_angle(uint64_t column, uint64_t width, uint64_t position, float theta,
+                     float* sine, float* cosine) {
+    const float exponent = (float)((-2.0 * (double)column) / (double)width);
+    const float frequency = powf(theta, exponent);
+    const float angle = (float)position * frequency;
+    *sine = sinf(angle);
+    *cosine = cosf(angle);
+}
+
+/* Split-half rotary embedding of [..., H, R, W]: row r of every plane sits at
+ * position a + r; columns c and c + W/2 form a pair. A row at position 0 is copied
+ * raw (src/cpu/queue.cpp:1497-1522); every other pair is four separately rounded
+ * FP32 products, one subtraction, one addition and one RNE encode each
+ * (src/cpu/queue.cpp:1369-1411). Leaves below F64 only. */
+int iomo_rope(const iomo_view* x, const iomo_view* out, uint64_t a, double theta) {
+    geometry_t gx, go;
+    if (geometry_of(x, &gx) || geometry_of(out, &go)) return 1;
+    if (x->rank < 3 || x->rank != out->rank || x->dtype != out->dtype) return 1;
+    for (uint32_t i = 0; i < x->rank; ++i) {
+        if (x->dims[i] != out->dims[i]) return 1;
+    }
+    if (gx.columns % 2 != 0 || x->base == out->base) return 1;
+    if (!(theta >= 1.0) || theta > 3.4028234663852886e38) return 1;
+    const format_t f = format_of(x->dtype);
+    if (!f.bits || f.bits > 32) return 2;
+    const float narrowed = (float)theta;
+    const uint64_t half = gx.columns / 2;
+    const uint64_t planes = leading_count(x);
+    for (uint64_t index = 0; index < planes; ++index) {
+        const uint64_t xp = view_plane(x, index);
+        const uint64_t op = view_plane(out, index);
+        for (uint64_t row = 0; row < gx.rows; ++row) {
+            const uint64_t position = a + row;
+            if (position == 0) {
+                for (uint64_t column = 0; column < gx.columns; ++column) {
+                    store_bits((unsigned char*)out->base, element_bit(out, &go, op, row, column), go.bits,
+                               load_bits((const unsigned char*)x->base,
+                                         element_bit(x, &gx, xp, row, column), gx.bits));
+                }
+                continue;
+            }
+            for (uint64_t column = 0; column < half; ++column) {
+                const float first = (float)codec_decode(
+                        load_bits((const unsigned char*)x->base,
+                                  element_bit(x, &gx, xp, row, column), gx.bits), f);
+                const float second = (float)codec_decode(
+                        load_bits((const unsigned char*)x->base,
+                                  element_bit(x, &gx, xp, row, column + half), gx.bits), f);
+                float sine, cosine;
+                iomo_rope_angle(column, gx.columns, position, narrowed, &sine, &cosine);
+                const volatile float first_product = first * cosine;
+                const volatile float second_product = second * sine;
+                const volatile float first_output = first_product - second_product;
+                const volatile float second_cosine = second * cosine;
+                const volatile float first_sine = first * sine;
+                const volatile float second_output = second_cosine + first_sine;
+                store_bits((unsigned char*)out->base, element_bit(out, &go, op, row, column), go.bits,
+                           codec_encode((long double)first_output, f));
+                store_bits((unsigned char*)out->base, element_bit(out, &go, op, row, column + half),
+                           go.bits, codec_encode((long double)second_output, f));
+            }
+        }
+    }
+    return 0;
+}
+
 /* ---- embedding: src/cpu/queue.cpp:941-1038 -------------------------------- */
 
 int iomo_embedding(const iomo_view* table, const iomo_view* indices,

@@ -57,6 +57,10 @@ int iomo_rmsnorm(const iomo_view* x, const iomo_view* scale, const iomo_view* ou
  * reference's GPU backends, src/cuda/copy.cu:498-503). */
 uint64_t iomo_scalar_silu(uint32_t dtype, uint64_t raw, int carrier);
 int iomo_silu(const iomo_view* x, const iomo_view* y, int carrier);
+/* RoPE (src/cpu/queue.cpp:1338-1592), FP32 carrier, the C library's powf/sinf/cosf. */
+void iomo_rope_angle(uint64_t column, uint64_t width, uint64_t position, float theta,
+                     float* sine, float* cosine);
+int iomo_rope(const iomo_view* x, const iomo_view* out, uint64_t a, double theta);
 int iomo_copy(const iomo_view* source, const iomo_view* destination);
 int iomo_cast(const iomo_view* source, const iomo_view* destination);
 /* *status = 1 and nothing is written when any index is negative or >= V. */

@@ -321,6 +321,10 @@ std::int64_t iomref_silu(void* queue, void* x, void* y) {
     return ops_of(queue).silu(view_of(x), view_of(y));
 }
 
+std::int64_t iomref_rope(void* queue, void* x, void* out, std::uint64_t a, double theta) {
+    return ops_of(queue).rope(view_of(x), view_of(out), a, theta);
+}
+
 std::int64_t iomref_copy(void* queue, void* source, void* destination) {
     return ops_of(queue).copy(view_of(source), view_of(destination));
 }

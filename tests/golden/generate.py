@@ -164,6 +164,25 @@ def silu_cases(ref, out, tag):
     out[f"silu_{tag}_F32_out"] = yf.storage.copy()
 
 
+ROPE_CASES = [((2, 3, 5, 64), 0, 10000.0), ((4, 17, 128), 7, 10000.0), ((1, 2, 33, 34), 2040, 500000.0)]
+
+
+def rope_cases(ref, out, tag):
+    """RoPE through the reference CPU backend (FP32 carrier; powf / sinf / cosf of this
+    host's C library fix the angle bits)."""
+    for dtype in (DataType.BF16, DataType.F32):
+        for i, (shape, a, theta) in enumerate(ROPE_CASES):
+            rng = np.random.default_rng(5000 + 10 * int(dtype) + i)
+            x = owner(ref, shape, dtype, random_payload(rng, shape, dtype, "normal"))
+            y = owner(ref, shape, dtype, random_payload(rng, shape, dtype))
+            key = f"rope_{tag}_{dtype.name}_{i}"
+            out[key + "_out_before"] = y.storage.copy()
+            token = ref.lib.iomref_rope(ref.queue, x.view().handle, y.view().handle, a, theta)
+            assert ref.run(token) == 0, ref.error()
+            out[key + "_x"] = x.storage.copy()
+            out[key + "_out"] = y.storage.copy()
+
+
 def main():
     fixtures = {}
     portable = Reference("portable")
@@ -171,11 +190,13 @@ def main():
     rmsnorm_cases(portable, fixtures, "portable")
     mover_cases(portable, fixtures)
     silu_cases(portable, fixtures, "portable")
+    rope_cases(portable, fixtures, "portable")
     portable.close()
     avx = Reference("avx512")
     assert avx.lib.iomref_avx512_bf16_active() == 1, "this host cannot run the AVX-512 BF16 build"
     rmsnorm_cases(avx, fixtures, "avx512")
     silu_cases(avx, fixtures, "avx512")
+    rope_cases(avx, fixtures, "avx512")
     avx.close()
     np.savez_compressed(HERE / "reference_vectors.npz", **fixtures)
     print(f"wrote {len(fixtures)} arrays, "

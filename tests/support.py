@@ -58,6 +58,11 @@ def oracle() -> ctypes.CDLL:
         lib.iomo_rmsnorm.argtypes = [_VIEW, _VIEW, _VIEW, ctypes.c_float, ctypes.c_int]
         lib.iomo_copy.restype = ctypes.c_int
         lib.iomo_copy.argtypes = [_VIEW, _VIEW]
+        lib.iomo_rope.restype = ctypes.c_int
+        lib.iomo_rope.argtypes = [_VIEW, _VIEW, ctypes.c_uint64, ctypes.c_double]
+        lib.iomo_rope_angle.restype = None
+        lib.iomo_rope_angle.argtypes = [ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_float,
+                                        ctypes.POINTER(ctypes.c_float), ctypes.POINTER(ctypes.c_float)]
         lib.iomo_silu.restype = ctypes.c_int
         lib.iomo_silu.argtypes = [_VIEW, _VIEW, ctypes.c_int]
         lib.iomo_scalar_silu.restype = ctypes.c_uint64
@@ -196,6 +201,7 @@ class Reference:
             "iomref_rmsnorm": (ctypes.c_int64, [vp, vp, vp, vp, ctypes.c_float]),
             "iomref_copy": (ctypes.c_int64, [vp, vp, vp]),
             "iomref_silu": (ctypes.c_int64, [vp, vp, vp]),
+            "iomref_rope": (ctypes.c_int64, [vp, vp, vp, ctypes.c_uint64, ctypes.c_double]),
             "iomref_embedding": (ctypes.c_int64, [vp, vp, vp, vp]),
             "iomref_cache_append": (ctypes.c_int64, [vp, vp, vp, u64]),
             "iomref_wait": (ctypes.c_int, [vp, ctypes.c_int64]),

@@ -139,3 +139,21 @@ def test_silu_golden(build):
     yf = host_from(GOLDEN[f"silu_{build}_F32_out_before"], (2, 17, 35), DataType.F32)
     assert oracle().iomo_silu(abi(xf.view()), abi(yf.view()), 0) == 0
     assert np.array_equal(yf.storage, GOLDEN[f"silu_{build}_F32_out"])
+
+
+ROPE_CASES = [((2, 3, 5, 64), 0, 10000.0), ((4, 17, 128), 7, 10000.0), ((1, 2, 33, 34), 2040, 500000.0)]
+
+
+@pytest.mark.parametrize("build", ["portable", "avx512"])
+@pytest.mark.parametrize("dtype", [DataType.BF16, DataType.F32])
+@pytest.mark.parametrize("case", range(len(ROPE_CASES)))
+def test_rope_golden(build, dtype, case):
+    """Oracle against the reference CPU backend's stored RoPE outputs. The angles go
+    through this host's powf / sinf / cosf, as they did when the vectors were made
+    (same image, same C library)."""
+    shape, a, theta = ROPE_CASES[case]
+    key = f"rope_{build}_{dtype.name}_{case}"
+    x = host_from(GOLDEN[key + "_x"], shape, dtype)
+    out = host_from(GOLDEN[key + "_out_before"], shape, dtype)
+    assert oracle().iomo_rope(abi(x.view()), abi(out.view()), a, theta) == 0
+    assert np.array_equal(out.storage, GOLDEN[key + "_out"])

@@ -208,6 +208,26 @@ def test_silu_and_fused_gate(pair):
     assert np.array_equal(out.read(), out2.read())
 
 
+@pytest.mark.parametrize("dtype", [DataType.BF16, DataType.F32])
+@pytest.mark.parametrize("shape,a", [((2, 3, 5, 64), 0), ((4, 17, 128), 7), ((1, 2, 33, 34), 2040)])
+def test_rope(pair, dtype, shape, a):
+    """RoPE behind the facade, candidate and reference CPU backend side by side, bit for
+    bit; a second call at a later position grows the candidate's rotary cache."""
+    rng = np.random.default_rng(51)
+    x = both(pair, shape, dtype, rng, kind="normal")
+    out = both(pair, shape, dtype, rng)
+    for position in (a, a + 3000):
+        for i, ref in enumerate(pair):
+            token = ref.lib.iomref_rope(ref.queue, x[i].view().handle, out[i].view().handle,
+                                        position, 10000.0)
+            assert ref.run(token) == 0, ref.error()
+        same(out)
+    same(x)
+    cpu, gpu = pair
+    assert gpu.lib.iomref_rope(gpu.queue, x[1].view().handle, x[1].view().handle, 0, 10000.0) == -1
+    assert gpu.lib.iomref_rope(gpu.queue, x[1].view().handle, out[1].view().handle, 0, 0.5) == -1
+
+
 def test_host_transfers_and_fused_extension(pair):
     cpu, gpu = pair
     rng = np.random.default_rng(10)

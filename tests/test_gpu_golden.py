@@ -97,3 +97,18 @@ def test_silu_golden_gpu(gpu):
     before = GOLDEN["silu_portable_F32_out_before"].view(np.uint32).astype(np.int64)
     untouched = want == before        # padding and nothing else (payloads are random)
     assert np.array_equal(got[untouched], want[untouched])
+
+
+@pytest.mark.parametrize("dtype", [DataType.BF16, DataType.F32])
+def test_rope_golden_gpu(gpu, dtype):
+    """The CUDA path against the reference CPU backend's stored RoPE outputs, bit for bit
+    (both builds stored the same bytes)."""
+    from test_golden import ROPE_CASES
+    device, queue = gpu
+    for case, (shape, a, theta) in enumerate(ROPE_CASES):
+        key = f"rope_portable_{dtype.name}_{case}"
+        dx = upload(device, host_from(GOLDEN[key + "_x"], shape, dtype))
+        do = upload(device, host_from(GOLDEN[key + "_out_before"], shape, dtype))
+        run(queue, queue.rope(dx.view(), do.view(), a, theta))
+        assert np.array_equal(download(do), GOLDEN[key + "_out"]), key
+        assert np.array_equal(GOLDEN[key + "_out"], GOLDEN[f"rope_avx512_{dtype.name}_{case}_out"])

@@ -207,6 +207,50 @@ def test_silu_views_and_ragged_extents_match_reference(ref, dtype):
     assert oracle().iomo_silu(abi(x.view()), abi(x.view()), 0) == 1
 
 
+@pytest.mark.parametrize("dtype", [DataType.BF16, DataType.F32])
+@pytest.mark.parametrize("shape,a", [((2, 3, 5, 64), 0), ((4, 17, 128), 7), ((1, 2, 33, 34), 2040),
+                                     ((2, 1, 1, 6), 123456)])
+@pytest.mark.parametrize("theta", [10000.0, 500000.0, 1.0])
+def test_rope_matches_reference(ref, dtype, shape, a, theta):
+    """Split-half RoPE: both reference CPU builds against the oracle, including the
+    raw-copy row at position 0, ragged widths and transformed leading views."""
+    rng = np.random.default_rng(41 + len(shape))
+    payload = random_payload(rng, shape, dtype, "normal")
+    if dtype == DataType.F32:
+        flat = payload.reshape(-1).view(np.uint32)
+        count = min(flat.size, SPECIAL_F32.size)
+        flat[:count] = SPECIAL_F32[:count]
+    else:
+        flat = payload.reshape(-1)
+        count = min(flat.size, SPECIAL_BF16.size)
+        flat[:count] = SPECIAL_BF16[:count]
+    x, rx = mirror(ref, shape, dtype, rng, payload=payload)
+    out, rout = mirror(ref, shape, dtype, rng)
+    token = ref.lib.iomref_rope(ref.queue, rx.view().handle, rout.view().handle, a, theta)
+    assert ref.run(token) == 0, ref.error()
+    assert oracle().iomo_rope(abi(x.view()), abi(out.view()), a, theta) == 0
+    assert np.array_equal(out.storage, rout.storage)
+
+
+def test_rope_views_and_rejections_match_reference(ref):
+    rng = np.random.default_rng(43)
+    x, rx = mirror(ref, (3, 2, 9, 32), DataType.BF16, rng, kind="normal")
+    out, rout = mirror(ref, (2, 3, 9, 32), DataType.BF16, rng)
+    xv, rxv = apply(x.view(), rx.view(), [("permute", ([1, 0],))])
+    assert ref.run(ref.lib.iomref_rope(ref.queue, rxv.handle, rout.view().handle, 5, 10000.0)) == 0
+    assert oracle().iomo_rope(abi(xv), abi(out.view()), 5, 10000.0) == 0
+    assert np.array_equal(out.storage, rout.storage)
+    # in place, odd width, rank two and theta below one are rejected by both
+    assert ref.lib.iomref_rope(ref.queue, rx.view().handle, rx.view().handle, 0, 10000.0) == -1
+    assert oracle().iomo_rope(abi(x.view()), abi(x.view()), 0, 10000.0) == 1
+    assert ref.lib.iomref_rope(ref.queue, rxv.handle, rout.view().handle, 0, 0.5) == -1
+    assert oracle().iomo_rope(abi(xv), abi(out.view()), 0, 0.5) == 1
+    odd, rodd = mirror(ref, (2, 4, 33), DataType.BF16, rng)
+    odd2, rodd2 = mirror(ref, (2, 4, 33), DataType.BF16, rng)
+    assert ref.lib.iomref_rope(ref.queue, rodd.view().handle, rodd2.view().handle, 0, 10000.0) == -1
+    assert oracle().iomo_rope(abi(odd.view()), abi(odd2.view()), 0, 10000.0) == 1
+
+
 @pytest.mark.parametrize("index_dtype", [DataType.U32, DataType.I64, DataType.U8, DataType.I16])
 def test_embedding_matches_reference(ref, index_dtype):
     rng = np.random.default_rng(13)
