@@ -41,7 +41,7 @@ WORKLOAD = (f"C2 x{PLANES}: BF16 [{PLANES},{ROWS},{HIDDEN}] residual ADD + RMSNo
 # dram__bytes_read.sum + dram__bytes_write.sum of one rmsnorm_kernel launch, from
 # the ncu capture summarised in profiles/ (taken on a [2,8192,2048] case; traffic
 # is proportional to the rows processed, so it is scaled by the plane count).
-NCU_TRAFFIC_BYTES_PER_PLANE = 211.63e6 / 2     # 134.32 MB read + 77.31 MB written, 2 planes
+NCU_TRAFFIC_BYTES_PER_PLANE = 213.98e6 / 2     # 134.32 MB read + 79.66 MB written, 2 planes
 
 
 def configure(planes: int) -> None:
