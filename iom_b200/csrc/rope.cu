@@ -51,9 +51,10 @@ __device__ __forceinline__ void rotate(float first, float second, float2 angle, 
 // of kRopePlanes planes): the angles of the tile are loaded once and kept in
 // registers while the warp walks the group's planes (heads and sequences share them).
 constexpr uint32_t kRopePlanes = 16;
+constexpr uint32_t kRopeBatch = 2;
 
 template <int ELEM>
-__global__ void __launch_bounds__(kRopeThreads)
+__global__ void __launch_bounds__(kRopeThreads, 4)
 rope_tile_kernel(const RopeParams p) {
     constexpr uint32_t kTileBytes = kTileSlots * ELEM;
     constexpr uint32_t kTileVectors = kTileBytes / 16;
@@ -92,12 +93,12 @@ rope_tile_kernel(const RopeParams p) {
                 }
             }
             const size_t partner = static_cast<size_t>(p.half_tiles) * kTileBytes;
-            // Four planes' vectors are in flight before the first is rotated.
-            for (uint32_t q0 = 0; q0 < planes_here; q0 += 4) {
-                uint4 a[4], b[4];
-                unsigned char* target[4];
+            // kRopeBatch planes' vectors are in flight before the first is rotated.
+            for (uint32_t q0 = 0; q0 < planes_here; q0 += kRopeBatch) {
+                uint4 a[kRopeBatch], b[kRopeBatch];
+                unsigned char* target[kRopeBatch];
 #pragma unroll
-                for (uint32_t u = 0; u < 4; ++u) {
+                for (uint32_t u = 0; u < kRopeBatch; ++u) {
                     if (q0 + u >= planes_here) continue;
                     const uint64_t x_plane = operand_plane(p.x, p.leading, first_plane + q0 + u);
                     const uint64_t out_plane = operand_plane(p.out, p.leading, first_plane + q0 + u);
@@ -109,7 +110,7 @@ rope_tile_kernel(const RopeParams p) {
                     b[u] = load_u4_stream(x_first + partner);
                 }
 #pragma unroll
-                for (uint32_t u = 0; u < 4; ++u) {
+                for (uint32_t u = 0; u < kRopeBatch; ++u) {
                     if (q0 + u >= planes_here) continue;
                     uint4 ra = a[u], rb = b[u];
                     if (!raw_copy) {
