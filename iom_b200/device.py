@@ -392,6 +392,47 @@ def make_b200_device(ordinal: int, memory: DeviceMemoryConfig,
     return B200Device(ordinal, memory, queue_config)
 
 
+class SubmissionFaults:
+    """Host-side fault table of one queue, for failure-path tests (the role of the
+    reference's test-only failure latches, src/cpu/queue.cpp:51-87,128-160): a named
+    point of the submission path is armed to fail once, after `skip` passages.
+    Nothing here touches the device: every fault is an error code or an exception
+    raised on the host, the context stays usable.
+
+      "launch"    the kernel library's entry point is not called; the wrapper reports
+                  IOMB_ERR_DEVICE -> the operation returns OidError::DeviceError
+      "record"    the completion event cannot be recorded after an accepted launch ->
+                  the stream is drained instead (the reference's second proof of
+                  completion) and the operation still returns a token
+      "complete"  the accepted operation is reported failed when its completion is
+                  observed -> retained failure, rethrown by every wait on the token
+    """
+
+    POINTS = ("launch", "record", "complete")
+
+    def __init__(self):
+        self._armed = {}
+
+    def arm(self, point: str, skip: int = 0) -> None:
+        if point not in self.POINTS:
+            raise ValueError(f"unknown fault point {point!r}")
+        self._armed[point] = int(skip)
+
+    def clear(self) -> None:
+        self._armed.clear()
+
+    def take(self, point: str) -> bool:
+        """True exactly once per arming, on the passage the arming named."""
+        left = self._armed.get(point)
+        if left is None:
+            return False
+        if left > 0:
+            self._armed[point] = left - 1
+            return False
+        del self._armed[point]
+        return True
+
+
 class CapturedSequence:
     """A run of queue operations recorded once and replayed as one CUDA graph launch:
     the launch-bound inner loop of a decode step (embedding, norms, cache appends,
@@ -505,6 +546,7 @@ class B200Queue:
         self._completed = 0
         self._closed = False
         self._capture = None      # the CapturedSequence being recorded, if any
+        self.faults = SubmissionFaults()
         self._sequences = []      # every recorded sequence, kept alive until closed
         # Queue-owned pinned cells for status read-backs, one per in-flight credit
         # (the reference keeps one pinned cell per queue, src/cuda/device.cpp:165-200).
@@ -550,7 +592,13 @@ class B200Queue:
         if record is None:
             return
         event, _owners, status_cell = record
-        event.synchronize()
+        if event is None:
+            self._stream.synchronize()      # no event could be recorded: drain the stream
+        else:
+            event.synchronize()
+        if self.faults.take("complete"):
+            self._failures[sequence] = DeviceError("injected completion failure")
+            return
         cells = status_cell if isinstance(status_cell, list) else \
             ([] if status_cell is None else [status_cell])
         if any(int(cell.item()) != 0 for cell in cells):
@@ -562,11 +610,15 @@ class B200Queue:
         try:
             self._retire(self._device.queue_config.max_in_flight_per_queue)
             with torch.cuda.device(self._device.torch_device):
+                if self.faults.take("launch"):
+                    raise DeviceError("injected launch failure")
                 status = launch(self._stream.cuda_stream)
                 if status != 0:
                     raise _status_to_exception(status)
-                event = torch.cuda.Event()
-                event.record(self._stream)
+                event = None
+                if not self.faults.take("record"):
+                    event = torch.cuda.Event()
+                    event.record(self._stream)
                 pinned = None
                 if status_cell is not None:
                     slot = (self._sequence + 1) % self._status_cells.numel()
