@@ -501,7 +501,9 @@ protected:
 
     oid binary_impl(const BinaryRequest& request) override {
         switch (request.out.spec.data_type) {
-            case DataType::I32: case DataType::U32: case DataType::F32: case DataType::BF16: break;
+            case DataType::I8: case DataType::U8: case DataType::I16: case DataType::U16:
+            case DataType::I32: case DataType::U32: case DataType::I64: case DataType::U64:
+            case DataType::F16: case DataType::BF16: case DataType::F32: break;
             default: throw detail::UnsupportedOperation();
         }
         std::lock_guard<std::mutex> order(submission_order_mutex_);

@@ -23,6 +23,8 @@
 // needs no special path here.
 #include "host.hpp"
 
+#include <cuda_fp16.h>
+
 namespace iomb {
 
 enum class Leaf : int { I32 = 0, F32 = 1, BF16 = 2 };
@@ -385,6 +387,91 @@ static int launch_op(int op, const BinaryParams& params, bool linear,
     }
 }
 
+// ---- every other byte-multiple leaf: one thread per logical element ------------
+//
+// I8/U8, I16/U16, I64/U64 (wrapping ADD/MUL/SUB) and F16 (one IEEE binary32
+// operation, one RNE narrowing to binary16, positive quiet NaN 0x7E00: equal to the
+// reference codec because 24 >= 2 * 11 + 2). These leaves are off the serving
+// path, so the kernel is the simple one: thread e owns logical element e of the
+// result, reads its two inputs through the same tile map the fast kernels use and
+// writes one element; broadcast operands read their row 0 / column 0.
+enum class Wide : int { Int8 = 0, Int16 = 1, Int64 = 2, Half = 3 };
+
+template <Wide W>
+struct WideTraits {
+    static constexpr int kBytes = W == Wide::Int8 ? 1 : W == Wide::Int64 ? 8 : 2;
+};
+
+template <int BYTES>
+__device__ __forceinline__ uint64_t load_element(const unsigned char* address) {
+    if constexpr (BYTES == 1) return *address;
+    if constexpr (BYTES == 2) return *reinterpret_cast<const uint16_t*>(address);
+    return *reinterpret_cast<const uint64_t*>(address);
+}
+
+template <int BYTES>
+__device__ __forceinline__ void store_element(unsigned char* address, uint64_t value) {
+    if constexpr (BYTES == 1) *address = static_cast<unsigned char>(value);
+    else if constexpr (BYTES == 2) *reinterpret_cast<uint16_t*>(address) = static_cast<uint16_t>(value);
+    else *reinterpret_cast<uint64_t*>(address) = value;
+}
+
+template <Wide W, int OP>
+__device__ __forceinline__ uint64_t apply_wide(uint64_t a, uint64_t b) {
+    if constexpr (W == Wide::Half) {
+        const float x = __half2float(__ushort_as_half(static_cast<unsigned short>(a)));
+        const float y = __half2float(__ushort_as_half(static_cast<unsigned short>(b)));
+        const float r = apply_f32<OP>(x, y);
+        if (r != r) return 0x7E00u;
+        return __half_as_ushort(__float2half_rn(r));
+    } else {
+        // Wrapping: the low bits of the 64-bit result are the result of every narrower width.
+        return OP == IOMB_ADD ? a + b : OP == IOMB_MUL ? a * b : a - b;
+    }
+}
+
+template <Wide W, int OP>
+__global__ void __launch_bounds__(kTiledThreads)
+binary_element_kernel(const BinaryParams p, uint64_t elements) {
+    constexpr int BYTES = WideTraits<W>::kBytes;
+    const uint64_t stride = static_cast<uint64_t>(gridDim.x) * kTiledThreads;
+    for (uint64_t e = static_cast<uint64_t>(blockIdx.x) * kTiledThreads + threadIdx.x; e < elements;
+         e += stride) {
+        const uint32_t col = static_cast<uint32_t>(e % p.cols);
+        const uint64_t rest = e / p.cols;
+        const uint32_t row = static_cast<uint32_t>(rest % p.rows);
+        const uint64_t index = rest / p.rows;
+        auto slot = [&](const Operand& operand) {
+            const uint32_t r = operand.bc_rows ? 0u : row;
+            const uint32_t c = operand.bc_cols ? 0u : col;
+            const uint64_t plane = operand_plane(operand, p.leading, index);
+            const uint64_t tile = (plane * operand.tile_rows + r / kTile) * operand.tile_cols + c / kTile;
+            return operand.base + (tile * kTileSlots + (r % kTile) * kTile + c % kTile) * BYTES;
+        };
+        const uint64_t a = load_element<BYTES>(slot(p.lhs));
+        const uint64_t b = load_element<BYTES>(slot(p.rhs));
+        store_element<BYTES>(const_cast<unsigned char*>(slot(p.out)), apply_wide<W, OP>(a, b));
+    }
+}
+
+template <Wide W>
+static int launch_element(int op, const BinaryParams& params, cudaStream_t stream) {
+    const uint64_t elements = params.leading.planes * params.rows * params.cols;
+    const unsigned grid = grid_for((elements + kTiledThreads - 1) / kTiledThreads, 16);
+    switch (op) {
+        case IOMB_ADD: binary_element_kernel<W, IOMB_ADD><<<grid, kTiledThreads, 0, stream>>>(params, elements); break;
+        case IOMB_MUL: binary_element_kernel<W, IOMB_MUL><<<grid, kTiledThreads, 0, stream>>>(params, elements); break;
+        case IOMB_SUB: binary_element_kernel<W, IOMB_SUB><<<grid, kTiledThreads, 0, stream>>>(params, elements); break;
+        default:
+            if constexpr (W == Wide::Half) {
+                binary_element_kernel<W, IOMB_DIV><<<grid, kTiledThreads, 0, stream>>>(params, elements);
+            } else {
+                return fail(IOMB_ERR_UNSUPPORTED, "binary: integer division is not admitted");
+            }
+    }
+    return check_launch("binary launch");
+}
+
 }  // namespace iomb
 
 extern "C" int iomb_binary(int op, const iomb_view* lhs, const iomb_view* rhs,
@@ -457,13 +544,19 @@ extern "C" int iomb_binary(int op, const iomb_view* lhs, const iomb_view* rhs,
             return fail(IOMB_ERR_INVALID_ARGUMENT, "binary input/output alias is forbidden");
         }
     }
-    Leaf leaf;
+    Leaf leaf = Leaf::I32;
+    int wide = -1;      // a Wide ordinal when the leaf takes the per-element kernel
     switch (out->dtype) {
         case IOMB_I32: case IOMB_U32: leaf = Leaf::I32; break;
         case IOMB_F32: leaf = Leaf::F32; break;
         case IOMB_BF16: leaf = Leaf::BF16; break;
+        case IOMB_I8: case IOMB_U8: wide = static_cast<int>(Wide::Int8); break;
+        case IOMB_I16: case IOMB_U16: wide = static_cast<int>(Wide::Int16); break;
+        case IOMB_I64: case IOMB_U64: wide = static_cast<int>(Wide::Int64); break;
+        case IOMB_F16: wide = static_cast<int>(Wide::Half); break;
         default:
-            return fail(IOMB_ERR_UNSUPPORTED, "binary: leaf is not I32, U32, F32 or BF16");
+            return fail(IOMB_ERR_UNSUPPORTED,
+                        "binary: leaf is not a byte-multiple integer, F16, BF16 or F32");
     }
 
     BinaryParams params{};
@@ -482,6 +575,15 @@ extern "C" int iomb_binary(int op, const iomb_view* lhs, const iomb_view* rhs,
     params.runs = (params.tile_cols + params.run_tiles - 1) / params.run_tiles;
     params.items = params.leading.planes * params.tile_rows * params.runs;
 
+    if (wide >= 0) {
+        cudaStream_t element_stream = static_cast<cudaStream_t>(stream);
+        switch (static_cast<Wide>(wide)) {
+            case Wide::Int8: return launch_element<Wide::Int8>(op, params, element_stream);
+            case Wide::Int16: return launch_element<Wide::Int16>(op, params, element_stream);
+            case Wide::Int64: return launch_element<Wide::Int64>(op, params, element_stream);
+            default: return launch_element<Wide::Half>(op, params, element_stream);
+        }
+    }
     const bool full = !broadcasts[0] && !broadcasts[1];
     const bool tile_multiple = fo.rows % kTile == 0 && fo.cols % kTile == 0;
     const bool linear = full && tile_multiple && params.leading.contiguous;

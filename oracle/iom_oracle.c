@@ -260,18 +260,72 @@ static uint32_t float_to_bf16_rne(float value) {
 
 /* The arithmetic the kernels implement: one IEEE binary32 add/mul/sub/div
  * (rounded once), then one RNE encode for BF16, every NaN result canonical.
- * Equal to iomo_scalar_binary for I32/U32/F32/BF16 because rounding a binary32
- * (or x87) result again to a format with fewer than half its significand bits
- * is innocuous for all four operations; tests/test_layout_and_codec.py proves
+ * Equal to iomo_scalar_binary for the byte-multiple integers, F32, BF16 and F16
+ * because rounding a binary32 (or x87) result again to a format with at most
+ * (p - 2) / 2 significand bits is innocuous for all four operations (F16: 11 bits
+ * against 24); tests/test_layout_and_codec.py proves
  * the equality exhaustively for BF16 and on boundary-rich samples for F32.
  * Integer division does not exist (the codec answers 0, admission rejects it). */
+/* binary16 <-> binary32 with plain integer arithmetic (no compiler half type):
+ * exact widening, and one round-to-nearest-even narrowing with gradual underflow
+ * and overflow to infinity. */
+static float half_to_float(uint32_t h) {
+    const uint32_t sign = (h & 0x8000u) << 16;
+    const uint32_t exponent = (h >> 10) & 0x1Fu;
+    uint32_t mantissa = h & 0x3FFu;
+    if (exponent == 0x1Fu) return bits_to_float(sign | 0x7F800000u | (mantissa << 13));
+    if (exponent == 0) {
+        if (mantissa == 0) return bits_to_float(sign);
+        int shift = 0;
+        while (!(mantissa & 0x400u)) {
+            mantissa <<= 1;
+            ++shift;
+        }
+        return bits_to_float(sign | ((uint32_t)(113 - shift) << 23) | ((mantissa & 0x3FFu) << 13));
+    }
+    return bits_to_float(sign | ((exponent + 112u) << 23) | (mantissa << 13));
+}
+
+static uint32_t float_to_half_rne(float value) {
+    const uint32_t bits = float_to_bits(value);
+    const uint32_t sign = (bits >> 16) & 0x8000u;
+    const uint32_t magnitude = bits & 0x7FFFFFFFu;
+    if (magnitude > 0x7F800000u) return 0x7E00u;                   /* canonical positive NaN */
+    if (magnitude >= 0x47800000u) return sign | 0x7C00u;           /* >= 2^16: infinity */
+    if (magnitude < 0x33000000u) return sign;                      /* < 2^-25: zero */
+    const int exponent = (int)(magnitude >> 23) - 127;
+    uint32_t significand = (magnitude & 0x7FFFFFu) | 0x800000u;    /* 24 bits */
+    int shift = 13;                                                /* normal: keep 11 bits */
+    if (exponent < -14) shift += -14 - exponent;                   /* subnormal: quantum 2^-24 */
+    uint32_t quotient = significand >> shift;
+    const uint32_t remainder = significand & ((1u << shift) - 1u);
+    const uint32_t half = 1u << (shift - 1);
+    if (remainder > half || (remainder == half && (quotient & 1u))) ++quotient;
+    uint32_t code;
+    if (exponent >= -14) {
+        code = ((uint32_t)(exponent + 15) << 10) + (quotient - 0x400u);
+        if (code >= 0x7C00u) code = 0x7C00u;
+    } else {
+        code = quotient;
+    }
+    return sign | code;
+}
+
 uint64_t iomo_scalar_binary_ieee(int op, uint32_t dtype, uint64_t a, uint64_t b) {
-    if (dtype == DT_I32 || dtype == DT_U32) {
-        const uint32_t x = (uint32_t)a, y = (uint32_t)b;
+    const unsigned width = integer_width(dtype);
+    if (width >= 8) {
+        /* Byte-multiple integers wrap; division does not exist. */
         if (op == 3) return 0;
-        return op == 0 ? (uint32_t)(x + y) : op == 1 ? (uint32_t)(x * y) : (uint32_t)(x - y);
+        const uint64_t mask = width == 64 ? ~(uint64_t)0 : (((uint64_t)1 << width) - 1);
+        return (op == 0 ? a + b : op == 1 ? a * b : a - b) & mask;
     }
     float x, y;
+    if (dtype == DT_F16) {
+        x = half_to_float((uint32_t)a);
+        y = half_to_float((uint32_t)b);
+        volatile float r16 = op == 0 ? x + y : op == 1 ? x * y : op == 2 ? x - y : x / y;
+        return float_to_half_rne(r16);
+    }
     if (dtype == DT_BF16) {
         x = bits_to_float((uint32_t)a << 16);
         y = bits_to_float((uint32_t)b << 16);

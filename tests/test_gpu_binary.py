@@ -8,7 +8,11 @@ from support import (HostTensor, SPECIAL_BF16, SPECIAL_F32, abi, oracle, random_
 
 pytestmark = pytest.mark.gpu
 OPS = {"add": 0, "mul": 1, "sub": 2, "div": 3}
-DTYPES = [DataType.I32, DataType.U32, DataType.F32, DataType.BF16]
+DTYPES = [DataType.I32, DataType.U32, DataType.F32, DataType.BF16,
+          # per-element kernel: the other byte-multiple integers and F16
+          DataType.I8, DataType.U8, DataType.I16, DataType.U16, DataType.I64, DataType.U64, DataType.F16]
+INTEGERS = (DataType.I8, DataType.U8, DataType.I16, DataType.U16, DataType.I32, DataType.U32,
+            DataType.I64, DataType.U64)
 
 CASES = [
     ((2, 17, 33), (2, 17, 33), (2, 17, 33)),
@@ -57,7 +61,7 @@ def check(queue, device, op, lhs, rhs, out, lv=None, rv=None, ov=None):
 @pytest.mark.parametrize("shapes", CASES)
 def test_binary_parity(gpu, dtype, op, shapes):
     device, queue = gpu
-    if op == "div" and dtype in (DataType.I32, DataType.U32):
+    if op == "div" and dtype in INTEGERS:
         pytest.skip("integer division is rejected (test_binary_rejections)")
     rng = np.random.default_rng(abs(hash((int(dtype), op, shapes))) & 0xFFFF)
     tensors = []
@@ -94,6 +98,28 @@ def test_binary_exhaustive_bf16_pairs(gpu):
     out = HostTensor((65536, 512), DataType.BF16)
     lhs.view().copy_from_host(np.repeat(a, 512).reshape(65536, 512))
     rhs.view().copy_from_host(np.tile(b, 65536).reshape(65536, 512))
+    for op in ("add", "mul", "sub", "div"):
+        dl, dr, do = upload(device, lhs), upload(device, rhs), upload(device, out)
+        run(queue, getattr(queue, op)(dl.view(), dr.view(), do.view()))
+        assert oracle().iomo_binary(OPS[op], abi(lhs.view()), abi(rhs.view()), abi(out.view()), 1) == 0
+        assert np.array_equal(download(do), out.storage)
+        for t in (dl, dr, do):
+            t.close()
+
+
+def test_binary_exhaustive_f16_pairs(gpu):
+    """Every F16 code against 192 boundary-rich codes, all four operations."""
+    device, queue = gpu
+    a = np.arange(65536, dtype=np.uint16)
+    mant = np.array([0, 1, 2, 0x1FF, 0x200, 0x201, 0x3FE, 0x3FF], dtype=np.uint16)
+    exps = np.array([0, 1, 2, 14, 15, 16, 29, 30, 31, 10, 20, 25], dtype=np.uint16)
+    b = np.array([(s << 15) | (e << 10) | m for s in (0, 1) for e in exps for m in mant],
+                 dtype=np.uint16)
+    lhs = HostTensor((65536, 192), DataType.F16)
+    rhs = HostTensor((65536, 192), DataType.F16)
+    out = HostTensor((65536, 192), DataType.F16)
+    lhs.view().copy_from_host(np.repeat(a, 192).reshape(65536, 192))
+    rhs.view().copy_from_host(np.tile(b, 65536).reshape(65536, 192))
     for op in ("add", "mul", "sub", "div"):
         dl, dr, do = upload(device, lhs), upload(device, rhs), upload(device, out)
         run(queue, getattr(queue, op)(dl.view(), dr.view(), do.view()))
@@ -161,5 +187,9 @@ def test_binary_rejections(gpu):
     i32 = device.create_tensor(HostTensor((16, 16), DataType.I32).spec)
     assert queue.div(i32.view(), i32.view(), i32.view()) == -2    # no integer division
     assert queue.sub(i32.view(), i32.view(), i32.view()) > 0
+    i8 = device.create_tensor(HostTensor((16, 16), DataType.I8).spec)
+    assert queue.div(i8.view(), i8.view(), i8.view()) == -2
+    f8 = device.create_tensor(HostTensor((16, 16), DataType.F8_E5M2).spec)
+    assert queue.add(f8.view(), f8.view(), f8.view()) == -2       # leaf not served
     with pytest.raises(ValueError):
         queue.wait(12345)

@@ -109,6 +109,20 @@ def test_ieee_form_equals_codec_bf16(op):
 
 
 @pytest.mark.parametrize("op", [ADD, MUL, SUB, DIV])
+def test_ieee_form_equals_codec_f16(op):
+    """Every F16 code against a boundary-rich set: a binary32 operation followed by one
+    RNE narrowing to binary16 equals the reference codec (24 >= 2 * 11 + 2)."""
+    a = np.arange(65536, dtype=np.uint16)
+    mant = np.array([0, 1, 2, 0x1FF, 0x200, 0x201, 0x3FE, 0x3FF], dtype=np.uint16)
+    exps = np.array([0, 1, 2, 14, 15, 16, 29, 30, 31, 10, 20, 25], dtype=np.uint16)
+    b = np.array([(s << 15) | (e << 10) | m for s in (0, 1) for e in exps for m in mant],
+                 dtype=np.uint16)
+    mismatches = oracle().iomo_codec_mismatches(op, int(DataType.F16), a.ctypes.data, a.size,
+                                                b.ctypes.data, b.size)
+    assert mismatches == 0
+
+
+@pytest.mark.parametrize("op", [ADD, MUL, SUB, DIV])
 def test_ieee_form_equals_codec_f32(op):
     rng = np.random.default_rng(9)
     exps = np.array([0, 1, 2, 23, 24, 25, 100, 126, 127, 128, 149, 150, 151, 230, 253, 254, 255],
