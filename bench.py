@@ -513,6 +513,29 @@ def ops_table(device, queue, only=None, iters: int = 10) -> dict:
         record("rope_bf16", 2 * count * 2, lambda: ok(queue.rope(q_in.view(), q_out.view(), 0, 10000.0)),
                str(list(shape)))
         release()
+    if only is None or only in ("embedding_prefill", "cache_append_prefill"):
+        # Prefill-sized data movement: 131072 token rows of the TinyLlama table (537 MB out),
+        # and 64 sequences x 4 KV heads x 2048 new rows appended into 4096-row caches.
+        table = tensor((32000, 2048), DataType.BF16)
+        count = 131072
+        ids = device.create_tensor(TensorSpec((1, count), DataType.U32))
+        made.append(ids)
+        ids.storage().view(torch.int32).copy_(
+            torch.randint(0, 32000, (ids.storage_nbytes // 4,), device=device.torch_device,
+                          dtype=torch.int32))
+        out = tensor((count, 2048), DataType.BF16)
+        ws = device.create_workspace(32)
+        record("embedding_prefill", 2 * count * 2048 * 2 + count * 4,
+               lambda: ok(queue.embedding(table.view(), ids.view(), out.view(), ws.view())),
+               f"table [32000,2048], {count} ids")
+        ws.close()
+        release()
+        k = tensor((64, 4, 2048, 64), DataType.BF16)
+        cache = tensor((64, 4, 4096, 64), DataType.BF16)
+        record("cache_append_prefill", 2 * 64 * 4 * 2048 * 64 * 2,
+               lambda: ok(queue.cache_append(k.view(), cache.view(), 1024)),
+               "K [64,4,2048,64] -> cache [64,4,4096,64] at row 1024")
+        release()
     if only is None or only in ("embedding_decode", "cache_append_decode_batched",
                                 "cache_append_decode_64calls", "cast_logits"):
         # Decode-step data movement, TinyLlama geometry (BASELINE config 4): microseconds.

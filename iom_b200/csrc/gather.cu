@@ -1,9 +1,9 @@
 // Row movers on tiled storage: embedding lookup and KV-cache append.
 //
 // A logical row of F elements is F/16 pieces of one in-tile row (16 elements)
-// at a one-tile stride. Both operations copy whole rows bit for bit, so they
-// share one device routine that moves a row as 16-byte vectors and masks the
-// feature tail.
+// at a one-tile stride. Both operations copy whole rows bit for bit as 16-byte
+// vectors, masking the feature tail; the work is cut by tiles, not by rows, so
+// that one side of every move is a whole contiguous tile.
 //
 // Replaces embedding_word_kernel (src/shared/standard_tiled_embedding.inl:117-199)
 // and cache_append_kernel (src/cuda/copy.cu:135-214). The reference append
@@ -13,7 +13,9 @@
 
 namespace iomb {
 
-constexpr int kRowThreads = 128;
+constexpr int kRowThreads = 256;
+constexpr int kRowWarps = kRowThreads / 32;
+constexpr uint32_t kTilesPerItem = 4;     // neighbouring tiles of a band one warp moves at once
 
 struct RowGeometry {
     uint32_t elem;          // leaf bytes
@@ -22,36 +24,32 @@ struct RowGeometry {
     uint32_t row_vectors;   // tile_cols * (16*elem/16)
 };
 
-// Moves vectors [first, first+count) of one logical row.
-__device__ __forceinline__ void move_row_vectors(
-        const unsigned char* src_row, unsigned char* dst_row, const RowGeometry& g,
-        uint32_t vector) {
-    const uint32_t vectors_per_piece = g.elem;            // (16*elem)/16
-    const uint32_t per_vector = 16 / g.elem;
-    const uint32_t tile = vector / vectors_per_piece;
-    const uint32_t cv = vector % vectors_per_piece;
-    const uint32_t col = tile * kTile + cv * per_vector;
-    if (col >= g.cols) return;
-    const size_t offset = static_cast<size_t>(tile) * kTileSlots * g.elem + cv * 16;
-    const uint32_t valid = min(per_vector, g.cols - col);
-    const uint4 value = load_u4(src_row + offset);
-    if (valid == per_vector) {
-        store_u4(dst_row + offset, value);
-    } else {
-        const uint32_t words[4] = {value.x, value.y, value.z, value.w};
-        const uint32_t bytes = valid * g.elem;
-        for (uint32_t b = 0; b < bytes; ++b) {
-            dst_row[offset + b] = static_cast<unsigned char>(words[b / 4] >> ((b & 3u) * 8));
-        }
+// Stores one 16-byte vector, or only its first `valid` elements at the feature tail.
+__device__ __forceinline__ void store_row_vector(unsigned char* address, uint4 value,
+                                                 uint32_t valid, uint32_t per_vector,
+                                                 uint32_t elem) {
+    if (valid >= per_vector) {
+        store_u4(address, value);
+        return;
+    }
+    const uint32_t words[4] = {value.x, value.y, value.z, value.w};
+    const uint32_t bytes = valid * elem;
+    for (uint32_t b = 0; b < bytes; ++b) {
+        address[b] = static_cast<unsigned char>(words[b / 4] >> ((b & 3u) * 8));
     }
 }
 
-// Byte address of in-tile row `row` of tile column 0 in (plane, row / 16).
-__device__ __forceinline__ unsigned char* row_address(
-        const Operand& operand, uint64_t plane, uint64_t row, uint32_t elem) {
-    const uint64_t tile = (plane * operand.tile_rows + row / kTile) * operand.tile_cols;
+// Byte address of tile (row / 16, tile_col) of `plane`, at in-tile row row % 16.
+__device__ __forceinline__ unsigned char* piece_address(
+        const Operand& operand, uint64_t plane, uint64_t row, uint32_t tile_col, uint32_t elem) {
+    const uint64_t tile = (plane * operand.tile_rows + row / kTile) * operand.tile_cols + tile_col;
     return operand.base + tile * kTileSlots * elem + (row % kTile) * kTile * elem;
 }
+
+// Both movers give one warp one 16x16 tile: the tile of the result (embedding) or
+// of the source (append). Its 16 in-tile rows are 16 consecutive row pieces, so a
+// warp reads or writes whole contiguous tiles; the other side of the move is, per
+// row, one piece of 16 elements somewhere else (a table row, a shifted cache row).
 
 // ---- embedding ---------------------------------------------------------------
 
@@ -62,48 +60,76 @@ struct EmbeddingParams {
     Leading leading;    // leading space of indices/out
     RowGeometry row;
     uint32_t run;             // R: rows per plane
+    uint32_t run_tiles;       // ceil(R / 16)
     uint32_t index_bytes;     // 1, 2, 4 or 8
     uint32_t index_signed;
     uint64_t vocabulary;
-    uint64_t total_rows;      // planes * run
-    uint32_t chunks;          // vector chunks per row
+    uint64_t items;           // planes * run_tiles * ceil(tile_cols / kTilesPerItem)
     uint32_t* status;
 };
 
 __global__ void __launch_bounds__(kRowThreads)
 embedding_kernel(const EmbeddingParams p) {
-    const uint64_t items = p.total_rows * p.chunks;
-    for (uint64_t item = blockIdx.x; item < items; item += gridDim.x) {
-        const uint32_t chunk = static_cast<uint32_t>(item % p.chunks);
-        const uint64_t global_row = item / p.chunks;
-        const uint32_t r = static_cast<uint32_t>(global_row % p.run);
-        const uint64_t index = global_row / p.run;
-        // indices[b, 0, r]: tile column r / 16, in-tile row 0, column r % 16.
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint64_t warp = static_cast<uint64_t>(blockIdx.x) * kRowWarps + (threadIdx.x >> 5);
+    const uint64_t warps = static_cast<uint64_t>(gridDim.x) * kRowWarps;
+    const uint32_t elem = p.row.elem;
+    const uint32_t vectors_per_row = elem;                 // (16 * elem) / 16
+    const uint32_t per_vector = 16 / elem;
+    const uint32_t tile_vectors = kTile * vectors_per_row;
+    const uint32_t groups = (p.row.tile_cols + kTilesPerItem - 1) / kTilesPerItem;
+    for (uint64_t item = warp; item < p.items; item += warps) {
+        // item = ((index * run_tiles) + tr) * groups + group: kTilesPerItem neighbouring
+        // tiles of one band share the band's ids, decoded once per lane.
+        const uint32_t group = static_cast<uint32_t>(item % groups);
+        const uint64_t rest = item / groups;
+        const uint32_t tr = static_cast<uint32_t>(rest % p.run_tiles);
+        const uint64_t index = rest / p.run_tiles;
         const uint64_t index_plane = operand_plane(p.indices, p.leading, index);
-        const unsigned char* id_address = p.indices.base
-                + ((index_plane * p.indices.tile_rows) * p.indices.tile_cols + r / kTile)
-                        * static_cast<uint64_t>(kTileSlots) * p.index_bytes
-                + (r % kTile) * p.index_bytes;
-        uint64_t id = 0;
-        switch (p.index_bytes) {
-            case 1: id = *id_address; break;
-            case 2: id = *reinterpret_cast<const uint16_t*>(id_address); break;
-            case 4: id = *reinterpret_cast<const uint32_t*>(id_address); break;
-            default: id = *reinterpret_cast<const uint64_t*>(id_address); break;
+        const uint64_t out_plane = operand_plane(p.out, p.leading, index);
+        const uint32_t first_tc = group * kTilesPerItem;
+        const uint32_t tiles = min(kTilesPerItem, p.row.tile_cols - first_tc);
+        for (uint32_t k = lane; k < tile_vectors; k += 32) {
+            const uint32_t row_in_tile = k / vectors_per_row;
+            const uint32_t r = tr * kTile + row_in_tile;
+            if (r >= p.run) continue;
+            const uint32_t cv = k % vectors_per_row;
+            // indices[b, 0, r]: tile column r / 16, in-tile row 0, column r % 16.
+            const unsigned char* id_address = p.indices.base
+                    + ((index_plane * p.indices.tile_rows) * p.indices.tile_cols + r / kTile)
+                            * static_cast<uint64_t>(kTileSlots) * p.index_bytes
+                    + (r % kTile) * p.index_bytes;
+            uint64_t id = 0;
+            switch (p.index_bytes) {
+                case 1: id = *id_address; break;
+                case 2: id = *reinterpret_cast<const uint16_t*>(id_address); break;
+                case 4: id = *reinterpret_cast<const uint32_t*>(id_address); break;
+                default: id = *reinterpret_cast<const uint64_t*>(id_address); break;
+            }
+            const bool negative = p.index_signed && ((id >> (p.index_bytes * 8 - 1)) & 1u);
+            if (negative || id >= p.vocabulary) {
+                // Never form a table address from an invalid id
+                // (standard_tiled_embedding.inl:167-172); one report per row.
+                if (group == 0 && cv == 0) atomicOr(p.status, 1u);
+                continue;
+            }
+            const unsigned char* src = piece_address(p.table, p.table.plane0, id, first_tc, elem) + cv * 16;
+            unsigned char* dst = piece_address(p.out, out_plane, r, first_tc, elem) + cv * 16;
+            const size_t tile_bytes = static_cast<size_t>(kTileSlots) * elem;
+            uint4 value[kTilesPerItem];
+#pragma unroll
+            for (uint32_t t = 0; t < kTilesPerItem; ++t) {
+                if (t < tiles) value[t] = load_u4(src + t * tile_bytes);
+            }
+#pragma unroll
+            for (uint32_t t = 0; t < kTilesPerItem; ++t) {
+                if (t >= tiles) continue;
+                const uint32_t col = (first_tc + t) * kTile + cv * per_vector;
+                if (col >= p.row.cols) continue;
+                store_row_vector(dst + t * tile_bytes, value[t], min(per_vector, p.row.cols - col),
+                                 per_vector, elem);
+            }
         }
-        const bool negative = p.index_signed && ((id >> (p.index_bytes * 8 - 1)) & 1u);
-        if (negative || id >= p.vocabulary) {
-            // Never form a table address from an invalid id
-            // (standard_tiled_embedding.inl:167-172).
-            if (threadIdx.x == 0 && chunk == 0) atomicOr(p.status, 1u);
-            continue;
-        }
-        const uint32_t vector = chunk * kRowThreads + threadIdx.x;
-        if (vector >= p.row.row_vectors) continue;
-        const unsigned char* src = row_address(p.table, p.table.plane0, id, p.row.elem);
-        unsigned char* dst = row_address(
-                p.out, operand_plane(p.out, p.leading, index), r, p.row.elem);
-        move_row_vectors(src, dst, p.row, vector);
     }
 }
 
@@ -115,38 +141,64 @@ struct AppendParams {
     Leading leading;
     RowGeometry row;
     uint32_t rows;              // R: appended rows per plane
+    uint32_t row_tiles;         // ceil(R / 16)
     uint64_t dst_rows;          // C: cache length
     uint64_t a;                 // scalar offset (positions == nullptr)
     const uint32_t* positions;  // per index of the first leading axis, or nullptr
     uint64_t planes_per_batch;  // logical planes per index of the first leading axis
-    uint64_t total_rows;        // planes * R
-    uint32_t chunks;
+    uint64_t items;             // planes * row_tiles * ceil(tile_cols / kTilesPerItem)
     uint32_t* status;           // batched only
 };
 
 __global__ void __launch_bounds__(kRowThreads)
 cache_append_kernel(const AppendParams p) {
-    const uint64_t items = p.total_rows * p.chunks;
-    for (uint64_t item = blockIdx.x; item < items; item += gridDim.x) {
-        const uint32_t chunk = static_cast<uint32_t>(item % p.chunks);
-        const uint64_t global_row = item / p.chunks;
-        const uint32_t r = static_cast<uint32_t>(global_row % p.rows);
-        const uint64_t index = global_row / p.rows;
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint64_t warp = static_cast<uint64_t>(blockIdx.x) * kRowWarps + (threadIdx.x >> 5);
+    const uint64_t warps = static_cast<uint64_t>(gridDim.x) * kRowWarps;
+    const uint32_t elem = p.row.elem;
+    const uint32_t vectors_per_row = elem;
+    const uint32_t per_vector = 16 / elem;
+    const uint32_t tile_vectors = kTile * vectors_per_row;
+    const uint32_t groups = (p.row.tile_cols + kTilesPerItem - 1) / kTilesPerItem;
+    for (uint64_t item = warp; item < p.items; item += warps) {
+        const uint32_t group = static_cast<uint32_t>(item % groups);
+        const uint64_t rest = item / groups;
+        const uint32_t tr = static_cast<uint32_t>(rest % p.row_tiles);
+        const uint64_t index = rest / p.row_tiles;
         uint64_t a = p.a;
         if (p.positions != nullptr) {
             a = p.positions[index / p.planes_per_batch];
             if (a > p.dst_rows || p.rows > p.dst_rows - a) {
-                if (threadIdx.x == 0 && chunk == 0 && r == 0) atomicOr(p.status, 1u);
+                if (lane == 0 && group == 0 && tr == 0) atomicOr(p.status, 1u);
                 continue;
             }
         }
-        const uint32_t vector = chunk * kRowThreads + threadIdx.x;
-        if (vector >= p.row.row_vectors) continue;
-        const unsigned char* src = row_address(
-                p.src, operand_plane(p.src, p.leading, index), r, p.row.elem);
-        unsigned char* dst = row_address(
-                p.dst, operand_plane(p.dst, p.leading, index), a + r, p.row.elem);
-        move_row_vectors(src, dst, p.row, vector);
+        const uint64_t src_plane = operand_plane(p.src, p.leading, index);
+        const uint64_t dst_plane = operand_plane(p.dst, p.leading, index);
+        const uint32_t first_tc = group * kTilesPerItem;
+        const uint32_t tiles = min(kTilesPerItem, p.row.tile_cols - first_tc);
+        const size_t tile_bytes = static_cast<size_t>(kTileSlots) * elem;
+        for (uint32_t k = lane; k < tile_vectors; k += 32) {
+            const uint32_t row_in_tile = k / vectors_per_row;
+            const uint32_t r = tr * kTile + row_in_tile;
+            if (r >= p.rows) continue;
+            const uint32_t cv = k % vectors_per_row;
+            const unsigned char* src = piece_address(p.src, src_plane, r, first_tc, elem) + cv * 16;
+            unsigned char* dst = piece_address(p.dst, dst_plane, a + r, first_tc, elem) + cv * 16;
+            uint4 value[kTilesPerItem];
+#pragma unroll
+            for (uint32_t t = 0; t < kTilesPerItem; ++t) {
+                if (t < tiles) value[t] = load_u4(src + t * tile_bytes);
+            }
+#pragma unroll
+            for (uint32_t t = 0; t < kTilesPerItem; ++t) {
+                if (t >= tiles) continue;
+                const uint32_t col = (first_tc + t) * kTile + cv * per_vector;
+                if (col >= p.row.cols) continue;
+                store_row_vector(dst + t * tile_bytes, value[t], min(per_vector, p.row.cols - col),
+                                 per_vector, elem);
+            }
+        }
     }
 }
 
@@ -228,8 +280,8 @@ static int append_dispatch(const iomb_view* source, const iomb_view* destination
     p.a = a;
     p.positions = positions;
     p.planes_per_batch = fs.planes / source->dims[0];
-    p.total_rows = fs.planes * fs.rows;
-    p.chunks = (p.row.row_vectors + kRowThreads - 1) / kRowThreads;
+    p.row_tiles = static_cast<uint32_t>(fs.tile_rows);
+    p.items = fs.planes * fs.tile_rows * ((fs.tile_cols + kTilesPerItem - 1) / kTilesPerItem);
     p.status = status;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (positions != nullptr) {
@@ -237,7 +289,7 @@ static int append_dispatch(const iomb_view* source, const iomb_view* destination
             return check_launch("cache_append status reset");
         }
     }
-    const unsigned grid = grid_for(p.total_rows * p.chunks, 16);
+    const unsigned grid = grid_one_shot((p.items + kRowWarps - 1) / kRowWarps);
     cache_append_kernel<<<grid, kRowThreads, 0, s>>>(p);
     return check_launch("cache_append launch");
 }
@@ -309,8 +361,8 @@ extern "C" int iomb_embedding(const iomb_view* table, const iomb_view* indices,
     p.index_bytes = fi.bytes;
     p.index_signed = index_signed ? 1u : 0u;
     p.vocabulary = ft.rows;
-    p.total_rows = p.leading.planes * fo.rows;
-    p.chunks = (p.row.row_vectors + kRowThreads - 1) / kRowThreads;
+    p.run_tiles = static_cast<uint32_t>(fo.tile_rows);
+    p.items = p.leading.planes * fo.tile_rows * ((fo.tile_cols + kTilesPerItem - 1) / kTilesPerItem);
     p.status = status;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     // Reset in queue order, as the reference does before its kernel
@@ -318,7 +370,7 @@ extern "C" int iomb_embedding(const iomb_view* table, const iomb_view* indices,
     if (cudaMemsetAsync(status, 0, sizeof(uint32_t), s) != cudaSuccess) {
         return check_launch("embedding status reset");
     }
-    const unsigned grid = grid_for(p.total_rows * p.chunks, 16);
+    const unsigned grid = grid_one_shot((p.items + kRowWarps - 1) / kRowWarps);
     embedding_kernel<<<grid, kRowThreads, 0, s>>>(p);
     return check_launch("embedding launch");
 }
