@@ -399,6 +399,7 @@ def ops_table(device, queue, only=None, iters: int = 10) -> dict:
         """Median CUDA-event time of one launch; `inner` launches share one event
         pair for microsecond-scale operations (the figure then includes the host's
         issue rate through this Python layer, as a caller would see it)."""
+        torch.cuda.synchronize()    # input fills run on another stream: let them finish first
         for _ in range(3):
             token = launch()
         queue.wait(token)
@@ -632,6 +633,51 @@ def ops_table(device, queue, only=None, iters: int = 10) -> dict:
     return results
 
 
+def elementwise_sweep(device, queue, iters: int = 5) -> dict:
+    """BASELINE config 3: I32 ADD, F32 MUL and BF16 ADD with full-shape, row-broadcast
+    [1,N] and column-broadcast [M,1] operands over 2^16 .. 2^30 elements, doubling
+    (shape [E / 2048, 2048]). Device-resident GB/s of algorithmic bytes per size;
+    sizes below the 126 MB L2 run out of cache and are reported as they are."""
+    import torch
+
+    from iom_b200.tensor import DataType, TensorSpec
+
+    n = 2048
+    results = {}
+    for dtype, name, b, op in ((DataType.I32, "add_i32", 4, "add"), (DataType.F32, "mul_f32", 4, "mul"),
+                               (DataType.BF16, "add_bf16", 2, "add")):
+        for exponent in range(16, 31):
+            elements = 1 << exponent
+            m = elements // n
+            tensors = [device.create_tensor(TensorSpec(shape, dtype))
+                       for shape in ((m, n), (m, n), (m, n), (1, n), (m, 1))]
+            for t in tensors:
+                t.storage().copy_(torch.randint(0, 64, (t.storage_nbytes,), device=device.torch_device,
+                                                dtype=torch.uint8))
+            x, y, o, row, col = tensors
+            fn = getattr(queue, op)
+            torch.cuda.synchronize()    # the fills above run on another stream
+            for form, rhs, nbytes in (("full", y, 3 * elements * b), ("row", row, (2 * elements + n) * b),
+                                      ("col", col, (2 * elements + m) * b)):
+                for _ in range(2):
+                    token = fn(x.view(), rhs.view(), o.view())
+                queue.wait(token)
+                pairs = []
+                for _ in range(iters):
+                    a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a0.record(queue.stream)
+                    token = fn(x.view(), rhs.view(), o.view())
+                    a1.record(queue.stream)
+                    pairs.append((a0, a1))
+                queue.wait(token)
+                torch.cuda.synchronize()
+                ms = sorted(p[0].elapsed_time(p[1]) for p in pairs)[len(pairs) // 2]
+                results[f"{name}_{form}_2^{exponent}"] = {"GB/s": nbytes / ms / 1e6, "us": ms * 1e3}
+            for t in tensors:
+                t.close()
+    return results
+
+
 # ---- CPU side: the reference's own CPU backend (or the oracle port) ---------------
 
 def _cpu_arm(threads: int, repeats: int, warmup: int) -> dict:
@@ -765,6 +811,8 @@ def main() -> None:
     parser.add_argument("--op", default=None,
                         help="run one row of the per-operation table and print it "
                              "(for profiler captures), e.g. --op rmsnorm_c5shard")
+    parser.add_argument("--sweep", action="store_true",
+                        help="run the elementwise size sweep (BASELINE config 3) and print its table")
     parser.add_argument("--no-e2e", action="store_true",
                         help="skip the host-buffer leg (used for profiler captures)")
     parser.add_argument("--planes", type=int, default=PLANES,
@@ -773,6 +821,14 @@ def main() -> None:
     args = parser.parse_args()
     configure(args.planes)
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.sweep:
+        from iom_b200.device import DeviceMemoryConfig, make_b200_device
+        device = make_b200_device(0, DeviceMemoryConfig(14 << 30))
+        queue = device.create_ops()
+        print(json.dumps({"sweep": "BASELINE config 3, [E/2048, 2048], E = 2^16 .. 2^30",
+                          "result": elementwise_sweep(device, queue, iters=max(1, min(args.steps, 7)))}))
+        queue.close()
+        return
     if args.op is not None:
         import torch
 
