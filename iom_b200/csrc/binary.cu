@@ -77,14 +77,21 @@ binary_linear_kernel(const uint4* __restrict__ lhs, const uint4* __restrict__ rh
         const uint64_t base = chunk * kChunk + threadIdx.x;
         uint4 a[kLinearUnroll], b[kLinearUnroll];
         if (base + kLinearThreads * (kLinearUnroll - 1) < vectors) {
+            // A whole chunk: each thread moves pairs of neighbouring vectors with
+            // 256-bit accesses (streams start on tile boundaries, so pairs are
+            // 32-byte aligned), half the load/store instructions of the 128-bit form.
+            const uint64_t pair = (chunk * kChunk) / 2 + threadIdx.x;
 #pragma unroll
-            for (int u = 0; u < kLinearUnroll; ++u) {
-                a[u] = load_u4_stream(lhs + base + u * kLinearThreads);
-                b[u] = load_u4_stream(rhs + base + u * kLinearThreads);
+            for (int u = 0; u < kLinearUnroll / 2; ++u) {
+                const uint64_t at = 2 * (pair + u * kLinearThreads);
+                load_u8_stream(lhs + at, &a[2 * u], &a[2 * u + 1]);
+                load_u8_stream(rhs + at, &b[2 * u], &b[2 * u + 1]);
             }
 #pragma unroll
-            for (int u = 0; u < kLinearUnroll; ++u) {
-                store_u4_stream(out + base + u * kLinearThreads, apply_vector<L, OP>(a[u], b[u]));
+            for (int u = 0; u < kLinearUnroll / 2; ++u) {
+                const uint64_t at = 2 * (pair + u * kLinearThreads);
+                store_u8_stream(out + at, apply_vector<L, OP>(a[2 * u], b[2 * u]),
+                                apply_vector<L, OP>(a[2 * u + 1], b[2 * u + 1]));
             }
         } else {
             for (int u = 0; u < kLinearUnroll; ++u) {
@@ -124,30 +131,38 @@ binary_stream_bc_kernel(const StreamBcParams p) {
     constexpr int ELEM = L == Leaf::BF16 ? 2 : 4;
     constexpr uint32_t kTileVectors = kTileSlots * ELEM / 16;     // 32 or 64
     constexpr uint32_t kVectorsPerRow = kTile * ELEM / 16;        // 2 or 4
-    constexpr uint64_t kChunk = static_cast<uint64_t>(kLinearThreads) * kLinearUnroll;
-    const uint64_t chunks = (p.vectors + kChunk - 1) / kChunk;
+    // Threads move pairs of neighbouring vectors (32 bytes, never across a tile row)
+    // with 256-bit accesses: kLinearUnroll / 2 pairs per thread, one 16 KiB chunk per CTA.
+    constexpr uint32_t kTilePairs = kTileVectors / 2;             // 16 or 32
+    constexpr uint32_t kPairsPerRow = kVectorsPerRow / 2;         // 1 or 2
+    constexpr int kPairUnroll = kLinearUnroll / 2;
+    constexpr uint64_t kChunk = static_cast<uint64_t>(kLinearThreads) * kPairUnroll;
+    const uint64_t pairs = p.vectors / 2;                         // whole tiles: always even
+    const uint64_t chunks = (pairs + kChunk - 1) / kChunk;
     for (uint64_t chunk = blockIdx.x; chunk < chunks; chunk += gridDim.x) {
         const uint64_t base = chunk * kChunk + threadIdx.x;
-        uint4 a[kLinearUnroll], b[kLinearUnroll];
+        uint4 a[kPairUnroll][2], b[kPairUnroll][2];
 #pragma unroll
-        for (int u = 0; u < kLinearUnroll; ++u) {
+        for (int u = 0; u < kPairUnroll; ++u) {
             const uint64_t index = base + u * kLinearThreads;
-            if (index < p.vectors) {
-                a[u] = load_u4_stream(p.big + index);
-                const uint32_t tile = static_cast<uint32_t>(index / kTileVectors);
-                const uint32_t in_tile = static_cast<uint32_t>(index % kTileVectors);
+            if (index < pairs) {
+                load_u8_stream(p.big + 2 * index, &a[u][0], &a[u][1]);
+                const uint32_t tile = static_cast<uint32_t>(index / kTilePairs);
+                const uint32_t in_tile = static_cast<uint32_t>(index % kTilePairs);
                 if constexpr (!COLUMN) {
                     const uint32_t tc = p.cols_shift < 32 ? tile & ((1u << p.cols_shift) - 1u)
                                                           : tile % p.tile_cols;
-                    b[u] = __ldg(reinterpret_cast<const uint4*>(
+                    const uint4* row0 = reinterpret_cast<const uint4*>(
                             p.small + static_cast<size_t>(tc) * kTileSlots * ELEM
-                            + (in_tile % kVectorsPerRow) * 16));
+                            + (in_tile % kPairsPerRow) * 32);
+                    b[u][0] = __ldg(row0);
+                    b[u][1] = __ldg(row0 + 1);
                 } else {
                     uint32_t band = p.cols_shift < 32 ? tile >> p.cols_shift : tile / p.tile_cols;
                     if (!p.single_plane) band %= p.tile_rows;
                     const unsigned char* cell = p.small
                             + static_cast<size_t>(band) * kTileSlots * ELEM
-                            + (in_tile / kVectorsPerRow) * kTile * ELEM;
+                            + (in_tile / kPairsPerRow) * kTile * ELEM;
                     uint32_t value;
                     if constexpr (ELEM == 4) {
                         value = __ldg(reinterpret_cast<const uint32_t*>(cell));
@@ -155,17 +170,20 @@ binary_stream_bc_kernel(const StreamBcParams p) {
                         const uint32_t half = __ldg(reinterpret_cast<const uint16_t*>(cell));
                         value = half | (half << 16);
                     }
-                    b[u] = make_uint4(value, value, value, value);
+                    b[u][0] = make_uint4(value, value, value, value);
+                    b[u][1] = b[u][0];
                 }
             }
         }
 #pragma unroll
-        for (int u = 0; u < kLinearUnroll; ++u) {
+        for (int u = 0; u < kPairUnroll; ++u) {
             const uint64_t index = base + u * kLinearThreads;
-            if (index < p.vectors) {
-                store_u4_stream(p.out + index,
-                                SMALL_IS_LHS ? apply_vector<L, OP>(b[u], a[u])
-                                             : apply_vector<L, OP>(a[u], b[u]));
+            if (index < pairs) {
+                store_u8_stream(p.out + 2 * index,
+                                SMALL_IS_LHS ? apply_vector<L, OP>(b[u][0], a[u][0])
+                                             : apply_vector<L, OP>(a[u][0], b[u][0]),
+                                SMALL_IS_LHS ? apply_vector<L, OP>(b[u][1], a[u][1])
+                                             : apply_vector<L, OP>(a[u][1], b[u][1]));
             }
         }
     }

@@ -51,11 +51,17 @@ copy_linear_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, uint6
     for (uint64_t chunk = blockIdx.x; chunk < chunks; chunk += gridDim.x) {
         const uint64_t base = chunk * kChunk + threadIdx.x;
         if (base + kCopyThreads * (kCopyUnroll - 1) < vectors) {
+            // A whole chunk: pairs of neighbouring vectors as 256-bit accesses.
             uint4 v[kCopyUnroll];
+            const uint64_t pair = (chunk * kChunk) / 2 + threadIdx.x;
 #pragma unroll
-            for (int u = 0; u < kCopyUnroll; ++u) v[u] = load_u4_stream(src + base + u * kCopyThreads);
+            for (int u = 0; u < kCopyUnroll / 2; ++u) {
+                load_u8_stream(src + 2 * (pair + u * kCopyThreads), &v[2 * u], &v[2 * u + 1]);
+            }
 #pragma unroll
-            for (int u = 0; u < kCopyUnroll; ++u) store_u4_stream(dst + base + u * kCopyThreads, v[u]);
+            for (int u = 0; u < kCopyUnroll / 2; ++u) {
+                store_u8_stream(dst + 2 * (pair + u * kCopyThreads), v[2 * u], v[2 * u + 1]);
+            }
         } else {
             for (int u = 0; u < kCopyUnroll; ++u) {
                 const uint64_t index = base + u * kCopyThreads;
@@ -88,8 +94,7 @@ cast_linear_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, uint6
                 if (whole || index < groups) {
                     uint4 lo, hi;
                     widen_vector(in[u], &lo, &hi);
-                    store_u4_stream(dst + 2 * index, lo);
-                    store_u4_stream(dst + 2 * index + 1, hi);
+                    store_u8_stream(dst + 2 * index, lo, hi);
                 }
             }
         } else {
@@ -98,8 +103,7 @@ cast_linear_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, uint6
             for (int u = 0; u < kBatch; ++u) {
                 const uint64_t index = base + u * kCopyThreads;
                 if (whole || index < groups) {
-                    lo[u] = load_u4_stream(src + 2 * index);
-                    hi[u] = load_u4_stream(src + 2 * index + 1);
+                    load_u8_stream(src + 2 * index, &lo[u], &hi[u]);
                 }
             }
 #pragma unroll
