@@ -328,7 +328,7 @@ def run_ours(args) -> dict:
             "scaling": "weak",
             "vs_baseline": None,
             "dtype": "f32 accumulate, bf16 storage",
-            "data": "synthetic (seeded normal, BASELINE config 2 distributions)",
+            "data": "synthetic (seeded normal, the TinyLlama prefill configuration's distributions)",
             "config": {"workload": WORKLOAD, "launches_per_step": 1,
                        "algorithmic_bytes_per_step": ALGORITHMIC_BYTES,
                        "l2": f"inputs larger than L2 ({ALGORITHMIC_BYTES / 1e9:.2f} GB touched "
@@ -539,7 +539,7 @@ def ops_table(device, queue, only=None, iters: int = 10) -> dict:
         release()
     if only is None or only in ("embedding_decode", "cache_append_decode_batched",
                                 "cache_append_decode_64calls", "cast_logits"):
-        # Decode-step data movement, TinyLlama geometry (BASELINE config 4): microseconds.
+        # Decode-step data movement, TinyLlama geometry (the decode-step configuration): microseconds.
         table = tensor((32000, 2048), DataType.BF16)
         ids = device.create_tensor(TensorSpec((1, 64), DataType.U32))
         made.append(ids)
@@ -634,7 +634,7 @@ def ops_table(device, queue, only=None, iters: int = 10) -> dict:
 
 
 def elementwise_sweep(device, queue, iters: int = 5) -> dict:
-    """BASELINE config 3: I32 ADD, F32 MUL and BF16 ADD with full-shape, row-broadcast
+    """The mixed elementwise sweep: I32 ADD, F32 MUL and BF16 ADD with full-shape, row-broadcast
     [1,N] and column-broadcast [M,1] operands over 2^16 .. 2^30 elements, doubling
     (shape [E / 2048, 2048]). Device-resident GB/s of algorithmic bytes per size;
     sizes below the 126 MB L2 run out of cache and are reported as they are."""
@@ -790,7 +790,7 @@ def run_reference(args) -> dict | None:
         "scaling": "weak",
         "vs_baseline": None,
         "dtype": "f32 accumulate, bf16 storage",
-        "data": "synthetic (seeded normal, BASELINE config 2 distributions)",
+        "data": "synthetic (seeded normal, the TinyLlama prefill configuration's distributions)",
         "config": {"workload": WORKLOAD, "sample": cpu["sample"]},
         "cpu_baseline": {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")},
         "e2e": {"value": cpu["value"], "unit": "GB/s", "h2d_bytes_per_step": 0,
@@ -812,7 +812,7 @@ def main() -> None:
                         help="run one row of the per-operation table and print it "
                              "(for profiler captures), e.g. --op rmsnorm_c5shard")
     parser.add_argument("--sweep", action="store_true",
-                        help="run the elementwise size sweep (BASELINE config 3) and print its table")
+                        help="run the elementwise size sweep and print its table")
     parser.add_argument("--no-e2e", action="store_true",
                         help="skip the host-buffer leg (used for profiler captures)")
     parser.add_argument("--planes", type=int, default=PLANES,
@@ -825,7 +825,7 @@ def main() -> None:
         from iom_b200.device import DeviceMemoryConfig, make_b200_device
         device = make_b200_device(0, DeviceMemoryConfig(14 << 30))
         queue = device.create_ops()
-        print(json.dumps({"sweep": "BASELINE config 3, [E/2048, 2048], E = 2^16 .. 2^30",
+        print(json.dumps({"sweep": "mixed elementwise sweep, [E/2048, 2048], E = 2^16 .. 2^30",
                           "result": elementwise_sweep(device, queue, iters=max(1, min(args.steps, 7)))}))
         queue.close()
         return
