@@ -37,5 +37,21 @@ oid add_rmsnorm(DeviceOps& queue, const TensorView& x, const TensorView& residua
 oid silu_mul(DeviceOps& queue, const TensorView& x, const TensorView& up, TensorView* activated,
              TensorView& out);
 
+// BF16 <-> F32 conversion between views of identical logical shape (codec decode /
+// encode: exact widening, RNE narrowing, canonical NaN).
+oid cast(DeviceOps& queue, const TensorView& source, TensorView& destination);
+
+// cache_append with one row offset per index of the first leading axis (a decode step's
+// K or V of every sequence in one launch). `positions` (dims[0] values) and `status`
+// (one word: reset to 0, set to 1 when some offset overruns its cache, that sequence
+// being skipped) are device addresses the caller owns until the token completes.
+oid cache_append_batched(DeviceOps& queue, const TensorView& source, TensorView& destination,
+                         const std::uint32_t* positions, std::uint32_t* status);
+
+// Whole-view FP32 sum of squares with a launch-independent order into the device float at
+// `result`; `scratch` is sumsq_scratch_bytes() bytes of device memory.
+oid sumsq(DeviceOps& queue, const TensorView& x, void* scratch, float* result);
+[[nodiscard]] std::size_t sumsq_scratch_bytes();
+
 }  // namespace b200
 }  // namespace iom

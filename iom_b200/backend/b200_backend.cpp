@@ -463,6 +463,50 @@ public:
         }
     }
 
+    // Extension entries (see iom_b200_backend.hpp): one admission / submission /
+    // failure-mapping path for calls that take raw device addresses besides views.
+    template <typename Launch>
+    oid extension(std::initializer_list<const TensorView*> views, Launch launch) {
+        try {
+            validate_views(queue_device(), views);
+            std::lock_guard<std::mutex> order(submission_order_mutex_);
+            return submit([this, launch](std::uint64_t sequence) {
+                device_->activate();
+                check_status(launch(stream_));
+                retire(sequence, [] {}, nullptr);
+            });
+        } catch (const std::invalid_argument&) {
+            return to_oid(OidError::InvalidArgument);
+        } catch (const detail::UnsupportedOperation&) {
+            return to_oid(OidError::Unsupported);
+        } catch (const std::bad_alloc&) {
+            return to_oid(OidError::ResourceExhausted);
+        } catch (...) {
+            return to_oid(OidError::DeviceError);
+        }
+    }
+
+    oid cast(const TensorView& source, TensorView& destination) {
+        const iomb_view vs = to_view(source), vd = to_view(destination);
+        return extension({&source, &destination},
+                         [vs, vd](cudaStream_t stream) { return iomb_cast(&vs, &vd, stream); });
+    }
+
+    oid cache_append_batched(const TensorView& source, TensorView& destination,
+                             const std::uint32_t* positions, std::uint32_t* status) {
+        const iomb_view vs = to_view(source), vd = to_view(destination);
+        return extension({&source, &destination}, [vs, vd, positions, status](cudaStream_t stream) {
+            return iomb_cache_append_batched(&vs, &vd, positions, status, stream);
+        });
+    }
+
+    oid sumsq(const TensorView& x, void* scratch, float* result) {
+        const iomb_view vx = to_view(x);
+        return extension({&x}, [vx, scratch, result](cudaStream_t stream) {
+            return iomb_sumsq(&vx, scratch, result, stream);
+        });
+    }
+
 protected:
     [[nodiscard]] std::string_view backend_label() const noexcept override { return "B200"; }
 
@@ -777,6 +821,27 @@ oid add_rmsnorm(DeviceOps& queue, const TensorView& x, const TensorView& residua
     if (native == nullptr) return to_oid(OidError::InvalidArgument);
     return native->add_rmsnorm(x, residual, scale, sum, out, eps);
 }
+
+oid cast(DeviceOps& queue, const TensorView& source, TensorView& destination) {
+    auto* native = dynamic_cast<B200Queue*>(&queue);
+    if (native == nullptr) return to_oid(OidError::InvalidArgument);
+    return native->cast(source, destination);
+}
+
+oid cache_append_batched(DeviceOps& queue, const TensorView& source, TensorView& destination,
+                         const std::uint32_t* positions, std::uint32_t* status) {
+    auto* native = dynamic_cast<B200Queue*>(&queue);
+    if (native == nullptr) return to_oid(OidError::InvalidArgument);
+    return native->cache_append_batched(source, destination, positions, status);
+}
+
+oid sumsq(DeviceOps& queue, const TensorView& x, void* scratch, float* result) {
+    auto* native = dynamic_cast<B200Queue*>(&queue);
+    if (native == nullptr) return to_oid(OidError::InvalidArgument);
+    return native->sumsq(x, scratch, result);
+}
+
+std::size_t sumsq_scratch_bytes() { return static_cast<std::size_t>(iomb_sumsq_scratch_bytes()); }
 
 oid silu_mul(DeviceOps& queue, const TensorView& x, const TensorView& up, TensorView* activated,
              TensorView& out) {

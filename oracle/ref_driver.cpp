@@ -399,6 +399,52 @@ std::int64_t iomref_silu_mul(void* queue, void* x, void* up, void* activated, vo
     return iom::b200::silu_mul(ops_of(queue), view_of(x), view_of(up),
                                activated != nullptr ? &view_of(activated) : nullptr, view_of(out));
 }
+
+std::int64_t iomref_cast(void* queue, void* source, void* destination) {
+    return iom::b200::cast(ops_of(queue), view_of(source), view_of(destination));
+}
+
+// positions: host array of `count` row offsets; staged into a workspace of the device
+// together with the status word. Returns the token; *status_out receives the status
+// word after completion.
+std::int64_t iomref_cache_append_batched(void* queue, void* source, void* destination,
+                                         const std::uint32_t* positions, std::uint32_t count,
+                                         std::uint32_t* status_out) {
+    std::uint32_t* device_words = nullptr;
+    if (cudaMalloc(reinterpret_cast<void**>(&device_words), (count + 8) * sizeof(std::uint32_t))
+            != cudaSuccess) {
+        return -4;
+    }
+    cudaMemcpy(device_words + 8, positions, count * sizeof(std::uint32_t), cudaMemcpyHostToDevice);
+    const std::int64_t token = iom::b200::cache_append_batched(
+            ops_of(queue), view_of(source), view_of(destination), device_words + 8, device_words);
+    if (token > 0) {
+        try {
+            ops_of(queue).wait(token);
+        } catch (...) {
+        }
+        cudaMemcpy(status_out, device_words, sizeof(std::uint32_t), cudaMemcpyDeviceToHost);
+    }
+    cudaFree(device_words);
+    return token;
+}
+
+std::int64_t iomref_sumsq(void* queue, void* x, float* value_out) {
+    void* scratch = nullptr;
+    if (cudaMalloc(&scratch, iom::b200::sumsq_scratch_bytes() + 32) != cudaSuccess) return -4;
+    float* result = reinterpret_cast<float*>(static_cast<unsigned char*>(scratch)
+                                             + iom::b200::sumsq_scratch_bytes());
+    const std::int64_t token = iom::b200::sumsq(ops_of(queue), view_of(x), scratch, result);
+    if (token > 0) {
+        try {
+            ops_of(queue).wait(token);
+        } catch (...) {
+        }
+        cudaMemcpy(value_out, result, sizeof(float), cudaMemcpyDeviceToHost);
+    }
+    cudaFree(scratch);
+    return token;
+}
 #endif
 
 }  // extern "C"

@@ -213,6 +213,11 @@ class Reference:
                 "iomref_tensor_download": (ctypes.c_int, [vp, vp, u64]),
                 "iomref_add_rmsnorm": (ctypes.c_int64, [vp, vp, vp, vp, vp, vp, ctypes.c_float]),
                 "iomref_silu_mul": (ctypes.c_int64, [vp, vp, vp, vp, vp]),
+                "iomref_cast": (ctypes.c_int64, [vp, vp, vp]),
+                "iomref_cache_append_batched": (ctypes.c_int64, [vp, vp, vp, ctypes.POINTER(ctypes.c_uint32),
+                                                                 ctypes.c_uint32,
+                                                                 ctypes.POINTER(ctypes.c_uint32)]),
+                "iomref_sumsq": (ctypes.c_int64, [vp, vp, ctypes.POINTER(ctypes.c_float)]),
             })
         for name, (restype, argtypes) in spec.items():
             fn = getattr(lib, name)

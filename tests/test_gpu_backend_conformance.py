@@ -229,6 +229,58 @@ def test_rope(pair, dtype, shape, a):
     assert gpu.lib.iomref_rope(gpu.queue, x[1].view().handle, out[1].view().handle, 0, 0.5) == -1
 
 
+def test_extension_entries_of_the_cpp_backend(pair):
+    """cast, batched cache_append and sumsq through the C++ backend's extension functions:
+    cast against the oracle's codec, the batched append against one reference CPU
+    cache_append per sequence, the sum of squares against FP64."""
+    import ctypes
+    from support import HostTensor, abi, oracle
+    cpu, gpu = pair
+    rng = np.random.default_rng(61)
+    payload = random_payload(rng, (3, 17, 40), DataType.BF16, "normal")
+    narrow = gpu.tensor((3, 17, 40), DataType.BF16)
+    narrow.view().from_host(payload)
+    wide = gpu.tensor((3, 17, 40), DataType.F32)
+    assert gpu.run(gpu.lib.iomref_cast(gpu.queue, narrow.view().handle, wide.view().handle)) == 0, gpu.error()
+    host_narrow, host_wide = HostTensor((3, 17, 40), DataType.BF16), HostTensor((3, 17, 40), DataType.F32)
+    host_narrow.view().copy_from_host(payload)
+    assert oracle().iomo_cast(abi(host_narrow.view()), abi(host_wide.view())) == 0
+    assert np.array_equal(wide.read(), host_wide.storage)
+    back = gpu.tensor((3, 17, 40), DataType.BF16)
+    assert gpu.run(gpu.lib.iomref_cast(gpu.queue, wide.view().handle, back.view().handle)) == 0
+    assert np.array_equal(back.read(), narrow.read())
+
+    # batched append: 6 sequences, 2 heads, one new row each, per-sequence positions
+    source = both(pair, (6, 2, 1, 48), DataType.BF16, rng, kind="normal")
+    cache = both(pair, (6, 2, 40, 48), DataType.BF16, rng, kind="normal")
+    positions = np.array([0, 39, 7, 16, 15, 31], dtype=np.uint32)
+    status = ctypes.c_uint32(9)
+    token = gpu.lib.iomref_cache_append_batched(
+        gpu.queue, source[1].view().handle, cache[1].view().handle,
+        positions.ctypes.data_as(ctypes.POINTER(ctypes.c_uint32)), 6, ctypes.byref(status))
+    assert token > 0 and status.value == 0
+    for b in range(6):
+        sv = source[0].view().select(0, b)
+        cv = cache[0].view().select(0, b)
+        assert cpu.run(cpu.lib.iomref_cache_append(cpu.queue, sv.handle, cv.handle, int(positions[b]))) == 0
+    same(cache)
+    positions[2] = 40                         # overruns: reported, that sequence skipped
+    before = cache[1].read().copy()
+    token = gpu.lib.iomref_cache_append_batched(
+        gpu.queue, source[1].view().handle, cache[1].view().handle,
+        positions.ctypes.data_as(ctypes.POINTER(ctypes.c_uint32)), 6, ctypes.byref(status))
+    assert token > 0 and status.value == 1
+    assert np.array_equal(cache[1].read(), before)   # the other rows were rewritten with the same bytes
+
+    x = gpu.tensor((5, 33, 70), DataType.F32)
+    values = rng.standard_normal((5, 33, 70)).astype(np.float32)
+    x.view().from_host(values)
+    result = ctypes.c_float(0.0)
+    assert gpu.lib.iomref_sumsq(gpu.queue, x.view().handle, ctypes.byref(result)) > 0
+    truth = float(np.sum(values.astype(np.float64) ** 2))
+    assert abs(result.value - truth) <= 1e-6 * truth
+
+
 def test_host_transfers_and_fused_extension(pair):
     cpu, gpu = pair
     rng = np.random.default_rng(10)
