@@ -292,6 +292,56 @@ int iomb_sumsq_static(const iomb_view* x, float* result, void* stream);
 int iomb_scatter(const iomb_view* destination, const void* staging, void* stream);
 int iomb_gather(const iomb_view* source, void* staging, void* stream);
 
+/*
+ * The stages of causal grouped-query attention that are not matrix products. They work on
+ * the two fixed workspace segments of the reference's CUDA backend
+ * (SdpaNonmatrixRequest, src/cuda/sdpa_nonmatrix_request.hpp:22-49): `scores`, FP32
+ * [planes, Hq, Rp, Lp], and `probability`, BF16 of the same extents, Rp = pad16(R),
+ * Lp = pad16(L), row-major, both 32-byte aligned and disjoint. Row r of every head sees the
+ * tokens t < min(L, a + r + 1). Admission as validate_geometry
+ * (src/cuda/sdpa_nonmatrix.cu:82-229): nonzero extents, L <= C, a < C, R <= C - a,
+ * Hq % Hkv == 0.
+ */
+typedef struct iomb_sdpa_stages {
+    float* scores;
+    void* probability;
+    uint64_t planes, Hq, Hkv, R, C, D, a, L;
+} iomb_sdpa_stages;
+
+/*
+ * scores[p,h,r,t] = scores[p,h,r,t] * (1 / sqrtf(D)) for the visible tokens, a product that
+ * is zero stored as +0; every other cell (masked, t >= L, r >= R) keeps its bytes.
+ * Replaces launch_sdpa_scale_mask / scale_mask_kernel (src/cuda/sdpa_nonmatrix.cu:347-371).
+ */
+int iomb_sdpa_scale_mask(const iomb_sdpa_stages* stages, void* stream);
+
+/*
+ * probability[p,h,r,t] for t < L from the scores of the visible tokens, everything else
+ * untouched. Replaces launch_sdpa_softmax / softmax_kernel (src/cuda/sdpa_nonmatrix.cu:373-477)
+ * with the same FP32 steps in the same order: a NaN among the visible scores, or only
+ * -inf, makes the visible cells the quiet NaN 0x7FC0; +inf scores share 1/count and the
+ * rest are +0; otherwise m = max of the finite scores, sum = expf(s - m) added in token
+ * order starting from +0, cell = BF16_RNE(expf(s - m) / sum) with true division; a
+ * subnormal quotient rounds to a subnormal BF16. Masked cells t < L are +0.
+ */
+int iomb_sdpa_softmax(const iomb_sdpa_stages* stages, void* stream);
+
+/*
+ * Both stages in one pass over the scores: results equal iomb_sdpa_scale_mask followed by
+ * iomb_sdpa_softmax bit for bit. With keep_scores != 0 the scaled scores are also stored
+ * (the workspace then equals the two-stage pipeline's); with 0 the scores segment is only
+ * read. No counterpart in the reference, which launches the two stages separately.
+ */
+int iomb_sdpa_scale_mask_softmax(const iomb_sdpa_stages* stages, int keep_scores, void* stream);
+
+/*
+ * Canonical stored zeros and NaNs in the merged attention output `out`, a BF16 view
+ * [B..., R, Hq*D]: -0 becomes +0, every NaN becomes 0x7FC0; tile padding is not touched.
+ * Replaces launch_sdpa_canonicalize_output / canonicalize_output_kernel
+ * (src/cuda/sdpa_nonmatrix.cu:479-507).
+ */
+int iomb_sdpa_canonicalize_output(const iomb_view* out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -29,6 +29,18 @@ class IombView(ctypes.Structure):
     ]
 
 
+class IombSdpaStages(ctypes.Structure):
+    """struct iomb_sdpa_stages."""
+
+    _fields_ = [
+        ("scores", ctypes.c_void_p),
+        ("probability", ctypes.c_void_p),
+        ("planes", ctypes.c_uint64), ("Hq", ctypes.c_uint64), ("Hkv", ctypes.c_uint64),
+        ("R", ctypes.c_uint64), ("C", ctypes.c_uint64), ("D", ctypes.c_uint64),
+        ("a", ctypes.c_uint64), ("L", ctypes.c_uint64),
+    ]
+
+
 # name -> (restype, argtypes); every symbol include/iom_b200.h declares.
 _VIEW = ctypes.POINTER(IombView)
 _U64P = ctypes.POINTER(ctypes.c_uint64)
@@ -59,6 +71,11 @@ PROTOTYPES = {
     "iomb_sumsq_static": (ctypes.c_int, [_VIEW, ctypes.c_void_p, ctypes.c_void_p]),
     "iomb_scatter": (ctypes.c_int, [_VIEW, ctypes.c_void_p, ctypes.c_void_p]),
     "iomb_gather": (ctypes.c_int, [_VIEW, ctypes.c_void_p, ctypes.c_void_p]),
+    "iomb_sdpa_scale_mask": (ctypes.c_int, [ctypes.POINTER(IombSdpaStages), ctypes.c_void_p]),
+    "iomb_sdpa_softmax": (ctypes.c_int, [ctypes.POINTER(IombSdpaStages), ctypes.c_void_p]),
+    "iomb_sdpa_scale_mask_softmax": (ctypes.c_int, [ctypes.POINTER(IombSdpaStages), ctypes.c_int,
+                                                    ctypes.c_void_p]),
+    "iomb_sdpa_canonicalize_output": (ctypes.c_int, [_VIEW, ctypes.c_void_p]),
 }
 
 _library = None

@@ -16,7 +16,7 @@ from pathlib import Path
 PACKAGE_DIR = Path(__file__).resolve().parent
 CSRC = PACKAGE_DIR / "csrc"
 LIBRARY = PACKAGE_DIR / "libiom_b200.so"
-SOURCES = ["host.cu", "binary.cu", "rmsnorm.cu", "copy.cu", "gather.cu", "sumsq.cu", "silu.cu", "rope.cu"]
+SOURCES = ["host.cu", "binary.cu", "rmsnorm.cu", "copy.cu", "gather.cu", "sumsq.cu", "silu.cu", "rope.cu", "sdpa.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

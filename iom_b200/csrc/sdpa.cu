@@ -1,0 +1,484 @@
+// The stages of causal grouped-query attention that are not matrix products:
+// scale + causal mask, row softmax, and canonical zeros/NaNs of the merged output.
+//
+// Reference: src/cuda/sdpa_nonmatrix.cu:347-507 runs one thread per score (scale/mask),
+// one thread per row walking its tokens four times (softmax) and one thread per output
+// element (canonicalisation). Here a row group is one CTA's job: 32 rows, whose sums of
+// exponentials are the 32 lanes of one warp adding in token order (the order is part of
+// the result), fed through shared memory by eight warps that evaluate expf, so the
+// additions overlap the exponentials and the global loads; every global access is a
+// coalesced row segment.
+//
+// Workspace layout (src/cuda/sdpa_nonmatrix_request.hpp:22-49): scores FP32 and
+// probability BF16, both [planes, Hq, Rp, Lp] row-major with Rp = pad16(R), Lp = pad16(L),
+// so every row starts on a 64-byte (scores) / 32-byte (probability) boundary.
+#include "host.hpp"
+
+#include <math.h>
+
+namespace iomb {
+
+namespace {
+
+constexpr int kGroupRows = 32;        // rows of one CTA job = lanes of the summing warp
+constexpr int kChunk = 128;           // tokens of one shared-memory tile
+constexpr int kExpWarps = 8;          // warps that fill the tiles (4 rows each)
+constexpr int kSoftmaxWarps = kExpWarps + 1;
+constexpr int kSoftmaxThreads = kSoftmaxWarps * 32;
+constexpr int kSoftmaxCtasPerSm = 3;  // row groups in flight stay inside L2 for the re-reads
+constexpr int kScaleThreads = 256;
+
+// Row classes of the special-value policy (src/cuda/sdpa_nonmatrix.cu:393-446).
+constexpr uint32_t kRowOrdinary = 0;
+constexpr uint32_t kRowNan = 1;       // a NaN among the visible scores, or only -inf
+constexpr uint32_t kRowInfinite = 2;  // one or more +inf: equal shares
+constexpr uint32_t kRowAbsent = 3;    // past the last logical row
+
+struct StageParams {
+    float* scores;
+    uint16_t* probability;
+    uint64_t rows_total;  // planes * Hq * R
+    uint64_t a;
+    uint32_t R, Rp, L, Lp;
+    float scale;          // 1 / sqrtf(D), both correctly rounded
+};
+
+__device__ __forceinline__ float scaled_score(float score, float scale) {
+    const float product = __fmul_rn(score, scale);
+    return product == 0.0f ? 0.0f : product;   // a zero product is stored as +0
+}
+
+// BF16 round-to-nearest-even of src/cuda/sdpa_nonmatrix.cu:317-336: infinities kept,
+// every NaN the quiet 0x7FC0, both zeros +0, subnormals rounded like normals.
+__device__ __forceinline__ uint16_t probability_bits(float value) {
+    const uint32_t bits = __float_as_uint(value);
+    if ((bits & 0x7f800000u) == 0x7f800000u) {
+        return (bits & 0x007fffffu) == 0 ? static_cast<uint16_t>(bits >> 16) : uint16_t{0x7fc0};
+    }
+    if ((bits & 0x7fffffffu) == 0) return 0;
+    return static_cast<uint16_t>((bits + 0x7fffu + ((bits >> 16) & 1u)) >> 16);
+}
+
+__device__ __forceinline__ bool is_positive_infinity(float value) {
+    return __float_as_uint(value) == 0x7f800000u;
+}
+
+__device__ __forceinline__ bool is_negative_infinity(float value) {
+    return __float_as_uint(value) == 0xff800000u;
+}
+
+// Element offset of logical row `index` (plane, head, row flattened) and its visible length.
+__device__ __forceinline__ void locate_row(const StageParams& p, uint64_t index,
+                                           uint64_t* base, uint32_t* visible) {
+    const uint64_t head = index / p.R;
+    const uint32_t row = static_cast<uint32_t>(index - head * p.R);
+    *base = (head * p.Rp + row) * p.Lp;
+    const uint64_t causal = p.a + row + 1;
+    *visible = causal < p.L ? static_cast<uint32_t>(causal) : p.L;
+}
+
+// One warp per row: 32-byte vectors over the visible prefix, the ragged end by element.
+__global__ void __launch_bounds__(kScaleThreads)
+scale_mask_kernel(const StageParams p) {
+    constexpr int kWarps = kScaleThreads / 32;
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint64_t warps = static_cast<uint64_t>(gridDim.x) * kWarps;
+    for (uint64_t index = static_cast<uint64_t>(blockIdx.x) * kWarps + (threadIdx.x >> 5);
+         index < p.rows_total; index += warps) {
+        uint64_t base;
+        uint32_t visible;
+        locate_row(p, index, &base, &visible);
+        float* row = p.scores + base;
+        const uint32_t whole = visible & ~7u;
+        for (uint32_t t = lane * 8; t < whole; t += 256) {
+            uint4 lo, hi;
+            load_u8_stream(row + t, &lo, &hi);
+            uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                w[k] = __float_as_uint(scaled_score(__uint_as_float(w[k]), p.scale));
+            }
+            store_u8_stream(row + t, make_uint4(w[0], w[1], w[2], w[3]),
+                            make_uint4(w[4], w[5], w[6], w[7]));
+        }
+        const uint32_t t = whole + lane;
+        if (t < visible) row[t] = scaled_score(row[t], p.scale);
+    }
+}
+
+// Row softmax. SCALE: the scores are raw and every load applies scaled_score first
+// (the fused scale/mask + softmax); KEEP (with SCALE): the first pass also stores the
+// scaled scores, after which the later passes read them as they are.
+//
+// Per group of 32 logical rows:
+//   pass A  every warp takes rows w, w+9, ...: classification and the maximum of the
+//           finite scores (exact in any order);
+//   pass B  warps 0..7 write expf(s - m) for 32 rows x 128 tokens into one of two
+//           shared tiles (+0 beyond a row's visible prefix and for special rows), warp 8
+//           adds the previous tile, lane r walking row r in token order: the sum of the
+//           reference, which starts at +0 and skips nothing but -inf scores, whose
+//           exponential is +0;
+//   pass C  every warp takes rows again: BF16_RNE(expf(s - m) / sum) for the visible
+//           tokens, +0 up to L, 16-byte stores.
+template <bool SCALE, bool KEEP>
+__global__ void __launch_bounds__(kSoftmaxThreads)
+softmax_kernel(const StageParams p) {
+    __shared__ float tile[2][kGroupRows][kChunk + 1];
+    __shared__ uint64_t s_base[kGroupRows];
+    __shared__ uint32_t s_visible[kGroupRows];
+    __shared__ uint32_t s_class[kGroupRows];
+    __shared__ float s_max[kGroupRows];
+    __shared__ float s_sum[kGroupRows];    // the sum, or 1 / count for a +inf row
+    __shared__ uint32_t s_chunks;
+
+    constexpr bool kScaleLater = SCALE && !KEEP;
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t warp = threadIdx.x >> 5;
+    const uint64_t groups = (p.rows_total + kGroupRows - 1) / kGroupRows;
+
+    for (uint64_t group = blockIdx.x; group < groups; group += gridDim.x) {
+        __syncthreads();   // the previous group's readers are done with the row records
+        if (threadIdx.x < kGroupRows) {
+            const uint64_t index = group * kGroupRows + threadIdx.x;
+            uint64_t base = 0;
+            uint32_t visible = 0;
+            if (index < p.rows_total) locate_row(p, index, &base, &visible);
+            s_base[threadIdx.x] = base;
+            s_visible[threadIdx.x] = visible;
+        }
+        __syncthreads();
+
+        // ---- pass A ---------------------------------------------------------------
+        for (uint32_t r = warp; r < kGroupRows; r += kSoftmaxWarps) {
+            const uint32_t visible = s_visible[r];
+            if (visible == 0) {
+                if (lane == 0) s_class[r] = kRowAbsent;
+                continue;
+            }
+            float* row = p.scores + s_base[r];
+            bool has_nan = false, not_all_negative = false;
+            uint32_t positive = 0;
+            float maximum = __uint_as_float(0xff800000u);
+            for (uint32_t t = lane * 4; t < visible; t += 128) {
+                const float4 v = *reinterpret_cast<const float4*>(row + t);
+                float s[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    if (t + k >= visible) continue;
+                    if constexpr (SCALE) s[k] = scaled_score(s[k], p.scale);
+                    if (s[k] != s[k]) {
+                        has_nan = true;
+                    } else if (is_positive_infinity(s[k])) {
+                        ++positive;
+                        not_all_negative = true;
+                    } else if (!is_negative_infinity(s[k])) {
+                        not_all_negative = true;
+                        maximum = fmaxf(maximum, s[k]);
+                    }
+                }
+                if constexpr (KEEP) {
+                    if (t + 4 <= visible) {
+                        *reinterpret_cast<float4*>(row + t) = make_float4(s[0], s[1], s[2], s[3]);
+                    } else {
+                        for (int k = 0; k < 4 && t + k < visible; ++k) row[t + k] = s[k];
+                    }
+                }
+            }
+#pragma unroll
+            for (int offset = 16; offset > 0; offset >>= 1) {
+                has_nan |= __shfl_xor_sync(0xffffffffu, has_nan ? 1 : 0, offset) != 0;
+                not_all_negative |= __shfl_xor_sync(0xffffffffu, not_all_negative ? 1 : 0, offset) != 0;
+                positive += __shfl_xor_sync(0xffffffffu, positive, offset);
+                maximum = fmaxf(maximum, __shfl_xor_sync(0xffffffffu, maximum, offset));
+            }
+            if (lane == 0) {
+                if (has_nan || !not_all_negative) {
+                    s_class[r] = kRowNan;
+                } else if (positive != 0) {
+                    s_class[r] = kRowInfinite;
+                    s_sum[r] = __fdiv_rn(1.0f, static_cast<float>(positive));
+                } else {
+                    s_class[r] = kRowOrdinary;
+                    s_max[r] = maximum;
+                }
+            }
+        }
+        __syncthreads();
+        if (warp == 0) {
+            uint32_t longest = s_class[lane] == kRowOrdinary ? s_visible[lane] : 0u;
+#pragma unroll
+            for (int offset = 16; offset > 0; offset >>= 1) {
+                longest = max(longest, __shfl_xor_sync(0xffffffffu, longest, offset));
+            }
+            if (lane == 0) s_chunks = (longest + kChunk - 1) / kChunk;
+        }
+        __syncthreads();
+
+        // ---- pass B ---------------------------------------------------------------
+        const uint32_t chunks = s_chunks;
+        float running = 0.0f;
+        for (uint32_t c = 0; c <= chunks; ++c) {
+            if (warp < kExpWarps && c < chunks) {
+#pragma unroll
+                for (uint32_t rr = 0; rr < kGroupRows / kExpWarps; ++rr) {
+                    const uint32_t r = warp * (kGroupRows / kExpWarps) + rr;
+                    const uint32_t visible = s_class[r] == kRowOrdinary ? s_visible[r] : 0u;
+                    const float* row = p.scores + s_base[r];
+                    const float maximum = s_max[r];
+#pragma unroll
+                    for (uint32_t k = 0; k < kChunk / 32; ++k) {
+                        const uint32_t t = c * kChunk + k * 32 + lane;
+                        float e = 0.0f;
+                        if (t < visible) {
+                            float s = row[t];
+                            if constexpr (kScaleLater) s = scaled_score(s, p.scale);
+                            e = expf(__fsub_rn(s, maximum));
+                        }
+                        tile[c & 1][r][k * 32 + lane] = e;
+                    }
+                }
+            } else if (warp == kExpWarps && c > 0) {
+                const float* column = &tile[(c - 1) & 1][lane][0];
+#pragma unroll 16
+                for (uint32_t t = 0; t < kChunk; ++t) running = __fadd_rn(running, column[t]);
+            }
+            __syncthreads();
+        }
+        if (warp == kExpWarps && s_class[lane] == kRowOrdinary) s_sum[lane] = running;
+        __syncthreads();
+
+        // ---- pass C ---------------------------------------------------------------
+        for (uint32_t r = warp; r < kGroupRows; r += kSoftmaxWarps) {
+            const uint32_t row_class = s_class[r];
+            if (row_class == kRowAbsent) continue;
+            const uint32_t visible = s_visible[r];
+            const float* row = p.scores + s_base[r];
+            uint16_t* out = p.probability + s_base[r];
+            const float maximum = s_max[r];
+            const float sum = s_sum[r];
+            for (uint32_t t = lane * 8; t < p.L; t += 256) {
+                uint32_t cell[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+                if (t < visible) {
+                    if (row_class == kRowNan) {
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) cell[k] = t + k < visible ? 0x7fc0u : 0u;
+                    } else {
+                        const float4 lo = *reinterpret_cast<const float4*>(row + t);
+                        const float4 hi = *reinterpret_cast<const float4*>(row + t + 4);
+                        float s[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) {
+                            if (t + k >= visible) continue;
+                            if constexpr (kScaleLater) s[k] = scaled_score(s[k], p.scale);
+                            if (row_class == kRowInfinite) {
+                                cell[k] = is_positive_infinity(s[k]) ? probability_bits(sum) : 0u;
+                            } else if (!is_negative_infinity(s[k])) {
+                                cell[k] = probability_bits(
+                                        __fdiv_rn(expf(__fsub_rn(s[k], maximum)), sum));
+                            }
+                        }
+                    }
+                }
+                if (t + 8 <= p.L) {
+                    *reinterpret_cast<uint4*>(out + t) = make_uint4(
+                            cell[0] | (cell[1] << 16), cell[2] | (cell[3] << 16),
+                            cell[4] | (cell[5] << 16), cell[6] | (cell[7] << 16));
+                } else {
+                    for (int k = 0; k < 8 && t + k < p.L; ++k) out[t + k] = static_cast<uint16_t>(cell[k]);
+                }
+            }
+        }
+    }
+}
+
+// Canonical zeros and NaNs of a BF16 view: one warp per 16x16 tile (32 lanes x 16 bytes),
+// four tiles per warp, the store issued only where a value changed.
+constexpr int kCanonThreads = 256;
+constexpr uint32_t kCanonTiles = 4;
+
+struct CanonParams {
+    Operand out;
+    Leading leading;
+    uint64_t items;       // planes * tile_rows * ceil(tile_cols / kCanonTiles)
+    uint32_t rows, cols, tile_rows, tile_cols, groups;
+};
+
+__device__ __forceinline__ uint32_t canonical_pair(uint32_t word) {
+    uint32_t lo = word & 0xffffu, hi = word >> 16;
+    if ((lo & 0x7fffu) == 0) lo = 0;
+    else if ((lo & 0x7f80u) == 0x7f80u && (lo & 0x007fu) != 0) lo = 0x7fc0u;
+    if ((hi & 0x7fffu) == 0) hi = 0;
+    else if ((hi & 0x7f80u) == 0x7f80u && (hi & 0x007fu) != 0) hi = 0x7fc0u;
+    return lo | (hi << 16);
+}
+
+__global__ void __launch_bounds__(kCanonThreads)
+canonicalize_kernel(const CanonParams p) {
+    constexpr int kWarps = kCanonThreads / 32;
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t row = lane >> 1, col = (lane & 1u) * 8;
+    const uint64_t warps = static_cast<uint64_t>(gridDim.x) * kWarps;
+    for (uint64_t item = static_cast<uint64_t>(blockIdx.x) * kWarps + (threadIdx.x >> 5);
+         item < p.items; item += warps) {
+        const uint32_t g = static_cast<uint32_t>(item % p.groups);
+        const uint64_t band = item / p.groups;
+        const uint32_t tr = static_cast<uint32_t>(band % p.tile_rows);
+        const uint64_t index = band / p.tile_rows;
+        if (row >= p.rows - tr * kTile) continue;
+        unsigned char* first = p.out.base
+                + ((operand_plane(p.out, p.leading, index) * p.tile_rows + tr) * p.tile_cols) * 512ull
+                + lane * 16;
+        const uint32_t tc0 = g * kCanonTiles;
+        uint4 value[kCanonTiles];
+        uint32_t valid[kCanonTiles];
+#pragma unroll
+        for (uint32_t k = 0; k < kCanonTiles; ++k) {
+            const uint32_t tc = tc0 + k;
+            valid[k] = 0;
+            if (tc < p.tile_cols) {
+                const uint32_t cols_left = p.cols - tc * kTile;
+                valid[k] = col < cols_left ? min(8u, cols_left - col) : 0u;
+            }
+            if (valid[k] != 0) value[k] = load_u4(first + (tc0 + k) * 512ull);
+        }
+#pragma unroll
+        for (uint32_t k = 0; k < kCanonTiles; ++k) {
+            if (valid[k] == 0) continue;
+            unsigned char* address = first + (tc0 + k) * 512ull;
+            const uint4 clean = make_uint4(canonical_pair(value[k].x), canonical_pair(value[k].y),
+                                           canonical_pair(value[k].z), canonical_pair(value[k].w));
+            if (valid[k] == 8) {
+                if (clean.x != value[k].x || clean.y != value[k].y || clean.z != value[k].z
+                    || clean.w != value[k].w) {
+                    store_u4(address, clean);
+                }
+            } else {
+                const uint32_t words[4] = {clean.x, clean.y, clean.z, clean.w};
+                uint16_t* cells = reinterpret_cast<uint16_t*>(address);
+                for (uint32_t e = 0; e < valid[k]; ++e) {
+                    cells[e] = static_cast<uint16_t>(words[e >> 1] >> ((e & 1u) * 16));
+                }
+            }
+        }
+    }
+}
+
+// ---- admission ------------------------------------------------------------------
+
+bool mul_overflows(uint64_t a, uint64_t b, uint64_t* out) {
+    return __builtin_mul_overflow(a, b, out);
+}
+
+// The rules of validate_geometry / validate_sdpa_nonmatrix_request
+// (src/cuda/sdpa_nonmatrix.cu:82-229,509-562) for the two workspace segments.
+int check_stages(const iomb_sdpa_stages* stages, const char* what, StageParams* p) {
+    if (stages == nullptr) return fail(IOMB_ERR_INVALID_ARGUMENT, "sdpa stages: null request");
+    const iomb_sdpa_stages& q = *stages;
+    if (q.scores == nullptr || q.probability == nullptr) {
+        return fail(IOMB_ERR_INVALID_ARGUMENT, "sdpa stages: workspace pointers must be non-null");
+    }
+    if (q.Hq == 0 || q.Hkv == 0 || q.R == 0 || q.C == 0 || q.D == 0 || q.L == 0 || q.planes == 0) {
+        return fail(IOMB_ERR_INVALID_ARGUMENT, "sdpa stages: dimensions must be nonzero");
+    }
+    if (q.L > q.C || q.a >= q.C || q.R > q.C - q.a) {
+        return fail(IOMB_ERR_INVALID_ARGUMENT, "sdpa stages: causal dimensions are invalid");
+    }
+    if (q.Hq % q.Hkv != 0) {
+        return fail(IOMB_ERR_INVALID_ARGUMENT, "sdpa stages: Hq is not a multiple of Hkv");
+    }
+    if (q.R > 0x7fffffffull || q.L > 0x7fffffffull || q.D > (1ull << 24)) {
+        return fail(IOMB_ERR_UNSUPPORTED, "sdpa stages: extent exceeds the kernel limit");
+    }
+    const uint64_t Rp = (q.R + 15) / 16 * 16, Lp = (q.L + 15) / 16 * 16;
+    uint64_t heads = 0, rows = 0, cells = 0, score_bytes = 0, logical_rows = 0;
+    if (mul_overflows(q.planes, q.Hq, &heads) || mul_overflows(heads, Rp, &rows)
+        || mul_overflows(rows, Lp, &cells) || mul_overflows(cells, 4, &score_bytes)
+        || mul_overflows(heads, q.R, &logical_rows)) {
+        return fail(IOMB_ERR_OVERFLOW, "sdpa stages: score extent overflows");
+    }
+    const uintptr_t s0 = reinterpret_cast<uintptr_t>(q.scores);
+    const uintptr_t p0 = reinterpret_cast<uintptr_t>(q.probability);
+    if ((s0 & 31u) != 0 || (p0 & 31u) != 0) {
+        return fail(IOMB_ERR_INVALID_ARGUMENT, "sdpa stages: workspace segments must be 32-byte aligned");
+    }
+    if (s0 + score_bytes < s0 || p0 + cells * 2 < p0) {
+        return fail(IOMB_ERR_OVERFLOW, "sdpa stages: pointer range overflows");
+    }
+    if (s0 < p0 + cells * 2 && p0 < s0 + score_bytes) {
+        return fail(IOMB_ERR_INVALID_ARGUMENT, "sdpa stages: scores and probability ranges overlap");
+    }
+    (void)what;
+    p->scores = q.scores;
+    p->probability = static_cast<uint16_t*>(q.probability);
+    p->rows_total = logical_rows;
+    p->a = q.a;
+    p->R = static_cast<uint32_t>(q.R);
+    p->Rp = static_cast<uint32_t>(Rp);
+    p->L = static_cast<uint32_t>(q.L);
+    p->Lp = static_cast<uint32_t>(Lp);
+    p->scale = 1.0f / sqrtf(static_cast<float>(q.D));
+    return IOMB_OK;
+}
+
+int softmax_launch(const iomb_sdpa_stages* stages, bool scale, bool keep, void* stream) {
+    StageParams p{};
+    const int status = check_stages(stages, "sdpa softmax", &p);
+    if (status != IOMB_OK) return status;
+    if (sm_count() <= 0) return fail(IOMB_ERR_DEVICE, "sdpa softmax: no CUDA device");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const unsigned grid = grid_for((p.rows_total + kGroupRows - 1) / kGroupRows, kSoftmaxCtasPerSm);
+    if (!scale) softmax_kernel<false, false><<<grid, kSoftmaxThreads, 0, s>>>(p);
+    else if (keep) softmax_kernel<true, true><<<grid, kSoftmaxThreads, 0, s>>>(p);
+    else softmax_kernel<true, false><<<grid, kSoftmaxThreads, 0, s>>>(p);
+    return check_launch("sdpa softmax launch");
+}
+
+}  // namespace
+
+}  // namespace iomb
+
+extern "C" int iomb_sdpa_scale_mask(const iomb_sdpa_stages* stages, void* stream) {
+    iomb::StageParams p{};
+    const int status = iomb::check_stages(stages, "sdpa scale_mask", &p);
+    if (status != IOMB_OK) return status;
+    if (iomb::sm_count() <= 0) return iomb::fail(IOMB_ERR_DEVICE, "sdpa scale_mask: no CUDA device");
+    const uint64_t ctas = (p.rows_total + iomb::kScaleThreads / 32 - 1) / (iomb::kScaleThreads / 32);
+    iomb::scale_mask_kernel<<<iomb::grid_one_shot(ctas), iomb::kScaleThreads, 0,
+                              static_cast<cudaStream_t>(stream)>>>(p);
+    return iomb::check_launch("sdpa scale_mask launch");
+}
+
+extern "C" int iomb_sdpa_softmax(const iomb_sdpa_stages* stages, void* stream) {
+    return iomb::softmax_launch(stages, false, false, stream);
+}
+
+extern "C" int iomb_sdpa_scale_mask_softmax(const iomb_sdpa_stages* stages, int keep_scores,
+                                            void* stream) {
+    return iomb::softmax_launch(stages, true, keep_scores != 0, stream);
+}
+
+extern "C" int iomb_sdpa_canonicalize_output(const iomb_view* out, void* stream) {
+    using namespace iomb;
+    ViewFacts facts{};
+    const int status = check_view(out, "sdpa output", &facts);
+    if (status != IOMB_OK) return status;
+    if (out->dtype != IOMB_BF16) return fail(IOMB_ERR_UNSUPPORTED, "sdpa output: leaf is not BF16");
+    if (facts.rows > 0xFFFFFFFFull || facts.cols > 0xFFFFFFFFull) {
+        return fail(IOMB_ERR_UNSUPPORTED, "sdpa output: matrix extent exceeds the kernel limit");
+    }
+    if (sm_count() <= 0) return fail(IOMB_ERR_DEVICE, "sdpa output: no CUDA device");
+    CanonParams p{};
+    uint64_t strides[1][kMaxLead] = {};
+    for (uint32_t axis = 0; axis < facts.leading; ++axis) strides[0][axis] = out->plane_strides[axis];
+    collapse_leading(facts.leading, out->dims, strides, 1, &p.leading);
+    p.out = make_operand(*out, facts, strides[0], p.leading, false, false);
+    p.rows = static_cast<uint32_t>(facts.rows);
+    p.cols = static_cast<uint32_t>(facts.cols);
+    p.tile_rows = static_cast<uint32_t>(facts.tile_rows);
+    p.tile_cols = static_cast<uint32_t>(facts.tile_cols);
+    p.groups = (p.tile_cols + kCanonTiles - 1) / kCanonTiles;
+    p.items = p.leading.planes * facts.tile_rows * p.groups;
+    const uint64_t ctas = (p.items + kCanonThreads / 32 - 1) / (kCanonThreads / 32);
+    canonicalize_kernel<<<grid_one_shot(ctas), kCanonThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    return check_launch("sdpa canonicalize launch");
+}

@@ -392,6 +392,45 @@ def make_b200_device(ordinal: int, memory: DeviceMemoryConfig,
     return B200Device(ordinal, memory, queue_config)
 
 
+class SdpaStages:
+    """The two workspace segments of the attention stages that are not matrix products,
+    laid out as the reference's CUDA backend does (src/cuda/sdpa_nonmatrix_request.hpp:22-49):
+    FP32 scores [planes, Hq, pad16(R), pad16(L)] at the start of the workspace range, the
+    BF16 probabilities of the same extents behind them, each segment rounded up to 32 bytes."""
+
+    def __init__(self, workspace: RawWorkspaceView, planes: int, Hq: int, Hkv: int, R: int,
+                 C: int, D: int, a: int, L: int):
+        for name, value in (("planes", planes), ("Hq", Hq), ("Hkv", Hkv), ("R", R), ("C", C),
+                            ("D", D), ("a", a), ("L", L)):
+            if not 0 <= value < 1 << 64:
+                raise ValueError(f"sdpa stages: {name} is out of range")
+        self.workspace = workspace
+        self.planes, self.Hq, self.Hkv, self.R, self.C, self.D, self.a, self.L = \
+            planes, Hq, Hkv, R, C, D, a, L
+        self.Rp, self.Lp = (R + 15) // 16 * 16, (L + 15) // 16 * 16
+        self.cells = planes * Hq * self.Rp * self.Lp
+        self.score_bytes = (self.cells * 4 + 31) // 32 * 32
+        self.probability_bytes = (self.cells * 2 + 31) // 32 * 32
+        if workspace is None or workspace.empty() or \
+                workspace.byte_size() < self.score_bytes + self.probability_bytes:
+            raise ValueError("sdpa stages: the workspace is smaller than workspace_bytes()")
+
+    @staticmethod
+    def workspace_bytes(planes: int, Hq: int, R: int, L: int) -> int:
+        cells = planes * Hq * ((R + 15) // 16 * 16) * ((L + 15) // 16 * 16)
+        return (cells * 4 + 31) // 32 * 32 + (cells * 2 + 31) // 32 * 32
+
+    def scores_address(self) -> int:
+        return self.workspace.address()
+
+    def probability_address(self) -> int:
+        return self.workspace.address() + self.score_bytes
+
+    def as_abi(self) -> "_abi.IombSdpaStages":
+        return _abi.IombSdpaStages(self.scores_address(), self.probability_address(), self.planes,
+                                   self.Hq, self.Hkv, self.R, self.C, self.D, self.a, self.L)
+
+
 class SubmissionFaults:
     """Host-side fault table of one queue, for failure-path tests (the role of the
     reference's test-only failure latches, src/cpu/queue.cpp:51-87,128-160): a named
@@ -935,3 +974,42 @@ class B200Queue:
 
     def sdpa(self, *args, **kwargs) -> int:
         return OID_UNSUPPORTED
+
+    # The stages of attention that are not matrix products (the backend-private launches
+    # of src/cuda/sdpa_nonmatrix.hpp:15-28), offered on their own until the QK and PV
+    # products exist here.
+    def _sdpa_stage(self, stages: "SdpaStages", call) -> int:
+        try:
+            if not isinstance(stages, SdpaStages):
+                raise ValueError("sdpa stage requires an SdpaStages description")
+            request = stages.as_abi()
+        except BaseException as error:
+            return _exception_to_oid(error)
+        return self._submit(lambda stream: call(ctypes.byref(request), stream),
+                            (stages.workspace.owner,))
+
+    def sdpa_scale_mask(self, stages: "SdpaStages") -> int:
+        """launch_sdpa_scale_mask: visible scores times 1/sqrt(D), zero products as +0."""
+        return self._sdpa_stage(stages, self._lib.iomb_sdpa_scale_mask)
+
+    def sdpa_softmax(self, stages: "SdpaStages") -> int:
+        """launch_sdpa_softmax: BF16 probabilities of the visible tokens, +0 up to L."""
+        return self._sdpa_stage(stages, self._lib.iomb_sdpa_softmax)
+
+    def sdpa_scale_mask_softmax(self, stages: "SdpaStages", keep_scores: bool = False) -> int:
+        """Extension: both stages in one pass; the scaled scores are stored only on request."""
+        keep = 1 if keep_scores else 0
+        return self._sdpa_stage(
+            stages, lambda request, stream: self._lib.iomb_sdpa_scale_mask_softmax(request, keep, stream))
+
+    def sdpa_canonicalize_output(self, out: TensorView) -> int:
+        """launch_sdpa_canonicalize_output: -0 to +0 and every NaN to 0x7FC0 in the merged
+        BF16 output [B..., R, Hq*D]."""
+        try:
+            self._check_view(out, "out")
+            view = out.as_abi()
+        except BaseException as error:
+            return _exception_to_oid(error)
+        return self._submit(
+            lambda stream: self._lib.iomb_sdpa_canonicalize_output(ctypes.byref(view), stream),
+            (out.owner,))

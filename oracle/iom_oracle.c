@@ -923,3 +923,114 @@ int iomo_gather(const iomo_view* source, void* logical) {
     }
     return 0;
 }
+
+/* ---- attention stages without matrix products: src/cuda/sdpa_nonmatrix.cu:347-507 ---- */
+
+static int sdpa_stages_ok(const iomo_sdpa_stages* q) {
+    if (!q || !q->scores || !q->probability) return 0;
+    if (!q->planes || !q->Hq || !q->Hkv || !q->R || !q->C || !q->D || !q->L) return 0;
+    if (q->L > q->C || q->a >= q->C || q->R > q->C - q->a) return 0;
+    return q->Hq % q->Hkv == 0;
+}
+
+static uint64_t sdpa_pad16(uint64_t v) { return (v + 15) / 16 * 16; }
+
+static uint64_t sdpa_visible(const iomo_sdpa_stages* q, uint64_t row) {
+    return q->L < q->a + row + 1 ? q->L : q->a + row + 1;
+}
+
+/* bf16_rne of src/cuda/sdpa_nonmatrix.cu:317-336. */
+static uint16_t sdpa_bf16(float value) {
+    uint32_t bits;
+    memcpy(&bits, &value, 4);
+    if ((bits & 0x7f800000u) == 0x7f800000u) {
+        return (bits & 0x007fffffu) == 0 ? (uint16_t)(bits >> 16) : (uint16_t)0x7fc0;
+    }
+    if ((bits & 0x7fffffffu) == 0) return 0;
+    return (uint16_t)((bits + 0x7fffu + ((bits >> 16) & 1u)) >> 16);
+}
+
+int iomo_sdpa_scale_mask(const iomo_sdpa_stages* q) {
+    if (!sdpa_stages_ok(q)) return 1;
+    const uint64_t Rp = sdpa_pad16(q->R), Lp = sdpa_pad16(q->L);
+    const float scale = 1.0f / sqrtf((float)q->D);
+    for (uint64_t head = 0; head < q->planes * q->Hq; ++head) {
+        for (uint64_t row = 0; row < q->R; ++row) {
+            float* cells = q->scores + (head * Rp + row) * Lp;
+            const uint64_t visible = sdpa_visible(q, row);
+            for (uint64_t token = 0; token < visible; ++token) {
+                const volatile float scaled = cells[token] * scale;
+                cells[token] = scaled == 0.0f ? 0.0f : scaled;
+            }
+        }
+    }
+    return 0;
+}
+
+int iomo_sdpa_softmax(const iomo_sdpa_stages* q) {
+    if (!sdpa_stages_ok(q)) return 1;
+    const uint64_t Rp = sdpa_pad16(q->R), Lp = sdpa_pad16(q->L);
+    for (uint64_t head = 0; head < q->planes * q->Hq; ++head) {
+        for (uint64_t row = 0; row < q->R; ++row) {
+            const float* cells = q->scores + (head * Rp + row) * Lp;
+            uint16_t* out = q->probability + (head * Rp + row) * Lp;
+            const uint64_t visible = sdpa_visible(q, row);
+            int has_nan = 0, all_negative = 1;
+            uint64_t positive = 0;
+            float maximum = -INFINITY;
+            for (uint64_t token = 0; token < visible; ++token) {
+                const float s = cells[token];
+                if (isnan(s)) { has_nan = 1; continue; }
+                if (isinf(s) && s > 0.0f) { ++positive; all_negative = 0; continue; }
+                if (isinf(s)) continue;
+                all_negative = 0;
+                if (s > maximum) maximum = s;
+            }
+            if (has_nan || all_negative) {
+                for (uint64_t token = 0; token < q->L; ++token) out[token] = token < visible ? 0x7fc0 : 0;
+                continue;
+            }
+            if (positive) {
+                const float share = 1.0f / (float)positive;
+                for (uint64_t token = 0; token < q->L; ++token) {
+                    const int hit = token < visible && isinf(cells[token]) && cells[token] > 0.0f;
+                    out[token] = hit ? sdpa_bf16(share) : 0;
+                }
+                continue;
+            }
+            float sum = 0.0f;
+            for (uint64_t token = 0; token < visible; ++token) {
+                if (isinf(cells[token])) continue;
+                const volatile float shifted = cells[token] - maximum;
+                const volatile float next = sum + expf(shifted);
+                sum = next;
+            }
+            for (uint64_t token = 0; token < q->L; ++token) {
+                if (token >= visible || isinf(cells[token])) { out[token] = 0; continue; }
+                const volatile float shifted = cells[token] - maximum;
+                const volatile float quotient = expf(shifted) / sum;
+                out[token] = sdpa_bf16(quotient);
+            }
+        }
+    }
+    return 0;
+}
+
+int iomo_sdpa_canonicalize_output(const iomo_view* out) {
+    geometry_t g;
+    if (geometry_of(out, &g) || out->dtype != 20) return 1;
+    const uint64_t planes = leading_count(out);
+    for (uint64_t index = 0; index < planes; ++index) {
+        const uint64_t p = view_plane(out, index);
+        for (uint64_t row = 0; row < g.rows; ++row) {
+            for (uint64_t column = 0; column < g.columns; ++column) {
+                const uint64_t bit = element_bit(out, &g, p, row, column);
+                uint64_t bits = load_bits((const unsigned char*)out->base, bit, 16);
+                if ((bits & 0x7fffu) == 0) bits = 0;
+                else if ((bits & 0x7f80u) == 0x7f80u && (bits & 0x007fu) != 0) bits = 0x7fc0u;
+                store_bits((unsigned char*)out->base, bit, 16, bits);
+            }
+        }
+    }
+    return 0;
+}

@@ -72,6 +72,24 @@ double iomo_sumsq(const iomo_view* x);
 int iomo_scatter(const iomo_view* destination, const void* logical);
 int iomo_gather(const iomo_view* source, void* logical);
 
+/*
+ * The attention stages that are not matrix products, on host copies of the two workspace
+ * segments (FP32 scores and BF16 probability, both [planes, Hq, pad16(R), pad16(L)]):
+ * the steps of src/cuda/sdpa_nonmatrix.cu:347-507 one for one, with the C library's expf,
+ * which is also what the reference CPU backend's softmax calls (src/cpu/sdpa.cpp:258-300).
+ * Pinned by the known answers of the reference's stage test
+ * (test/cuda/test_cuda_sdpa_nonmatrix.cpp) on the CPU, and on a GPU against the
+ * reference's own stage kernels compiled into oracle/_ref.
+ */
+typedef struct iomo_sdpa_stages {
+    float* scores;
+    uint16_t* probability;
+    uint64_t planes, Hq, Hkv, R, C, D, a, L;
+} iomo_sdpa_stages;
+int iomo_sdpa_scale_mask(const iomo_sdpa_stages* stages);
+int iomo_sdpa_softmax(const iomo_sdpa_stages* stages);
+int iomo_sdpa_canonicalize_output(const iomo_view* out);
+
 #ifdef __cplusplus
 }
 #endif

@@ -12,7 +12,7 @@ from pathlib import Path
 
 import numpy as np
 
-from iom_b200._abi import IombView
+from iom_b200._abi import IombSdpaStages, IombView
 from iom_b200.tensor import DataType, TensorSpec, TensorView, dense_plane_strides, leaf_bits
 
 REPO = Path(__file__).resolve().parent.parent
@@ -79,8 +79,71 @@ def oracle() -> ctypes.CDLL:
         lib.iomo_scatter.argtypes = [_VIEW, ctypes.c_void_p]
         lib.iomo_gather.restype = ctypes.c_int
         lib.iomo_gather.argtypes = [_VIEW, ctypes.c_void_p]
+        lib.iomo_sdpa_scale_mask.restype = ctypes.c_int
+        lib.iomo_sdpa_scale_mask.argtypes = [ctypes.POINTER(IombSdpaStages)]
+        lib.iomo_sdpa_softmax.restype = ctypes.c_int
+        lib.iomo_sdpa_softmax.argtypes = [ctypes.POINTER(IombSdpaStages)]
+        lib.iomo_sdpa_canonicalize_output.restype = ctypes.c_int
+        lib.iomo_sdpa_canonicalize_output.argtypes = [_VIEW]
         _oracle = lib
     return _oracle
+
+
+class HostStages:
+    """Host copies of the attention stage workspace: FP32 scores and BF16 probabilities,
+    both [planes, Hq, pad16(R), pad16(L)], for the oracle's stage functions."""
+
+    def __init__(self, planes, Hq, Hkv, R, C, D, a, L, score_fill=777.0, probability_fill=0xA5A5):
+        self.geometry = (planes, Hq, Hkv, R, C, D, a, L)
+        self.Rp, self.Lp = (R + 15) // 16 * 16, (L + 15) // 16 * 16
+        shape = (planes, Hq, self.Rp, self.Lp)
+        self.scores = np.full(shape, score_fill, dtype=np.float32)
+        self.probability = np.full(shape, probability_fill, dtype=np.uint16)
+
+    def visible(self, row: int) -> int:
+        _, _, _, _, _, _, a, L = self.geometry
+        return min(L, a + row + 1)
+
+    def visible_mask(self) -> np.ndarray:
+        """Boolean [Rp, Lp]: the cells the causal prefix rule lets row r see."""
+        _, _, _, R, _, _, a, L = self.geometry
+        rows = np.arange(self.Rp)[:, None]
+        tokens = np.arange(self.Lp)[None, :]
+        return (rows < R) & (tokens < L) & (tokens <= a + rows)
+
+    def request(self) -> "IombSdpaStages":
+        return IombSdpaStages(self.scores.ctypes.data, self.probability.ctypes.data, *self.geometry)
+
+    def scale_mask(self):
+        assert oracle().iomo_sdpa_scale_mask(ctypes.byref(self.request())) == 0
+        return self
+
+    def softmax(self):
+        assert oracle().iomo_sdpa_softmax(ctypes.byref(self.request())) == 0
+        return self
+
+
+_sdpa_reference = None
+
+
+def sdpa_reference_stages_or_skip() -> ctypes.CDLL:
+    """The reference's own CUDA stage kernels (oracle/_ref/libiomref_sdpa_stages.so, built by
+    `make -C oracle cudastages` where the reference checkout is present)."""
+    global _sdpa_reference
+    path = ORACLE_DIR / "_ref" / "libiomref_sdpa_stages.so"
+    if _sdpa_reference is None:
+        if not path.exists():
+            import pytest
+            pytest.skip("reference stage kernels are not built (make -C oracle cudastages)")
+        lib = ctypes.CDLL(str(path))
+        u64, u64p = ctypes.c_uint64, ctypes.POINTER(ctypes.c_uint64)
+        lib.iomref_sdpa_stage.restype = ctypes.c_int
+        lib.iomref_sdpa_stage.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                          u64, u64, u64p, ctypes.c_uint32, u64p,
+                                          u64, u64, u64, u64, u64, u64, u64, ctypes.c_void_p]
+        lib.iomref_sdpa_error.restype = ctypes.c_char_p
+        _sdpa_reference = lib
+    return _sdpa_reference
 
 
 # ---- numpy <-> leaf encodings ------------------------------------------------
