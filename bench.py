@@ -514,6 +514,36 @@ def ops_table(device, queue, only=None, iters: int = 10) -> dict:
         record("rope_bf16", 2 * count * 2, lambda: ok(queue.rope(q_in.view(), q_out.view(), 0, 10000.0)),
                str(list(shape)))
         release()
+    if only is None or only in ("sdpa_scale_mask", "sdpa_softmax", "sdpa_scale_mask_softmax",
+                                "sdpa_canonicalize_output"):
+        # Attention stages at TinyLlama prefill geometry: 32 heads, 2048 query rows against
+        # 2048 cached tokens from an empty cache (a = 0): FP32 scores 537 MB, BF16
+        # probabilities 268 MB. Algorithmic bytes: a visible score is read (and, for
+        # scale/mask, written) once, every probability cell below L is written once.
+        from iom_b200.device import SdpaStages
+        heads, rows_q, tokens = 32, 2048, 2048
+        ws = device.create_workspace(SdpaStages.workspace_bytes(1, heads, rows_q, tokens))
+        stages = SdpaStages(ws.view(), 1, heads, 4, rows_q, tokens, 64, 0, tokens)
+        ws.tensor()[:stages.cells * 4].view(torch.float32).copy_(
+            torch.randn(stages.cells, device=device.torch_device) * 8.0)
+        visible = heads * sum(min(tokens, r + 1) for r in range(rows_q))
+        below = heads * rows_q * tokens
+        note = f"Hq {heads}, R {rows_q}, L {tokens}, a 0"
+        if only is None or only == "sdpa_softmax":
+            record("sdpa_softmax", visible * 4 + below * 2, lambda: ok(queue.sdpa_softmax(stages)), note)
+        if only is None or only == "sdpa_scale_mask_softmax":
+            record("sdpa_scale_mask_softmax", visible * 4 + below * 2,
+                   lambda: ok(queue.sdpa_scale_mask_softmax(stages)), note + ", scores only read")
+        if only is None or only == "sdpa_scale_mask":
+            # last: it rescales the scores in place on every launch
+            record("sdpa_scale_mask", visible * 8, lambda: ok(queue.sdpa_scale_mask(stages)), note)
+        ws.close()
+        if only is None or only == "sdpa_canonicalize_output":
+            merged = tensor((16, 8192, 2048), DataType.BF16)
+            record("sdpa_canonicalize_output", 16 * 8192 * 2048 * 2,
+                   lambda: ok(queue.sdpa_canonicalize_output(merged.view())),
+                   "[16,8192,2048] read, nothing to rewrite")
+            release()
     if only is None or only in ("embedding_prefill", "cache_append_prefill"):
         # Prefill-sized data movement: 131072 token rows of the TinyLlama table (537 MB out),
         # and 64 sequences x 4 KV heads x 2048 new rows appended into 4096-row caches.

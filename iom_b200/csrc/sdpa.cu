@@ -21,7 +21,7 @@ namespace iomb {
 namespace {
 
 constexpr int kGroupRows = 32;        // rows of one CTA job = lanes of the summing warp
-constexpr int kChunk = 128;           // tokens of one shared-memory tile
+constexpr int kChunk = 256;           // tokens of one shared-memory tile
 constexpr int kExpWarps = 8;          // warps that fill the tiles (4 rows each)
 constexpr int kSoftmaxWarps = kExpWarps + 1;
 constexpr int kSoftmaxThreads = kSoftmaxWarps * 32;
@@ -111,19 +111,47 @@ scale_mask_kernel(const StageParams p) {
 // scaled scores, after which the later passes read them as they are.
 //
 // Per group of 32 logical rows:
-//   pass A  every warp takes rows w, w+9, ...: classification and the maximum of the
-//           finite scores (exact in any order);
-//   pass B  warps 0..7 write expf(s - m) for 32 rows x 128 tokens into one of two
+//   pass A  every warp takes rows w, w+9, ...: one NaN-propagating maximum per score
+//           classifies the row (NaN: a NaN was seen; -inf: nothing but -inf; +inf: the
+//           equal-share case, whose +inf are then counted; else the finite maximum);
+//   pass B  warps 0..7 write expf(s - m) for 32 rows x 256 tokens into one of two
 //           shared tiles (+0 beyond a row's visible prefix and for special rows), warp 8
 //           adds the previous tile, lane r walking row r in token order: the sum of the
 //           reference, which starts at +0 and skips nothing but -inf scores, whose
-//           exponential is +0;
-//   pass C  every warp takes rows again: BF16_RNE(expf(s - m) / sum) for the visible
-//           tokens, +0 up to L, 16-byte stores.
+//           exponential is +0. Rows are 260 floats apart, so the 16-byte reads of eight
+//           neighbouring lanes fall into eight different bank groups;
+//   pass C  (row, 512-token segment) items over all warps, both halves loaded first: BF16_RNE(expf(s - m) / sum)
+//           for the visible tokens, +0 up to L, 16-byte stores. The quotient is formed as
+//           expf(s - m) * RN(1 / sum), which lies within two FP32 steps of the correctly
+//           rounded quotient; unless its low half is within four steps of the BF16 tie
+//           (5 codes in 8192) both round to the same BF16, and in that case the true
+//           division is done instead.
+constexpr int kRowStride = kChunk + 4;
+
+__device__ __forceinline__ float max_nan(float a, float b) {
+    float r;
+    asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+    return r;
+}
+
+__device__ __forceinline__ float negative_infinity() { return __uint_as_float(0xff800000u); }
+
+// BF16 code of a probability in [0, 1] that is not a NaN: plain round-to-nearest-even on
+// the bits (a zero stays 0, subnormals round like normals).
+__device__ __forceinline__ uint32_t round_bits(uint32_t bits) {
+    return (bits + 0x7fffu + ((bits >> 16) & 1u)) >> 16;
+}
+
+__device__ __forceinline__ uint32_t quotient_bits(float e, float sum, float reciprocal) {
+    uint32_t bits = __float_as_uint(__fmul_rn(e, reciprocal));
+    if (((bits + 4u) & 0xffffu) - 0x8000u <= 8u) bits = __float_as_uint(__fdiv_rn(e, sum));
+    return round_bits(bits);
+}
+
 template <bool SCALE, bool KEEP>
-__global__ void __launch_bounds__(kSoftmaxThreads)
+__global__ void __launch_bounds__(kSoftmaxThreads, kSoftmaxCtasPerSm)
 softmax_kernel(const StageParams p) {
-    __shared__ float tile[2][kGroupRows][kChunk + 1];
+    extern __shared__ __align__(16) float tile[];   // [2][kGroupRows][kRowStride]
     __shared__ uint64_t s_base[kGroupRows];
     __shared__ uint32_t s_visible[kGroupRows];
     __shared__ uint32_t s_class[kGroupRows];
@@ -135,6 +163,7 @@ softmax_kernel(const StageParams p) {
     const uint32_t lane = threadIdx.x & 31u;
     const uint32_t warp = threadIdx.x >> 5;
     const uint64_t groups = (p.rows_total + kGroupRows - 1) / kGroupRows;
+    const uint32_t segments = (p.L + 511u) / 512u;
 
     for (uint64_t group = blockIdx.x; group < groups; group += gridDim.x) {
         __syncthreads();   // the previous group's readers are done with the row records
@@ -156,50 +185,64 @@ softmax_kernel(const StageParams p) {
                 continue;
             }
             float* row = p.scores + s_base[r];
-            bool has_nan = false, not_all_negative = false;
-            uint32_t positive = 0;
-            float maximum = __uint_as_float(0xff800000u);
-            for (uint32_t t = lane * 4; t < visible; t += 128) {
-                const float4 v = *reinterpret_cast<const float4*>(row + t);
-                float s[4] = {v.x, v.y, v.z, v.w};
+            float top = negative_infinity();
+            for (uint32_t t0 = lane * 4; t0 < visible; t0 += 4 * 128) {
+                float4 v[4];                      // four row segments in flight per lane
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    if (t + k >= visible) continue;
-                    if constexpr (SCALE) s[k] = scaled_score(s[k], p.scale);
-                    if (s[k] != s[k]) {
-                        has_nan = true;
-                    } else if (is_positive_infinity(s[k])) {
-                        ++positive;
-                        not_all_negative = true;
-                    } else if (!is_negative_infinity(s[k])) {
-                        not_all_negative = true;
-                        maximum = fmaxf(maximum, s[k]);
-                    }
+                for (int u = 0; u < 4; ++u) {
+                    const uint32_t t = t0 + u * 128;
+                    if (t < visible) v[u] = *reinterpret_cast<const float4*>(row + t);
                 }
-                if constexpr (KEEP) {
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const uint32_t t = t0 + u * 128;
+                    if (t >= visible) break;
+                    float s[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+                    if constexpr (SCALE) {
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) s[k] = scaled_score(s[k], p.scale);
+                    }
                     if (t + 4 <= visible) {
-                        *reinterpret_cast<float4*>(row + t) = make_float4(s[0], s[1], s[2], s[3]);
+                        top = max_nan(max_nan(max_nan(top, s[0]), max_nan(s[1], s[2])), s[3]);
+                        if constexpr (KEEP) {
+                            *reinterpret_cast<float4*>(row + t) = make_float4(s[0], s[1], s[2], s[3]);
+                        }
                     } else {
-                        for (int k = 0; k < 4 && t + k < visible; ++k) row[t + k] = s[k];
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            if (t + k >= visible) continue;
+                            top = max_nan(top, s[k]);
+                            if constexpr (KEEP) row[t + k] = s[k];
+                        }
                     }
                 }
             }
 #pragma unroll
             for (int offset = 16; offset > 0; offset >>= 1) {
-                has_nan |= __shfl_xor_sync(0xffffffffu, has_nan ? 1 : 0, offset) != 0;
-                not_all_negative |= __shfl_xor_sync(0xffffffffu, not_all_negative ? 1 : 0, offset) != 0;
-                positive += __shfl_xor_sync(0xffffffffu, positive, offset);
-                maximum = fmaxf(maximum, __shfl_xor_sync(0xffffffffu, maximum, offset));
+                top = max_nan(top, __shfl_xor_sync(0xffffffffu, top, offset));
+            }
+            uint32_t positive = 0;
+            if constexpr (KEEP) __syncwarp();   // the scaled scores of the other lanes
+            if (is_positive_infinity(top)) {   // rare: count the +inf scores of the row
+                for (uint32_t t = lane; t < visible; t += 32) {
+                    float s = row[t];
+                    if constexpr (kScaleLater) s = scaled_score(s, p.scale);
+                    positive += is_positive_infinity(s) ? 1u : 0u;
+                }
+#pragma unroll
+                for (int offset = 16; offset > 0; offset >>= 1) {
+                    positive += __shfl_xor_sync(0xffffffffu, positive, offset);
+                }
             }
             if (lane == 0) {
-                if (has_nan || !not_all_negative) {
+                if (top != top || is_negative_infinity(top)) {
                     s_class[r] = kRowNan;
                 } else if (positive != 0) {
                     s_class[r] = kRowInfinite;
                     s_sum[r] = __fdiv_rn(1.0f, static_cast<float>(positive));
                 } else {
                     s_class[r] = kRowOrdinary;
-                    s_max[r] = maximum;
+                    s_max[r] = top;
                 }
             }
         }
@@ -213,34 +256,63 @@ softmax_kernel(const StageParams p) {
             if (lane == 0) s_chunks = (longest + kChunk - 1) / kChunk;
         }
         __syncthreads();
-
         // ---- pass B ---------------------------------------------------------------
         const uint32_t chunks = s_chunks;
         float running = 0.0f;
         for (uint32_t c = 0; c <= chunks; ++c) {
             if (warp < kExpWarps && c < chunks) {
+                float* buffer = tile + (c & 1u) * (kGroupRows * kRowStride);
+                constexpr uint32_t kRowsPerWarp = kGroupRows / kExpWarps;
+                constexpr uint32_t kVectors = kChunk / 128;      // float4 per lane and row
+                float4 v[kRowsPerWarp][kVectors];
 #pragma unroll
-                for (uint32_t rr = 0; rr < kGroupRows / kExpWarps; ++rr) {
-                    const uint32_t r = warp * (kGroupRows / kExpWarps) + rr;
+                for (uint32_t rr = 0; rr < kRowsPerWarp; ++rr) {
+                    const uint32_t r = warp * kRowsPerWarp + rr;
                     const uint32_t visible = s_class[r] == kRowOrdinary ? s_visible[r] : 0u;
                     const float* row = p.scores + s_base[r];
+#pragma unroll
+                    for (uint32_t k = 0; k < kVectors; ++k) {
+                        const uint32_t t = c * kChunk + k * 128 + lane * 4;
+                        v[rr][k] = t < visible ? *reinterpret_cast<const float4*>(row + t)
+                                               : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                    }
+                }
+#pragma unroll
+                for (uint32_t rr = 0; rr < kRowsPerWarp; ++rr) {
+                    const uint32_t r = warp * kRowsPerWarp + rr;
+                    const uint32_t visible = s_class[r] == kRowOrdinary ? s_visible[r] : 0u;
                     const float maximum = s_max[r];
 #pragma unroll
-                    for (uint32_t k = 0; k < kChunk / 32; ++k) {
-                        const uint32_t t = c * kChunk + k * 32 + lane;
-                        float e = 0.0f;
-                        if (t < visible) {
-                            float s = row[t];
-                            if constexpr (kScaleLater) s = scaled_score(s, p.scale);
-                            e = expf(__fsub_rn(s, maximum));
+                    for (uint32_t k = 0; k < kVectors; ++k) {
+                        const uint32_t t = c * kChunk + k * 128 + lane * 4;
+                        float s[4] = {v[rr][k].x, v[rr][k].y, v[rr][k].z, v[rr][k].w};
+                        float e[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                        if (t + 4 <= visible) {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                if constexpr (kScaleLater) s[j] = scaled_score(s[j], p.scale);
+                                e[j] = expf(__fsub_rn(s[j], maximum));
+                            }
+                        } else if (t < visible) {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                if (t + j >= visible) continue;
+                                if constexpr (kScaleLater) s[j] = scaled_score(s[j], p.scale);
+                                e[j] = expf(__fsub_rn(s[j], maximum));
+                            }
                         }
-                        tile[c & 1][r][k * 32 + lane] = e;
+                        *reinterpret_cast<float4*>(buffer + r * kRowStride + k * 128 + lane * 4) =
+                                make_float4(e[0], e[1], e[2], e[3]);
                     }
                 }
             } else if (warp == kExpWarps && c > 0) {
-                const float* column = &tile[(c - 1) & 1][lane][0];
-#pragma unroll 16
-                for (uint32_t t = 0; t < kChunk; ++t) running = __fadd_rn(running, column[t]);
+                const float4* column = reinterpret_cast<const float4*>(
+                        tile + ((c - 1) & 1u) * (kGroupRows * kRowStride) + lane * kRowStride);
+#pragma unroll 8
+                for (uint32_t t = 0; t < kChunk / 4; ++t) {
+                    const float4 e = column[t];
+                    running = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(running, e.x), e.y), e.z), e.w);
+                }
             }
             __syncthreads();
         }
@@ -248,33 +320,59 @@ softmax_kernel(const StageParams p) {
         __syncthreads();
 
         // ---- pass C ---------------------------------------------------------------
-        for (uint32_t r = warp; r < kGroupRows; r += kSoftmaxWarps) {
+        for (uint32_t item = warp; item < kGroupRows * segments; item += kSoftmaxWarps) {
+            const uint32_t r = item / segments;
             const uint32_t row_class = s_class[r];
             if (row_class == kRowAbsent) continue;
+            const uint32_t t0 = (item - r * segments) * 512u + lane * 8;
             const uint32_t visible = s_visible[r];
             const float* row = p.scores + s_base[r];
             uint16_t* out = p.probability + s_base[r];
-            const float maximum = s_max[r];
             const float sum = s_sum[r];
-            for (uint32_t t = lane * 8; t < p.L; t += 256) {
+            const float maximum = s_max[r];
+            float4 lo[2], hi[2];                  // both halves of the segment in flight
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const uint32_t t = t0 + u * 256;
+                if (t < visible && row_class != kRowNan) {
+                    lo[u] = *reinterpret_cast<const float4*>(row + t);
+                    hi[u] = *reinterpret_cast<const float4*>(row + t + 4);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const uint32_t t = t0 + u * 256;
+                if (t >= p.L) break;
                 uint32_t cell[8] = {0, 0, 0, 0, 0, 0, 0, 0};
                 if (t < visible) {
                     if (row_class == kRowNan) {
 #pragma unroll
                         for (int k = 0; k < 8; ++k) cell[k] = t + k < visible ? 0x7fc0u : 0u;
                     } else {
-                        const float4 lo = *reinterpret_cast<const float4*>(row + t);
-                        const float4 hi = *reinterpret_cast<const float4*>(row + t + 4);
-                        float s[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+                        float s[8] = {lo[u].x, lo[u].y, lo[u].z, lo[u].w, hi[u].x, hi[u].y, hi[u].z, hi[u].w};
+                        if constexpr (kScaleLater) {
 #pragma unroll
-                        for (int k = 0; k < 8; ++k) {
-                            if (t + k >= visible) continue;
-                            if constexpr (kScaleLater) s[k] = scaled_score(s[k], p.scale);
-                            if (row_class == kRowInfinite) {
-                                cell[k] = is_positive_infinity(s[k]) ? probability_bits(sum) : 0u;
-                            } else if (!is_negative_infinity(s[k])) {
-                                cell[k] = probability_bits(
-                                        __fdiv_rn(expf(__fsub_rn(s[k], maximum)), sum));
+                            for (int k = 0; k < 8; ++k) s[k] = scaled_score(s[k], p.scale);
+                        }
+                        if (row_class == kRowInfinite) {
+                            const uint32_t share = probability_bits(sum);
+#pragma unroll
+                            for (int k = 0; k < 8; ++k) {
+                                cell[k] = t + k < visible && is_positive_infinity(s[k]) ? share : 0u;
+                            }
+                        } else {
+                            const float reciprocal = __frcp_rn(sum);
+                            if (t + 8 <= visible) {
+#pragma unroll
+                                for (int k = 0; k < 8; ++k) {
+                                    cell[k] = quotient_bits(expf(__fsub_rn(s[k], maximum)), sum, reciprocal);
+                                }
+                            } else {
+#pragma unroll
+                                for (int k = 0; k < 8; ++k) {
+                                    if (t + k >= visible) continue;
+                                    cell[k] = quotient_bits(expf(__fsub_rn(s[k], maximum)), sum, reciprocal);
+                                }
                             }
                         }
                     }
@@ -284,7 +382,10 @@ softmax_kernel(const StageParams p) {
                             cell[0] | (cell[1] << 16), cell[2] | (cell[3] << 16),
                             cell[4] | (cell[5] << 16), cell[6] | (cell[7] << 16));
                 } else {
-                    for (int k = 0; k < 8 && t + k < p.L; ++k) out[t + k] = static_cast<uint16_t>(cell[k]);
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) {
+                        if (t + k < p.L) out[t + k] = static_cast<uint16_t>(cell[k]);
+                    }
                 }
             }
         }
@@ -363,6 +464,35 @@ canonicalize_kernel(const CanonParams p) {
     }
 }
 
+// The same over a dense run of whole tiles (contiguous planes, both extents multiples of
+// 16): 32-byte loads, four per thread in flight.
+__global__ void __launch_bounds__(kCanonThreads)
+canonicalize_linear_kernel(unsigned char* data, uint64_t pairs) {
+    constexpr int kUnroll = 4;
+    const uint64_t stride = static_cast<uint64_t>(gridDim.x) * kCanonThreads;
+    for (uint64_t first = static_cast<uint64_t>(blockIdx.x) * kCanonThreads * kUnroll + threadIdx.x;
+         first < pairs; first += stride * kUnroll) {
+        uint4 lo[kUnroll], hi[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            const uint64_t i = first + static_cast<uint64_t>(u) * kCanonThreads;
+            if (i < pairs) load_u8_stream(data + i * 32, &lo[u], &hi[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            const uint64_t i = first + static_cast<uint64_t>(u) * kCanonThreads;
+            if (i >= pairs) break;
+            const uint4 a = make_uint4(canonical_pair(lo[u].x), canonical_pair(lo[u].y),
+                                       canonical_pair(lo[u].z), canonical_pair(lo[u].w));
+            const uint4 b = make_uint4(canonical_pair(hi[u].x), canonical_pair(hi[u].y),
+                                       canonical_pair(hi[u].z), canonical_pair(hi[u].w));
+            const uint32_t changed = (a.x ^ lo[u].x) | (a.y ^ lo[u].y) | (a.z ^ lo[u].z) | (a.w ^ lo[u].w)
+                    | (b.x ^ hi[u].x) | (b.y ^ hi[u].y) | (b.z ^ hi[u].z) | (b.w ^ hi[u].w);
+            if (changed != 0) store_u8_stream(data + i * 32, a, b);
+        }
+    }
+}
+
 // ---- admission ------------------------------------------------------------------
 
 bool mul_overflows(uint64_t a, uint64_t b, uint64_t* out) {
@@ -427,9 +557,14 @@ int softmax_launch(const iomb_sdpa_stages* stages, bool scale, bool keep, void* 
     if (sm_count() <= 0) return fail(IOMB_ERR_DEVICE, "sdpa softmax: no CUDA device");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const unsigned grid = grid_for((p.rows_total + kGroupRows - 1) / kGroupRows, kSoftmaxCtasPerSm);
-    if (!scale) softmax_kernel<false, false><<<grid, kSoftmaxThreads, 0, s>>>(p);
-    else if (keep) softmax_kernel<true, true><<<grid, kSoftmaxThreads, 0, s>>>(p);
-    else softmax_kernel<true, false><<<grid, kSoftmaxThreads, 0, s>>>(p);
+    constexpr int kTileBytes = 2 * kGroupRows * kRowStride * static_cast<int>(sizeof(float));
+    auto kernel = !scale ? softmax_kernel<false, false>
+                         : (keep ? softmax_kernel<true, true> : softmax_kernel<true, false>);
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTileBytes)
+        != cudaSuccess) {
+        return check_launch("sdpa softmax shared-memory attribute");
+    }
+    kernel<<<grid, kSoftmaxThreads, kTileBytes, s>>>(p);
     return check_launch("sdpa softmax launch");
 }
 
@@ -478,6 +613,14 @@ extern "C" int iomb_sdpa_canonicalize_output(const iomb_view* out, void* stream)
     p.tile_cols = static_cast<uint32_t>(facts.tile_cols);
     p.groups = (p.tile_cols + kCanonTiles - 1) / kCanonTiles;
     p.items = p.leading.planes * facts.tile_rows * p.groups;
+    if (p.leading.contiguous && facts.rows % kTile == 0 && facts.cols % kTile == 0) {
+        unsigned char* start = static_cast<unsigned char*>(out->base) + out->plane_offset * facts.plane_bytes;
+        const uint64_t pairs = p.leading.planes * facts.plane_bytes / 32;
+        const uint64_t per_cta = static_cast<uint64_t>(kCanonThreads) * 4;
+        canonicalize_linear_kernel<<<grid_one_shot((pairs + per_cta - 1) / per_cta), kCanonThreads, 0,
+                                     static_cast<cudaStream_t>(stream)>>>(start, pairs);
+        return check_launch("sdpa canonicalize launch");
+    }
     const uint64_t ctas = (p.items + kCanonThreads / 32 - 1) / (kCanonThreads / 32);
     canonicalize_kernel<<<grid_one_shot(ctas), kCanonThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
     return check_launch("sdpa canonicalize launch");

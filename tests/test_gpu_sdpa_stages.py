@@ -187,7 +187,8 @@ def special_codes(rng, shape):
     return codes
 
 
-@pytest.mark.parametrize("shape", [(2, 17, 32), (1, 1, 64), (3, 2, 33, 40), (130, 2048), (5, 16, 7)])
+@pytest.mark.parametrize("shape", [(2, 17, 32), (1, 1, 64), (3, 2, 33, 40), (130, 2048), (5, 16, 7),
+                                   (3, 32, 64), (144, 2048), (2, 3, 16, 16)])
 def test_output_canonicalisation_against_the_oracle_and_the_reference(gpu, shape):
     device, queue = gpu
     rng = np.random.default_rng(21)
