@@ -116,7 +116,16 @@ GEOMETRIES = [
 ]
 
 
-@pytest.mark.parametrize("geometry", GEOMETRIES)
+# At least 256 rows per SM of a B200 (37 888) of at most 512 tokens: these run the kernel
+# with one lane per row.
+MANY_ROWS = [
+    (1, 64, 4, 600, 700, 64, 12, 500),     # prefixes up to 500 tokens, 38 400 rows
+    (300, 8, 2, 16, 40, 16, 24, 40),       # short rows, many planes
+    (2, 148, 37, 130, 200, 8, 3, 77),      # L < a + R, head count not a multiple of 32
+]
+
+
+@pytest.mark.parametrize("geometry", GEOMETRIES + MANY_ROWS)
 def test_stages_against_the_oracle(gpu, geometry):
     device, queue = gpu
     host = random_case(11, *geometry)
@@ -142,7 +151,7 @@ def test_stages_against_the_oracle(gpu, geometry):
     ds.close()
 
 
-@pytest.mark.parametrize("geometry", GEOMETRIES)
+@pytest.mark.parametrize("geometry", GEOMETRIES + MANY_ROWS)
 def test_stages_bit_identical_to_the_reference_kernels(gpu, geometry):
     lib = sdpa_reference_stages_or_skip()
     device, queue = gpu
@@ -163,7 +172,7 @@ def test_stages_bit_identical_to_the_reference_kernels(gpu, geometry):
 
 
 @pytest.mark.parametrize("keep", [False, True])
-@pytest.mark.parametrize("geometry", GEOMETRIES[:5])
+@pytest.mark.parametrize("geometry", GEOMETRIES[:5] + MANY_ROWS)
 def test_fused_stage_equals_the_two_launches(gpu, geometry, keep):
     device, queue = gpu
     host = random_case(13, *geometry)
