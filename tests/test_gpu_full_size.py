@@ -64,6 +64,7 @@ def test_fused_add_rmsnorm_at_the_benchmark_size(big):
     w = device.create_tensor(hw.spec)
     w.storage().copy_(torch.from_numpy(hw.storage.copy()))
     total, out, total2, out2 = (device.create_tensor(TensorSpec(shape, DataType.BF16)) for _ in range(4))
+    torch.cuda.synchronize()      # the fills ran on torch's stream, the operations use the queue's
     run(queue, queue.add_rmsnorm(x.view(), r.view(), w.view(), total.view(), out.view(), 1e-5))
     assert oracle().iomo_binary(0, abi(hx.view()), abi(hr.view()), abi(hs.view()), 0) == 0
     assert oracle().iomo_rmsnorm(abi(hs.view()), abi(hw.view()), abi(ho.view()), 1e-5, 0) == 0
@@ -95,6 +96,7 @@ def test_rmsnorm_at_the_sharded_size(big):
     w = device.create_tensor(hw.spec)
     w.storage().copy_(torch.from_numpy(hw.storage.copy()))
     out = device.create_tensor(TensorSpec((32768, 8192), DataType.BF16))
+    torch.cuda.synchronize()
     for order in (0, 1):
         run(queue, queue.rmsnorm(x.view(), w.view(), out.view(), 1e-6, order=order))
         assert oracle().iomo_rmsnorm(abi(hx.view()), abi(hw.view()), abi(ho.view()), 1e-6, order) == 0
@@ -106,6 +108,7 @@ def test_rmsnorm_at_the_sharded_size(big):
     ones.storage().view(torch.int16).fill_(0x3F80)
     scratch = device.create_workspace(int(device._lib.iomb_sumsq_scratch_bytes()))
     cell = device.create_workspace(32)
+    torch.cuda.synchronize()
     run(queue, queue.sumsq(ones.view(), scratch.view(), cell.view().address()))
     value = cell.tensor()[:4].view(torch.float32).item()
     assert value == float(1 << 28)
@@ -142,6 +145,7 @@ def test_elementwise_at_two_to_the_thirty(big, dtype, op):
     row.storage().view(torch_type).fill_(identity)
     col.storage().view(torch_type).fill_(identity)
     fn = getattr(queue, op)
+    torch.cuda.synchronize()      # the fills ran on torch's stream, the operations use the queue's
     # the operation is commutative bit for bit
     run(queue, fn(x.view(), y.view(), o.view()))
     run(queue, fn(y.view(), x.view(), o2.view()))
@@ -183,6 +187,7 @@ def test_decode_step_data_movement_at_full_geometry(big):
         tensors.append(t)
     dt, di, do = tensors
     workspace = device.create_workspace(32)
+    torch.cuda.synchronize()
     run(queue, queue.embedding(dt.view(), di.view(), do.view(), workspace.view()))
     status = ctypes.c_uint32(9)
     assert oracle().iomo_embedding(abi(table.view()), abi(ids.view()), abi(out.view()),
@@ -195,6 +200,7 @@ def test_decode_step_data_movement_at_full_geometry(big):
     dl, dw = device.create_tensor(logits.spec), device.create_tensor(wide.spec)
     dl.storage().copy_(torch.from_numpy(logits.storage.copy()))
     dw.storage().copy_(torch.from_numpy(wide.storage.copy()))
+    torch.cuda.synchronize()
     run(queue, queue.cast(dl.view(), dw.view()))
     assert oracle().iomo_cast(abi(logits.view()), abi(wide.view())) == 0
     assert np.array_equal(dw.storage().cpu().numpy(), wide.storage)
