@@ -53,5 +53,21 @@ oid cache_append_batched(DeviceOps& queue, const TensorView& source, TensorView&
 oid sumsq(DeviceOps& queue, const TensorView& x, void* scratch, float* result);
 [[nodiscard]] std::size_t sumsq_scratch_bytes();
 
+// The attention stages that are not matrix products, on the two workspace segments of the
+// reference's CUDA backend (src/cuda/sdpa_nonmatrix_request.hpp:22-49): FP32 scores and BF16
+// probabilities, both [planes, Hq, pad16(R), pad16(L)], device pointers aligned to 32 bytes.
+// They replace launch_sdpa_scale_mask / launch_sdpa_softmax / launch_sdpa_canonicalize_output
+// (src/cuda/sdpa_nonmatrix.hpp:15-28); sdpa_scale_mask_softmax does the first two in one pass
+// and stores the scaled scores only when asked to.
+struct SdpaStages {
+    float* scores = nullptr;
+    void* probability = nullptr;
+    std::uint64_t planes = 0, Hq = 0, Hkv = 0, R = 0, C = 0, D = 0, a = 0, L = 0;
+};
+oid sdpa_scale_mask(DeviceOps& queue, const SdpaStages& stages);
+oid sdpa_softmax(DeviceOps& queue, const SdpaStages& stages);
+oid sdpa_scale_mask_softmax(DeviceOps& queue, const SdpaStages& stages, bool keep_scores);
+oid sdpa_canonicalize_output(DeviceOps& queue, TensorView& out);
+
 }  // namespace b200
 }  // namespace iom

@@ -507,6 +507,26 @@ public:
         });
     }
 
+    // stage: 0 scale/mask, 1 softmax, 2 both (scores only read), 3 both (scaled scores stored)
+    oid sdpa_stage(int stage, const b200::SdpaStages& s) {
+        const iomb_sdpa_stages request{s.scores, s.probability, s.planes, s.Hq, s.Hkv,
+                                       s.R, s.C, s.D, s.a, s.L};
+        return extension({}, [stage, request](cudaStream_t stream) {
+            switch (stage) {
+                case 0: return iomb_sdpa_scale_mask(&request, stream);
+                case 1: return iomb_sdpa_softmax(&request, stream);
+                default: return iomb_sdpa_scale_mask_softmax(&request, stage == 3 ? 1 : 0, stream);
+            }
+        });
+    }
+
+    oid sdpa_canonicalize_output(TensorView& out) {
+        const iomb_view vo = to_view(out);
+        return extension({&out}, [vo](cudaStream_t stream) {
+            return iomb_sdpa_canonicalize_output(&vo, stream);
+        });
+    }
+
 protected:
     [[nodiscard]] std::string_view backend_label() const noexcept override { return "B200"; }
 
@@ -839,6 +859,25 @@ oid sumsq(DeviceOps& queue, const TensorView& x, void* scratch, float* result) {
     auto* native = dynamic_cast<B200Queue*>(&queue);
     if (native == nullptr) return to_oid(OidError::InvalidArgument);
     return native->sumsq(x, scratch, result);
+}
+
+namespace {
+oid sdpa_stage_of(DeviceOps& queue, int stage, const SdpaStages& stages) {
+    auto* native = dynamic_cast<B200Queue*>(&queue);
+    if (native == nullptr) return to_oid(OidError::InvalidArgument);
+    return native->sdpa_stage(stage, stages);
+}
+}  // namespace
+
+oid sdpa_scale_mask(DeviceOps& queue, const SdpaStages& stages) { return sdpa_stage_of(queue, 0, stages); }
+oid sdpa_softmax(DeviceOps& queue, const SdpaStages& stages) { return sdpa_stage_of(queue, 1, stages); }
+oid sdpa_scale_mask_softmax(DeviceOps& queue, const SdpaStages& stages, bool keep_scores) {
+    return sdpa_stage_of(queue, keep_scores ? 3 : 2, stages);
+}
+oid sdpa_canonicalize_output(DeviceOps& queue, TensorView& out) {
+    auto* native = dynamic_cast<B200Queue*>(&queue);
+    if (native == nullptr) return to_oid(OidError::InvalidArgument);
+    return native->sdpa_canonicalize_output(out);
 }
 
 std::size_t sumsq_scratch_bytes() { return static_cast<std::size_t>(iomb_sumsq_scratch_bytes()); }

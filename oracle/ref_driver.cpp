@@ -445,6 +445,32 @@ std::int64_t iomref_sumsq(void* queue, void* x, float* value_out) {
     cudaFree(scratch);
     return token;
 }
+
+// stage 0..3 as B200Queue::sdpa_stage, 4 = canonicalise `out`; device pointers from the caller.
+std::int64_t iomref_sdpa_stage_b200(void* queue, int stage, void* scores, void* probability,
+                                    const std::uint64_t* geometry, void* out) {
+    std::int64_t token;
+    if (stage == 4) {
+        token = iom::b200::sdpa_canonicalize_output(ops_of(queue), view_of(out));
+    } else {
+        iom::b200::SdpaStages s;
+        s.scores = static_cast<float*>(scores);
+        s.probability = probability;
+        s.planes = geometry[0]; s.Hq = geometry[1]; s.Hkv = geometry[2]; s.R = geometry[3];
+        s.C = geometry[4]; s.D = geometry[5]; s.a = geometry[6]; s.L = geometry[7];
+        if (stage == 0) token = iom::b200::sdpa_scale_mask(ops_of(queue), s);
+        else if (stage == 1) token = iom::b200::sdpa_softmax(ops_of(queue), s);
+        else token = iom::b200::sdpa_scale_mask_softmax(ops_of(queue), s, stage == 3);
+    }
+    if (token > 0) {
+        try {
+            ops_of(queue).wait(token);
+        } catch (...) {
+            return -5;
+        }
+    }
+    return token;
+}
 #endif
 
 }  // extern "C"

@@ -281,6 +281,8 @@ class Reference:
                                                                  ctypes.c_uint32,
                                                                  ctypes.POINTER(ctypes.c_uint32)]),
                 "iomref_sumsq": (ctypes.c_int64, [vp, vp, ctypes.POINTER(ctypes.c_float)]),
+                "iomref_sdpa_stage_b200": (ctypes.c_int64, [vp, ctypes.c_int, vp, vp,
+                                                            ctypes.POINTER(ctypes.c_uint64), vp]),
             })
         for name, (restype, argtypes) in spec.items():
             fn = getattr(lib, name)

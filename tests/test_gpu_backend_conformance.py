@@ -281,6 +281,57 @@ def test_extension_entries_of_the_cpp_backend(pair):
     assert abs(result.value - truth) <= 1e-6 * truth
 
 
+def test_attention_stage_extensions_of_the_cpp_backend(pair):
+    """The attention stages through the C++ backend's extension functions: two launches and
+    the fused one against the oracle (scores bit for bit up to NaN payloads, probabilities
+    within one BF16 code), the fused stage equal to the two launches, and the output
+    canonicalisation against its rule (-0 to +0, every NaN to 0x7FC0)."""
+    import ctypes
+    import torch
+    from sdpa_stage_cases import random_case
+    cpu, gpu = pair
+    geometry = (2, 4, 2, 37, 64, 16, 5, 45)
+    host = random_case(31, *geometry)
+    raw_scores = host.scores.copy()
+    packed = (ctypes.c_uint64 * 8)(*geometry)
+
+    def device_copy():
+        return (torch.from_numpy(raw_scores.copy()).cuda(),
+                torch.from_numpy(host.probability.astype(np.int16).copy()).cuda())
+
+    s2, p2 = device_copy()
+    for stage in (0, 1):
+        assert gpu.lib.iomref_sdpa_stage_b200(gpu.queue, stage, s2.data_ptr(), p2.data_ptr(), packed, None) > 0
+    s1, p1 = device_copy()
+    assert gpu.lib.iomref_sdpa_stage_b200(gpu.queue, 3, s1.data_ptr(), p1.data_ptr(), packed, None) > 0
+    s0, p0 = device_copy()
+    assert gpu.lib.iomref_sdpa_stage_b200(gpu.queue, 2, s0.data_ptr(), p0.data_ptr(), packed, None) > 0
+    torch.cuda.synchronize()
+    assert torch.equal(p1, p2) and torch.equal(p0, p2)
+    assert torch.equal(s1.view(torch.int32), s2.view(torch.int32))
+    assert np.array_equal(s0.cpu().numpy().view(np.uint32), raw_scores.view(np.uint32))   # only read
+    host.scale_mask().softmax()
+    got_scores = s2.cpu().numpy()
+    same = (got_scores.view(np.uint32) == host.scores.view(np.uint32)) | (np.isnan(got_scores) & np.isnan(host.scores))
+    assert same.all()
+    distance = np.abs(p2.cpu().numpy().view(np.uint16).astype(np.int32) - host.probability.astype(np.int32))
+    assert distance.max() <= 1 and (distance != 0).mean() <= 2e-3
+
+    rng = np.random.default_rng(32)
+    codes = rng.integers(0, 65536, size=(3, 19, 40), dtype=np.uint16)
+    codes[0, 0, :4] = [0x8000, 0x7FFF, 0xFF81, 0x3F80]
+    out = gpu.tensor((3, 19, 40), DataType.BF16)
+    out.view().from_host(codes)
+    assert gpu.lib.iomref_sdpa_stage_b200(gpu.queue, 4, None, None, packed, out.view().handle) > 0
+    got = out.view().to_host()
+    expected = codes.copy()
+    zero = (codes & 0x7FFF) == 0
+    nan = ((codes & 0x7F80) == 0x7F80) & ((codes & 0x007F) != 0)
+    expected[zero] = 0
+    expected[nan] = 0x7FC0
+    assert np.array_equal(np.asarray(got).view(np.uint16).reshape(codes.shape), expected)
+
+
 def test_host_transfers_and_fused_extension(pair):
     cpu, gpu = pair
     rng = np.random.default_rng(10)
