@@ -23,6 +23,8 @@
 // needs no special path here.
 #include "host.hpp"
 
+#include <type_traits>
+
 #include <cuda_fp16.h>
 
 namespace iomb {
@@ -407,17 +409,20 @@ static int launch_op(int op, const BinaryParams& params, bool linear,
 
 // ---- every other byte-multiple leaf: one thread per logical element ------------
 //
-// I8/U8, I16/U16, I64/U64 (wrapping ADD/MUL/SUB) and F16 (one IEEE binary32
+// I8/U8, I16/U16, I64/U64 (wrapping ADD/MUL/SUB), F16 (one IEEE binary32
 // operation, one RNE narrowing to binary16, positive quiet NaN 0x7E00: equal to the
-// reference codec because 24 >= 2 * 11 + 2). These leaves are off the serving
+// reference codec because 24 >= 2 * 11 + 2) and the two 8-bit floating leaves
+// F8_E4M3FN / F8_E5M2 (decoded exactly to binary32, one binary32 operation, one encode
+// by the codec's rules, see F8Format). These leaves are off the serving
 // path, so the kernel is the simple one: thread e owns logical element e of the
 // result, reads its two inputs through the same tile map the fast kernels use and
 // writes one element; broadcast operands read their row 0 / column 0.
-enum class Wide : int { Int8 = 0, Int16 = 1, Int64 = 2, Half = 3 };
+enum class Wide : int { Int8 = 0, Int16 = 1, Int64 = 2, Half = 3, F8E4M3 = 4, F8E5M2 = 5 };
 
 template <Wide W>
 struct WideTraits {
-    static constexpr int kBytes = W == Wide::Int8 ? 1 : W == Wide::Int64 ? 8 : 2;
+    static constexpr int kBytes =
+            (W == Wide::Int8 || W == Wide::F8E4M3 || W == Wide::F8E5M2) ? 1 : W == Wide::Int64 ? 8 : 2;
 };
 
 template <int BYTES>
@@ -434,9 +439,84 @@ __device__ __forceinline__ void store_element(unsigned char* address, uint64_t v
     else *reinterpret_cast<uint64_t*>(address) = value;
 }
 
+// The 8-bit floating formats as the reference codec defines them
+// (src/shared/scalar_binary_codec.hpp:30-108). E4M3FN: bias 7, finite only, yet every code
+// with all exponent bits set decodes as NaN, so the largest finite value is 240 (0x77),
+// which is also what an overflow or an infinite result encodes to; NaN is 0x7F. E5M2: bias
+// 15, infinities 0x7C / 0xFC, NaN 0x7E. Results are NaN-positive, zeros keep their sign,
+// subnormals are kept, rounding is to nearest even.
+template <int EBITS, int FBITS, int BIAS, bool INFS>
+struct F8Format {
+    static constexpr uint32_t kExpMask = (1u << EBITS) - 1;
+    static constexpr uint32_t kFracMask = (1u << FBITS) - 1;
+    static constexpr int kMinSub = 1 - BIAS - FBITS;            // exponent of the smallest subnormal
+    static constexpr int kMaxExp = static_cast<int>(kExpMask) - 1 - BIAS;
+    static constexpr uint32_t kNan = (kExpMask << FBITS) | (INFS ? 1u << (FBITS - 1) : kFracMask);
+    static constexpr uint32_t kOverflow = INFS ? kExpMask << FBITS : ((kExpMask - 1) << FBITS) | kFracMask;
+
+    __device__ static float decode(uint32_t raw) {
+        const uint32_t sign = (raw >> (EBITS + FBITS)) & 1u;
+        const uint32_t exponent = (raw >> FBITS) & kExpMask;
+        const uint32_t fraction = raw & kFracMask;
+        float value;
+        if (exponent == kExpMask) {
+            value = (INFS && fraction == 0) ? __uint_as_float(0x7f800000u) : __uint_as_float(0x7fc00000u);
+        } else if (exponent == 0) {
+            value = __fmul_rn(__uint2float_rn(fraction),
+                              __uint_as_float(static_cast<uint32_t>(kMinSub + 127) << 23));
+        } else {
+            value = __fmul_rn(__uint2float_rn((1u << FBITS) + fraction),
+                              __uint_as_float((exponent + 127u - BIAS - FBITS) << 23));
+        }
+        return sign ? -value : value;
+    }
+
+    // `value` is a binary32 result of one operation on two decoded operands: zero, normal,
+    // infinite or NaN (the smallest nonzero magnitude, 2^-32, is far above binary32's
+    // subnormal range).
+    __device__ static uint32_t encode(float value) {
+        if (value != value) return kNan;
+        const uint32_t bits = __float_as_uint(value);
+        const uint32_t sign = (bits >> 31) << (EBITS + FBITS);
+        const uint32_t magnitude = bits & 0x7fffffffu;
+        if (magnitude == 0x7f800000u) return sign | kOverflow;
+        if (magnitude == 0) return sign;
+        int exponent = static_cast<int>(magnitude >> 23) - 127;
+        const uint32_t significand = (magnitude & 0x007fffffu) | 0x00800000u;   // 24 bits
+        if (exponent < kMinSub + FBITS) {
+            // q = RNE(value * 2^-kMinSub); q == 2^FBITS is the smallest normal's code
+            const int shift = 23 + kMinSub - exponent;
+            if (shift > 25) return sign;
+            const uint32_t kept = significand >> shift;
+            const uint32_t rest = significand & ((1u << shift) - 1u);
+            const uint32_t half = 1u << (shift - 1);
+            return sign | (kept + ((rest > half || (rest == half && (kept & 1u))) ? 1u : 0u));
+        }
+        if (exponent > kMaxExp) return sign | kOverflow;
+        constexpr int kShift = 23 - FBITS;
+        uint32_t kept = significand >> kShift;                    // 1.fraction, FBITS + 1 bits
+        const uint32_t rest = significand & ((1u << kShift) - 1u);
+        constexpr uint32_t kHalf = 1u << (kShift - 1);
+        kept += (rest > kHalf || (rest == kHalf && (kept & 1u))) ? 1u : 0u;
+        if (kept == (2u << FBITS)) {
+            kept = 1u << FBITS;
+            ++exponent;
+        }
+        if (exponent > kMaxExp) return sign | kOverflow;
+        return sign | (static_cast<uint32_t>(exponent + BIAS) << FBITS) | (kept & kFracMask);
+    }
+};
+using F8E4M3Format = F8Format<4, 3, 7, false>;
+using F8E5M2Format = F8Format<5, 2, 15, true>;
+
 template <Wide W, int OP>
 __device__ __forceinline__ uint64_t apply_wide(uint64_t a, uint64_t b) {
-    if constexpr (W == Wide::Half) {
+    if constexpr (W == Wide::F8E4M3 || W == Wide::F8E5M2) {
+        using Format = typename std::conditional<W == Wide::F8E4M3, F8E4M3Format, F8E5M2Format>::type;
+        const float r = apply_f32<OP>(Format::decode(static_cast<uint32_t>(a)),
+                                      Format::decode(static_cast<uint32_t>(b)));
+        return Format::encode(r);
+    } else if constexpr (W == Wide::Half) {
         const float x = __half2float(__ushort_as_half(static_cast<unsigned short>(a)));
         const float y = __half2float(__ushort_as_half(static_cast<unsigned short>(b)));
         const float r = apply_f32<OP>(x, y);
@@ -481,7 +561,7 @@ static int launch_element(int op, const BinaryParams& params, cudaStream_t strea
         case IOMB_MUL: binary_element_kernel<W, IOMB_MUL><<<grid, kTiledThreads, 0, stream>>>(params, elements); break;
         case IOMB_SUB: binary_element_kernel<W, IOMB_SUB><<<grid, kTiledThreads, 0, stream>>>(params, elements); break;
         default:
-            if constexpr (W == Wide::Half) {
+            if constexpr (W == Wide::Half || W == Wide::F8E4M3 || W == Wide::F8E5M2) {
                 binary_element_kernel<W, IOMB_DIV><<<grid, kTiledThreads, 0, stream>>>(params, elements);
             } else {
                 return fail(IOMB_ERR_UNSUPPORTED, "binary: integer division is not admitted");
@@ -572,9 +652,11 @@ extern "C" int iomb_binary(int op, const iomb_view* lhs, const iomb_view* rhs,
         case IOMB_I16: case IOMB_U16: wide = static_cast<int>(Wide::Int16); break;
         case IOMB_I64: case IOMB_U64: wide = static_cast<int>(Wide::Int64); break;
         case IOMB_F16: wide = static_cast<int>(Wide::Half); break;
+        case IOMB_F8_E4M3FN: wide = static_cast<int>(Wide::F8E4M3); break;
+        case IOMB_F8_E5M2: wide = static_cast<int>(Wide::F8E5M2); break;
         default:
             return fail(IOMB_ERR_UNSUPPORTED,
-                        "binary: leaf is not a byte-multiple integer, F16, BF16 or F32");
+                        "binary: leaf is not a byte-multiple integer, F8_E4M3FN, F8_E5M2, F16, BF16 or F32");
     }
 
     BinaryParams params{};
@@ -599,6 +681,8 @@ extern "C" int iomb_binary(int op, const iomb_view* lhs, const iomb_view* rhs,
             case Wide::Int8: return launch_element<Wide::Int8>(op, params, element_stream);
             case Wide::Int16: return launch_element<Wide::Int16>(op, params, element_stream);
             case Wide::Int64: return launch_element<Wide::Int64>(op, params, element_stream);
+            case Wide::F8E4M3: return launch_element<Wide::F8E4M3>(op, params, element_stream);
+            case Wide::F8E5M2: return launch_element<Wide::F8E5M2>(op, params, element_stream);
             default: return launch_element<Wide::Half>(op, params, element_stream);
         }
     }

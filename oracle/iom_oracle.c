@@ -320,6 +320,15 @@ uint64_t iomo_scalar_binary_ieee(int op, uint32_t dtype, uint64_t a, uint64_t b)
         return (op == 0 ? a + b : op == 1 ? a * b : a - b) & mask;
     }
     float x, y;
+    if (dtype == DT_F8_E4M3FN || dtype == DT_F8_E5M2) {
+        /* exact decode, one binary32 operation, one encode: 24 >= 2 * 4 + 2 */
+        const format_t f8 = format_of(dtype);
+        x = (float)codec_decode(a, f8);
+        y = (float)codec_decode(b, f8);
+        volatile float r8 = op == 0 ? x + y : op == 1 ? x * y : op == 2 ? x - y : x / y;
+        const float narrow = r8;
+        return isnan(narrow) ? codec_encode((long double)NAN, f8) : codec_encode((long double)narrow, f8);
+    }
     if (dtype == DT_F16) {
         x = half_to_float((uint32_t)a);
         y = half_to_float((uint32_t)b);
@@ -345,9 +354,11 @@ uint64_t iomo_codec_mismatches(int op, uint32_t dtype, const void* a, uint64_t n
     const uint32_t bits = iomo_leaf_bits(dtype);
     uint64_t mismatches = 0;
     for (uint64_t i = 0; i < na; ++i) {
-        const uint64_t x = bits == 16 ? ((const uint16_t*)a)[i] : ((const uint32_t*)a)[i];
+        const uint64_t x = bits == 8 ? ((const uint8_t*)a)[i]
+                : bits == 16 ? ((const uint16_t*)a)[i] : ((const uint32_t*)a)[i];
         for (uint64_t j = 0; j < nb; ++j) {
-            const uint64_t y = bits == 16 ? ((const uint16_t*)b)[j] : ((const uint32_t*)b)[j];
+            const uint64_t y = bits == 8 ? ((const uint8_t*)b)[j]
+                    : bits == 16 ? ((const uint16_t*)b)[j] : ((const uint32_t*)b)[j];
             if (iomo_scalar_binary(op, dtype, x, y) != iomo_scalar_binary_ieee(op, dtype, x, y)) {
                 ++mismatches;
             }

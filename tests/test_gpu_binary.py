@@ -10,7 +10,8 @@ pytestmark = pytest.mark.gpu
 OPS = {"add": 0, "mul": 1, "sub": 2, "div": 3}
 DTYPES = [DataType.I32, DataType.U32, DataType.F32, DataType.BF16,
           # per-element kernel: the other byte-multiple integers and F16
-          DataType.I8, DataType.U8, DataType.I16, DataType.U16, DataType.I64, DataType.U64, DataType.F16]
+          DataType.I8, DataType.U8, DataType.I16, DataType.U16, DataType.I64, DataType.U64, DataType.F16,
+          DataType.F8_E4M3FN, DataType.F8_E5M2]
 INTEGERS = (DataType.I8, DataType.U8, DataType.I16, DataType.U16, DataType.I32, DataType.U32,
             DataType.I64, DataType.U64)
 
@@ -129,6 +130,23 @@ def test_binary_exhaustive_f16_pairs(gpu):
             t.close()
 
 
+@pytest.mark.parametrize("dtype", [DataType.F8_E4M3FN, DataType.F8_E5M2])
+def test_binary_every_f8_pair(gpu, dtype):
+    """All 65 536 pairs of an 8-bit floating leaf, all four operations, against the codec."""
+    device, queue = gpu
+    codes = np.arange(256, dtype=np.uint8)
+    lhs, rhs, out = (HostTensor((256, 256), dtype) for _ in range(3))
+    lhs.view().copy_from_host(np.repeat(codes, 256).reshape(256, 256))
+    rhs.view().copy_from_host(np.tile(codes, 256).reshape(256, 256))
+    for op in ("add", "mul", "sub", "div"):
+        dl, dr, do = upload(device, lhs), upload(device, rhs), upload(device, out)
+        run(queue, getattr(queue, op)(dl.view(), dr.view(), do.view()))
+        assert oracle().iomo_binary(OPS[op], abi(lhs.view()), abi(rhs.view()), abi(out.view()), 0) == 0
+        assert np.array_equal(download(do), out.storage), op
+        for t in (dl, dr, do):
+            t.close()
+
+
 def test_binary_views_and_alias(gpu):
     device, queue = gpu
     rng = np.random.default_rng(7)
@@ -190,6 +208,8 @@ def test_binary_rejections(gpu):
     i8 = device.create_tensor(HostTensor((16, 16), DataType.I8).spec)
     assert queue.div(i8.view(), i8.view(), i8.view()) == -2
     f8 = device.create_tensor(HostTensor((16, 16), DataType.F8_E5M2).spec)
-    assert queue.add(f8.view(), f8.view(), f8.view()) == -2       # leaf not served
+    assert queue.div(f8.view(), f8.view(), f8.view()) > 0         # a floating leaf: division exists
+    e8 = device.create_tensor(HostTensor((16, 16), DataType.F8_E8M0).spec)
+    assert queue.add(e8.view(), e8.view(), e8.view()) == -2       # not a numeric leaf
     with pytest.raises(ValueError):
         queue.wait(12345)

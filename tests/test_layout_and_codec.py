@@ -122,6 +122,30 @@ def test_ieee_form_equals_codec_f16(op):
     assert mismatches == 0
 
 
+@pytest.mark.parametrize("dtype", [DataType.F8_E4M3FN, DataType.F8_E5M2])
+@pytest.mark.parametrize("op", [ADD, MUL, SUB, DIV])
+def test_ieee_form_equals_codec_f8_every_pair(op, dtype):
+    """All 65 536 pairs of the 8-bit floating leaves: exact decode, one binary32 operation and
+    one encode by the codec's rules equal the reference codec's long double evaluation."""
+    codes = np.arange(256, dtype=np.uint8)
+    assert oracle().iomo_codec_mismatches(op, int(dtype), codes.ctypes.data, 256, codes.ctypes.data, 256) == 0
+
+
+def test_f8_known_codes():
+    """The codec's reading of the two formats (src/shared/scalar_binary_codec.hpp:30-108):
+    E4M3FN has no infinities and every all-ones exponent is NaN, so 240 (0x77) is the largest
+    value and the overflow code; E5M2 overflows to its infinities."""
+    e4, e5 = int(DataType.F8_E4M3FN), int(DataType.F8_E5M2)
+    assert binary(ADD, DataType.F8_E4M3FN, 0x77, 0x77) == 0x77          # 240 + 240 saturates
+    assert binary(ADD, DataType.F8_E4M3FN, 0x78, 0x00) == 0x7F          # exponent 15 reads as NaN
+    assert binary(MUL, DataType.F8_E4M3FN, 0x01, 0x01) == 0x00          # 2^-18 rounds to zero
+    assert binary(SUB, DataType.F8_E4M3FN, 0x38, 0x38) == 0x00          # 1 - 1 = +0
+    assert binary(ADD, DataType.F8_E5M2, 0x7B, 0x7B) == 0x7C            # 57344 * 2 -> +inf
+    assert binary(SUB, DataType.F8_E5M2, 0x7C, 0x7C) == 0x7E            # inf - inf -> NaN
+    assert binary(DIV, DataType.F8_E5M2, 0x3C, 0x80) == 0xFC            # 1 / -0 -> -inf
+    assert e4 == 16 and e5 == 17
+
+
 @pytest.mark.parametrize("op", [ADD, MUL, SUB, DIV])
 def test_ieee_form_equals_codec_f32(op):
     rng = np.random.default_rng(9)
