@@ -116,8 +116,9 @@ uint64_t iomb_plane_slot(uint64_t rows, uint64_t columns, uint64_t plane,
  * (src/shared/gpu_queue_operations.inl:65-124,756-818; src/shared/standard_tiled_add.inl:206-464);
  * admission rules of DeviceOps::validate_binary (src/device_ops_binary.cpp:102-181).
  * Leaves: I32/U32, F32, BF16 on the vector kernels; I8/U8, I16/U16, I64/U64, F16, F8_E4M3FN and
- * F8_E5M2 on a per-element kernel. Integers wrap and have no division
- * (src/device_ops_binary.cpp:46-57).
+ * F8_E5M2 on a per-element kernel; I2/U2, I4/U4, F4_E2M1, F6_E2M3, F6_E3M2 on a kernel that
+ * owns whole tile rows (padding bits survive). Every numeric leaf of the reference except F64.
+ * Integers wrap and have no division (src/device_ops_binary.cpp:46-57).
  * Arithmetic equals the scalar codec (src/shared/scalar_binary_codec.hpp:120-178):
  * IEEE binary32 op (division correctly rounded), one RNE encode, every NaN result is
  * the positive quiet NaN (0x7FC00000 / 0x7FC0).

@@ -567,6 +567,8 @@ protected:
         switch (request.out.spec.data_type) {
             case DataType::I8: case DataType::U8: case DataType::I16: case DataType::U16:
             case DataType::I32: case DataType::U32: case DataType::I64: case DataType::U64:
+            case DataType::I2: case DataType::U2: case DataType::I4: case DataType::U4:
+            case DataType::F4_E2M1: case DataType::F6_E2M3: case DataType::F6_E3M2:
             case DataType::F8_E4M3FN: case DataType::F8_E5M2:
             case DataType::F16: case DataType::BF16: case DataType::F32: break;
             default: throw detail::UnsupportedOperation();

@@ -445,21 +445,27 @@ __device__ __forceinline__ void store_element(unsigned char* address, uint64_t v
 // which is also what an overflow or an infinite result encodes to; NaN is 0x7F. E5M2: bias
 // 15, infinities 0x7C / 0xFC, NaN 0x7E. Results are NaN-positive, zeros keep their sign,
 // subnormals are kept, rounding is to nearest even.
-template <int EBITS, int FBITS, int BIAS, bool INFS>
+//
+// RESERVED = false is the codec's rule for the formats with fewer than four exponent bits
+// (F4_E2M1, F6_E2M3, F6_E3M2): every code is a finite value, and an infinite or NaN result
+// encodes to the largest value (a NaN to the positive one).
+template <int EBITS, int FBITS, int BIAS, bool INFS, bool RESERVED = true>
 struct F8Format {
     static constexpr uint32_t kExpMask = (1u << EBITS) - 1;
     static constexpr uint32_t kFracMask = (1u << FBITS) - 1;
+    static constexpr uint32_t kTopExp = kExpMask - (RESERVED ? 1u : 0u);   // largest finite exponent field
     static constexpr int kMinSub = 1 - BIAS - FBITS;            // exponent of the smallest subnormal
-    static constexpr int kMaxExp = static_cast<int>(kExpMask) - 1 - BIAS;
-    static constexpr uint32_t kNan = (kExpMask << FBITS) | (INFS ? 1u << (FBITS - 1) : kFracMask);
-    static constexpr uint32_t kOverflow = INFS ? kExpMask << FBITS : ((kExpMask - 1) << FBITS) | kFracMask;
+    static constexpr int kMaxExp = static_cast<int>(kTopExp) - BIAS;
+    static constexpr uint32_t kOverflow = INFS ? kExpMask << FBITS : (kTopExp << FBITS) | kFracMask;
+    static constexpr uint32_t kNan = !RESERVED ? kOverflow
+            : (kExpMask << FBITS) | (INFS ? 1u << (FBITS - 1) : kFracMask);
 
     __device__ static float decode(uint32_t raw) {
         const uint32_t sign = (raw >> (EBITS + FBITS)) & 1u;
         const uint32_t exponent = (raw >> FBITS) & kExpMask;
         const uint32_t fraction = raw & kFracMask;
         float value;
-        if (exponent == kExpMask) {
+        if (RESERVED && exponent == kExpMask) {
             value = (INFS && fraction == 0) ? __uint_as_float(0x7f800000u) : __uint_as_float(0x7fc00000u);
         } else if (exponent == 0) {
             value = __fmul_rn(__uint2float_rn(fraction),
@@ -508,6 +514,9 @@ struct F8Format {
 };
 using F8E4M3Format = F8Format<4, 3, 7, false>;
 using F8E5M2Format = F8Format<5, 2, 15, true>;
+using F4E2M1Format = F8Format<2, 1, 1, false, false>;
+using F6E2M3Format = F8Format<2, 3, 1, false, false>;
+using F6E3M2Format = F8Format<3, 2, 3, false, false>;
 
 template <Wide W, int OP>
 __device__ __forceinline__ uint64_t apply_wide(uint64_t a, uint64_t b) {
@@ -550,6 +559,93 @@ binary_element_kernel(const BinaryParams p, uint64_t elements) {
         const uint64_t b = load_element<BYTES>(slot(p.rhs));
         store_element<BYTES>(const_cast<unsigned char*>(slot(p.out)), apply_wide<W, OP>(a, b));
     }
+}
+
+// ---- leaves narrower than a byte: one thread per 16-element tile row -------------
+//
+// I2/U2, I4/U4 (wrapping) and F4_E2M1, F6_E2M3, F6_E3M2 (decode, one binary32 operation,
+// encode). Slots are packed LSB first (src/tensor.cpp:136-164 gives the slot, the slot
+// times the leaf width the bit), so a tile row of 16 slots is 4, 8 or 12 whole bytes on a
+// 4-byte boundary: the thread that owns it reads it, replaces the logical columns and
+// writes it back, and the bits of padding columns survive. Inputs are fetched element by
+// element through the tile map (broadcast operands read their row 0 / column 0).
+enum class Narrow : int { Int = 0, F4E2M1 = 1, F6E2M3 = 2, F6E3M2 = 3 };
+
+template <int BITS, Narrow KIND, int OP>
+__device__ __forceinline__ uint32_t apply_narrow(uint32_t a, uint32_t b) {
+    if constexpr (KIND == Narrow::Int) {
+        const uint32_t r = OP == IOMB_ADD ? a + b : OP == IOMB_MUL ? a * b : a - b;
+        return r & ((1u << BITS) - 1u);
+    } else {
+        using Format = typename std::conditional<KIND == Narrow::F4E2M1, F4E2M1Format,
+                typename std::conditional<KIND == Narrow::F6E2M3, F6E2M3Format, F6E3M2Format>::type>::type;
+        return Format::encode(apply_f32<OP>(Format::decode(a), Format::decode(b)));
+    }
+}
+
+template <int BITS>
+__device__ __forceinline__ uint32_t fetch_narrow(const Operand& operand, const Leading& leading,
+                                                 uint64_t index, uint32_t row, uint32_t col) {
+    const uint32_t r = operand.bc_rows ? 0u : row;
+    const uint32_t c = operand.bc_cols ? 0u : col;
+    const uint64_t plane = operand_plane(operand, leading, index);
+    const uint64_t tile = (plane * operand.tile_rows + r / kTile) * operand.tile_cols + c / kTile;
+    const uint64_t bit = (tile * kTileSlots + (r % kTile) * kTile + c % kTile) * BITS;
+    const unsigned char* byte = operand.base + (bit >> 3);
+    const uint32_t shift = static_cast<uint32_t>(bit & 7u);
+    uint32_t value = static_cast<uint32_t>(byte[0]) >> shift;
+    if (shift + BITS > 8) value |= static_cast<uint32_t>(byte[1]) << (8 - shift);
+    return value & ((1u << BITS) - 1u);
+}
+
+template <int BITS, Narrow KIND, int OP>
+__global__ void __launch_bounds__(kTiledThreads)
+binary_narrow_kernel(const BinaryParams p, uint64_t items) {
+    constexpr int kWords = BITS / 2;                 // 32-bit words of one tile row
+    const uint64_t stride = static_cast<uint64_t>(gridDim.x) * kTiledThreads;
+    for (uint64_t item = static_cast<uint64_t>(blockIdx.x) * kTiledThreads + threadIdx.x; item < items;
+         item += stride) {
+        const uint32_t tc = static_cast<uint32_t>(item % p.tile_cols);
+        const uint64_t rest = item / p.tile_cols;
+        const uint32_t row = static_cast<uint32_t>(rest % p.rows);
+        const uint64_t index = rest / p.rows;
+        const uint32_t live = min(kTile, p.cols - tc * kTile);
+        const uint64_t out_tile = (operand_plane(p.out, p.leading, index) * p.out.tile_rows + row / kTile)
+                * p.out.tile_cols + tc;
+        uint32_t* words = reinterpret_cast<uint32_t*>(
+                p.out.base + (out_tile * kTileSlots + (row % kTile) * kTile) * BITS / 8);
+        unsigned __int128 packed = 0;
+#pragma unroll
+        for (int w = 0; w < kWords; ++w) packed |= static_cast<unsigned __int128>(words[w]) << (32 * w);
+        for (uint32_t c = 0; c < live; ++c) {
+            const uint32_t col = tc * kTile + c;
+            const uint32_t a = fetch_narrow<BITS>(p.lhs, p.leading, index, row, col);
+            const uint32_t b = fetch_narrow<BITS>(p.rhs, p.leading, index, row, col);
+            const unsigned __int128 mask = static_cast<unsigned __int128>((1u << BITS) - 1u) << (c * BITS);
+            packed = (packed & ~mask)
+                    | (static_cast<unsigned __int128>(apply_narrow<BITS, KIND, OP>(a, b)) << (c * BITS));
+        }
+#pragma unroll
+        for (int w = 0; w < kWords; ++w) words[w] = static_cast<uint32_t>(packed >> (32 * w));
+    }
+}
+
+template <int BITS, Narrow KIND>
+static int launch_narrow(int op, const BinaryParams& params, cudaStream_t stream) {
+    const uint64_t items = params.leading.planes * params.rows * params.tile_cols;
+    const unsigned grid = grid_for((items + kTiledThreads - 1) / kTiledThreads, 16);
+    switch (op) {
+        case IOMB_ADD: binary_narrow_kernel<BITS, KIND, IOMB_ADD><<<grid, kTiledThreads, 0, stream>>>(params, items); break;
+        case IOMB_MUL: binary_narrow_kernel<BITS, KIND, IOMB_MUL><<<grid, kTiledThreads, 0, stream>>>(params, items); break;
+        case IOMB_SUB: binary_narrow_kernel<BITS, KIND, IOMB_SUB><<<grid, kTiledThreads, 0, stream>>>(params, items); break;
+        default:
+            if constexpr (KIND != Narrow::Int) {
+                binary_narrow_kernel<BITS, KIND, IOMB_DIV><<<grid, kTiledThreads, 0, stream>>>(params, items);
+            } else {
+                return fail(IOMB_ERR_UNSUPPORTED, "binary: integer division is not admitted");
+            }
+    }
+    return check_launch("binary launch");
 }
 
 template <Wide W>
@@ -644,7 +740,13 @@ extern "C" int iomb_binary(int op, const iomb_view* lhs, const iomb_view* rhs,
     }
     Leaf leaf = Leaf::I32;
     int wide = -1;      // a Wide ordinal when the leaf takes the per-element kernel
+    int narrow = -1;    // 0..4 when the leaf is narrower than a byte
     switch (out->dtype) {
+        case IOMB_I2: case IOMB_U2: narrow = 0; break;
+        case IOMB_I4: case IOMB_U4: narrow = 1; break;
+        case IOMB_F4_E2M1: narrow = 2; break;
+        case IOMB_F6_E2M3: narrow = 3; break;
+        case IOMB_F6_E3M2: narrow = 4; break;
         case IOMB_I32: case IOMB_U32: leaf = Leaf::I32; break;
         case IOMB_F32: leaf = Leaf::F32; break;
         case IOMB_BF16: leaf = Leaf::BF16; break;
@@ -656,7 +758,7 @@ extern "C" int iomb_binary(int op, const iomb_view* lhs, const iomb_view* rhs,
         case IOMB_F8_E5M2: wide = static_cast<int>(Wide::F8E5M2); break;
         default:
             return fail(IOMB_ERR_UNSUPPORTED,
-                        "binary: leaf is not a byte-multiple integer, F8_E4M3FN, F8_E5M2, F16, BF16 or F32");
+                        "binary: leaf is BOOL, F8_E8M0 or F64");
     }
 
     BinaryParams params{};
@@ -675,6 +777,16 @@ extern "C" int iomb_binary(int op, const iomb_view* lhs, const iomb_view* rhs,
     params.runs = (params.tile_cols + params.run_tiles - 1) / params.run_tiles;
     params.items = params.leading.planes * params.tile_rows * params.runs;
 
+    if (narrow >= 0) {
+        cudaStream_t narrow_stream = static_cast<cudaStream_t>(stream);
+        switch (narrow) {
+            case 0: return launch_narrow<2, Narrow::Int>(op, params, narrow_stream);
+            case 1: return launch_narrow<4, Narrow::Int>(op, params, narrow_stream);
+            case 2: return launch_narrow<4, Narrow::F4E2M1>(op, params, narrow_stream);
+            case 3: return launch_narrow<6, Narrow::F6E2M3>(op, params, narrow_stream);
+            default: return launch_narrow<6, Narrow::F6E3M2>(op, params, narrow_stream);
+        }
+    }
     if (wide >= 0) {
         cudaStream_t element_stream = static_cast<cudaStream_t>(stream);
         switch (static_cast<Wide>(wide)) {

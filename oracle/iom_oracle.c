@@ -313,15 +313,15 @@ static uint32_t float_to_half_rne(float value) {
 
 uint64_t iomo_scalar_binary_ieee(int op, uint32_t dtype, uint64_t a, uint64_t b) {
     const unsigned width = integer_width(dtype);
-    if (width >= 8) {
-        /* Byte-multiple integers wrap; division does not exist. */
+    if (width) {
+        /* Integers of every width wrap; division does not exist. */
         if (op == 3) return 0;
         const uint64_t mask = width == 64 ? ~(uint64_t)0 : (((uint64_t)1 << width) - 1);
         return (op == 0 ? a + b : op == 1 ? a * b : a - b) & mask;
     }
     float x, y;
-    if (dtype == DT_F8_E4M3FN || dtype == DT_F8_E5M2) {
-        /* exact decode, one binary32 operation, one encode: 24 >= 2 * 4 + 2 */
+    if (format_of(dtype).bits && format_of(dtype).bits <= 8) {
+        /* F4, F6, F8: exact decode, one binary32 operation, one encode: 24 >= 2 * 4 + 2 */
         const format_t f8 = format_of(dtype);
         x = (float)codec_decode(a, f8);
         y = (float)codec_decode(b, f8);
@@ -354,10 +354,10 @@ uint64_t iomo_codec_mismatches(int op, uint32_t dtype, const void* a, uint64_t n
     const uint32_t bits = iomo_leaf_bits(dtype);
     uint64_t mismatches = 0;
     for (uint64_t i = 0; i < na; ++i) {
-        const uint64_t x = bits == 8 ? ((const uint8_t*)a)[i]
+        const uint64_t x = bits <= 8 ? ((const uint8_t*)a)[i]
                 : bits == 16 ? ((const uint16_t*)a)[i] : ((const uint32_t*)a)[i];
         for (uint64_t j = 0; j < nb; ++j) {
-            const uint64_t y = bits == 8 ? ((const uint8_t*)b)[j]
+            const uint64_t y = bits <= 8 ? ((const uint8_t*)b)[j]
                     : bits == 16 ? ((const uint16_t*)b)[j] : ((const uint32_t*)b)[j];
             if (iomo_scalar_binary(op, dtype, x, y) != iomo_scalar_binary_ieee(op, dtype, x, y)) {
                 ++mismatches;

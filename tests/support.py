@@ -436,6 +436,9 @@ def random_payload(rng: np.random.Generator, shape, data_type: DataType, kind: s
         else:
             values = rng.uniform(-1.0, 1.0, size=shape).astype(np.float32)
         return values if data_type == DataType.F32 else f32_to_bf16_bits(values)
+    if leaf_bits(data_type) < 8:
+        # narrower than a byte: the logical payload is packed LSB first; every bit pattern is a value
+        return rng.integers(0, 256, size=TensorSpec(shape, data_type).logical_nbytes(), dtype=np.uint8)
     info = np.iinfo(NUMPY_OF[data_type])
     return rng.integers(info.min, info.max, size=shape, dtype=NUMPY_OF[data_type], endpoint=True)
 

@@ -11,9 +11,12 @@ OPS = {"add": 0, "mul": 1, "sub": 2, "div": 3}
 DTYPES = [DataType.I32, DataType.U32, DataType.F32, DataType.BF16,
           # per-element kernel: the other byte-multiple integers and F16
           DataType.I8, DataType.U8, DataType.I16, DataType.U16, DataType.I64, DataType.U64, DataType.F16,
-          DataType.F8_E4M3FN, DataType.F8_E5M2]
+          DataType.F8_E4M3FN, DataType.F8_E5M2,
+          # one thread per tile row: the leaves narrower than a byte
+          DataType.I2, DataType.U2, DataType.I4, DataType.U4, DataType.F4_E2M1, DataType.F6_E2M3,
+          DataType.F6_E3M2]
 INTEGERS = (DataType.I8, DataType.U8, DataType.I16, DataType.U16, DataType.I32, DataType.U32,
-            DataType.I64, DataType.U64)
+            DataType.I64, DataType.U64, DataType.I2, DataType.U2, DataType.I4, DataType.U4)
 
 CASES = [
     ((2, 17, 33), (2, 17, 33), (2, 17, 33)),

@@ -131,6 +131,28 @@ def test_ieee_form_equals_codec_f8_every_pair(op, dtype):
     assert oracle().iomo_codec_mismatches(op, int(dtype), codes.ctypes.data, 256, codes.ctypes.data, 256) == 0
 
 
+@pytest.mark.parametrize("dtype,bits", [(DataType.F4_E2M1, 4), (DataType.F6_E2M3, 6), (DataType.F6_E3M2, 6),
+                                        (DataType.I2, 2), (DataType.U2, 2), (DataType.I4, 4), (DataType.U4, 4)])
+@pytest.mark.parametrize("op", [ADD, MUL, SUB, DIV])
+def test_ieee_form_equals_codec_every_pair_of_the_narrow_leaves(op, dtype, bits):
+    """Every pair of codes of the leaves narrower than a byte. The small floats have no NaN
+    and no infinity: such a result encodes to the largest value (a NaN to the positive one)."""
+    if op == DIV and dtype in (DataType.I2, DataType.U2, DataType.I4, DataType.U4):
+        pytest.skip("the reference admits no integer division")
+    codes = np.arange(1 << bits, dtype=np.uint8)
+    assert oracle().iomo_codec_mismatches(op, int(dtype), codes.ctypes.data, codes.size,
+                                          codes.ctypes.data, codes.size) == 0
+
+
+def test_narrow_float_known_codes():
+    assert binary(DIV, DataType.F4_E2M1, 0x0, 0x0) == 0x7        # 0 / 0: NaN -> +6, the largest value
+    assert binary(DIV, DataType.F4_E2M1, 0xA, 0x0) == 0xF        # -1 / 0: -inf -> -6
+    assert binary(ADD, DataType.F4_E2M1, 0x7, 0x7) == 0x7        # 6 + 6 saturates
+    assert binary(ADD, DataType.F4_E2M1, 0x1, 0x1) == 0x2        # 0.5 + 0.5 = 1
+    assert binary(MUL, DataType.F6_E3M2, 0x01, 0x01) == 0x00     # 2^-8 rounds to zero
+    assert binary(SUB, DataType.I4, 0x0, 0x1) == 0xF             # wraps
+
+
 def test_f8_known_codes():
     """The codec's reading of the two formats (src/shared/scalar_binary_codec.hpp:30-108):
     E4M3FN has no infinities and every all-ones exponent is NaN, so 240 (0x77) is the largest

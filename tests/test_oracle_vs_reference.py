@@ -61,12 +61,15 @@ BINARY_CASES = [
 @pytest.mark.parametrize("dtype", [DataType.I32, DataType.U32, DataType.F32, DataType.BF16,
                                    DataType.I8, DataType.U8, DataType.I16, DataType.U16,
                                    DataType.I64, DataType.U64, DataType.F16,
-                                   DataType.F8_E4M3FN, DataType.F8_E5M2])
+                                   DataType.F8_E4M3FN, DataType.F8_E5M2,
+                                   DataType.I2, DataType.U2, DataType.I4, DataType.U4,
+                                   DataType.F4_E2M1, DataType.F6_E2M3, DataType.F6_E3M2])
 @pytest.mark.parametrize("op", ["add", "mul", "sub", "div"])
 @pytest.mark.parametrize("shapes", BINARY_CASES)
 def test_binary_matches_reference(ref, dtype, op, shapes):
     if op == "div" and dtype not in (DataType.F32, DataType.BF16, DataType.F16, DataType.F8_E4M3FN,
-                                     DataType.F8_E5M2):
+                                     DataType.F8_E5M2, DataType.F4_E2M1, DataType.F6_E2M3,
+                                     DataType.F6_E3M2):
         pytest.skip("the reference admits no integer division")
     rng = np.random.default_rng(hash((int(dtype), op, shapes)) & 0xFFFF)
     lhs, rlhs = mirror(ref, shapes[0], dtype, rng)
