@@ -154,7 +154,8 @@ int iomb_add_rmsnorm(const iomb_view* x, const iomb_view* residual,
  * Bit-exact copy between two views of identical specification.
  * Replaces GpuQueue copy path + grid_stride_copy_kernel
  * (src/shared/standard_tiled_copy_metadata.inl:177-282; admission src/device_ops_copy.cpp:17-52).
- * Any byte-multiple leaf (8/16/32/64 bits). An identical window is a no-op.
+ * Any byte-multiple leaf (8/16/32/64 bits) and the leaves of 2, 4 and 6 bits (the bits of
+ * padding slots are preserved). An identical window is a no-op.
  */
 int iomb_copy(const iomb_view* source, const iomb_view* destination, void* stream);
 
@@ -289,7 +290,8 @@ int iomb_sumsq_static(const iomb_view* x, float* result, void* stream);
  * loops (src/shared/standard_tiled_copy.inl:286-441). `staging` is a device
  * buffer holding the view's logical row-major payload (exactly
  * logical_nbytes, LSB-first packed; include/iom/tensor.hpp:330-342).
- * Byte-multiple leaves.
+ * Byte-multiple leaves and the leaves of 2, 4 and 6 bits (BOOL, whose host form is one byte
+ * per value, is not implemented).
  */
 int iomb_scatter(const iomb_view* destination, const void* staging, void* stream);
 int iomb_gather(const iomb_view* source, void* staging, void* stream);

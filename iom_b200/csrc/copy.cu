@@ -284,6 +284,95 @@ static bool same_shape(const iomb_view& a, const iomb_view& b) {
     return true;
 }
 
+// ---- leaves of 2, 4 and 6 bits ------------------------------------------------------
+//
+// Slots are packed LSB first, so the 16 slots of a tile row are 4, 8 or 12 whole bytes. One
+// thread owns one tile row of the tiled side: it replaces the logical columns and keeps the
+// bits of the padding columns. The logical (host-layout) payload is one LSB-first bit
+// stream over planes, rows and columns (include/iom/tensor.hpp:330-342), so its rows do not
+// start on byte boundaries: when it is the destination, one thread owns one payload byte.
+struct NarrowParams {
+    Operand src;              // tiled source (copy, gather)
+    Operand dst;              // tiled destination (copy, scatter)
+    Leading leading;
+    unsigned char* logical;   // payload (scatter: source, gather: destination)
+    uint32_t rows, cols, tile_rows, tile_cols, bits;
+    uint64_t items;
+};
+
+__device__ __forceinline__ uint32_t narrow_bits_at(const unsigned char* base, uint64_t bit, uint32_t bits) {
+    const unsigned char* byte = base + (bit >> 3);
+    const uint32_t shift = static_cast<uint32_t>(bit & 7u);
+    uint32_t value = static_cast<uint32_t>(byte[0]) >> shift;
+    if (shift + bits > 8) value |= static_cast<uint32_t>(byte[1]) << (8 - shift);
+    return value & ((1u << bits) - 1u);
+}
+
+__device__ __forceinline__ uint64_t narrow_slot(const Operand& operand, const Leading& leading,
+                                                uint64_t index, uint32_t row, uint32_t col) {
+    const uint64_t tile = (operand_plane(operand, leading, index) * operand.tile_rows + row / kTile)
+            * operand.tile_cols + col / kTile;
+    return tile * kTileSlots + (row % kTile) * kTile + col % kTile;
+}
+
+// FROM_LOGICAL: scatter (payload -> tiled), else copy (tiled -> tiled).
+template <bool FROM_LOGICAL>
+__global__ void __launch_bounds__(kCopyThreads)
+narrow_rows_kernel(const NarrowParams p) {
+    const uint64_t stride = static_cast<uint64_t>(gridDim.x) * kCopyThreads;
+    const uint32_t row_bytes = 2 * p.bits;
+    for (uint64_t item = static_cast<uint64_t>(blockIdx.x) * kCopyThreads + threadIdx.x; item < p.items;
+         item += stride) {
+        const uint32_t tc = static_cast<uint32_t>(item % p.tile_cols);
+        const uint64_t rest = item / p.tile_cols;
+        const uint32_t row = static_cast<uint32_t>(rest % p.rows);
+        const uint64_t index = rest / p.rows;
+        const uint32_t live = min(kTile, p.cols - tc * kTile);
+        unsigned char* out = p.dst.base + narrow_slot(p.dst, p.leading, index, row, tc * kTile) * p.bits / 8;
+        unsigned __int128 packed = 0;
+        for (uint32_t b = 0; b < row_bytes; ++b) packed |= static_cast<unsigned __int128>(out[b]) << (8 * b);
+        for (uint32_t c = 0; c < live; ++c) {
+            const uint32_t col = tc * kTile + c;
+            uint32_t value;
+            if constexpr (FROM_LOGICAL) {
+                const uint64_t element = (index * p.rows + row) * p.cols + col;
+                value = narrow_bits_at(p.logical, element * p.bits, p.bits);
+            } else {
+                value = narrow_bits_at(p.src.base, narrow_slot(p.src, p.leading, index, row, col) * p.bits, p.bits);
+            }
+            const unsigned __int128 mask = static_cast<unsigned __int128>((1u << p.bits) - 1u) << (c * p.bits);
+            packed = (packed & ~mask) | (static_cast<unsigned __int128>(value) << (c * p.bits));
+        }
+        for (uint32_t b = 0; b < row_bytes; ++b) out[b] = static_cast<unsigned char>(packed >> (8 * b));
+    }
+}
+
+// gather: one thread per payload byte; the bits past the last element are zero.
+__global__ void __launch_bounds__(kCopyThreads)
+narrow_gather_kernel(const NarrowParams p) {
+    const uint64_t stride = static_cast<uint64_t>(gridDim.x) * kCopyThreads;
+    const uint64_t elements = p.leading.planes * p.rows * p.cols;
+    for (uint64_t byte = static_cast<uint64_t>(blockIdx.x) * kCopyThreads + threadIdx.x; byte < p.items;
+         byte += stride) {
+        const uint64_t first_bit = byte * 8;
+        uint32_t assembled = 0;
+        for (uint64_t element = first_bit / p.bits; element < elements && element * p.bits < first_bit + 8;
+             ++element) {
+            const uint32_t col = static_cast<uint32_t>(element % p.cols);
+            const uint64_t rest = element / p.cols;
+            const uint32_t row = static_cast<uint32_t>(rest % p.rows);
+            const uint64_t index = rest / p.rows;
+            const uint32_t value = narrow_bits_at(
+                    p.src.base, narrow_slot(p.src, p.leading, index, row, col) * p.bits, p.bits);
+            const int64_t offset = static_cast<int64_t>(element * p.bits) - static_cast<int64_t>(first_bit);
+            assembled |= offset >= 0 ? value << offset : value >> (-offset);
+        }
+        p.logical[byte] = static_cast<unsigned char>(assembled);
+    }
+}
+
+static bool narrow_leaf(uint32_t bits) { return bits == 2 || bits == 4 || bits == 6; }
+
 static int move_dispatch(const iomb_view* source, const iomb_view* destination, Move move,
                          void* stream) {
     ViewFacts fs{}, fd{};
@@ -332,6 +421,18 @@ static int move_dispatch(const iomb_view* source, const iomb_view* destination, 
                         reinterpret_cast<const uint4*>(src), reinterpret_cast<uint4*>(dst), groups);
             }
         }
+    } else if (fd.bytes == 0) {
+        NarrowParams n{};
+        n.src = p.src;
+        n.dst = p.dst;
+        n.leading = p.leading;
+        n.rows = p.rows;
+        n.cols = p.cols;
+        n.tile_rows = p.tile_rows;
+        n.tile_cols = p.tile_cols;
+        n.bits = fd.bits;
+        n.items = p.leading.planes * fd.rows * fd.tile_cols;
+        narrow_rows_kernel<false><<<grid_for((n.items + kCopyThreads - 1) / kCopyThreads, 8), kCopyThreads, 0, s>>>(n);
     } else {
         const unsigned grid = grid_one_shot((p.items + kCopyWarps - 1) / kCopyWarps);
         if (move == Move::Copy) {
@@ -350,9 +451,36 @@ static int layout_dispatch(const iomb_view* view, void* logical, bool to_tiled, 
     const int status = check_view(view, to_tiled ? "scatter destination" : "gather source", &f);
     if (status != IOMB_OK) return status;
     if (logical == nullptr) return fail(IOMB_ERR_INVALID_ARGUMENT, "staging buffer is null");
-    if (f.bytes == 0) return fail(IOMB_ERR_UNSUPPORTED, "host transfer: sub-byte leaves are not implemented");
+    if (f.bytes == 0 && !narrow_leaf(f.bits)) {
+        return fail(IOMB_ERR_UNSUPPORTED, "host transfer: BOOL is not implemented");
+    }
     if (f.rows > 0xFFFFFFFFull || f.cols > 0xFFFFFFFFull) {
         return fail(IOMB_ERR_UNSUPPORTED, "host transfer: matrix extent exceeds the kernel limit");
+    }
+    if (f.bytes == 0) {
+        NarrowParams n{};
+        uint64_t narrow_strides[1][kMaxLead] = {};
+        for (uint32_t axis = 0; axis < f.leading; ++axis) narrow_strides[0][axis] = view->plane_strides[axis];
+        collapse_leading(f.leading, view->dims, narrow_strides, 1, &n.leading);
+        n.src = make_operand(*view, f, narrow_strides[0], n.leading, false, false);
+        n.dst = n.src;
+        n.logical = static_cast<unsigned char*>(logical);
+        n.rows = static_cast<uint32_t>(f.rows);
+        n.cols = static_cast<uint32_t>(f.cols);
+        n.tile_rows = static_cast<uint32_t>(f.tile_rows);
+        n.tile_cols = static_cast<uint32_t>(f.tile_cols);
+        n.bits = f.bits;
+        cudaStream_t narrow_stream = static_cast<cudaStream_t>(stream);
+        if (to_tiled) {
+            n.items = n.leading.planes * f.rows * f.tile_cols;
+            narrow_rows_kernel<true><<<grid_for((n.items + kCopyThreads - 1) / kCopyThreads, 8), kCopyThreads, 0,
+                                       narrow_stream>>>(n);
+        } else {
+            n.items = (n.leading.planes * f.rows * f.cols * f.bits + 7) / 8;
+            narrow_gather_kernel<<<grid_for((n.items + kCopyThreads - 1) / kCopyThreads, 8), kCopyThreads, 0,
+                                   narrow_stream>>>(n);
+        }
+        return check_launch("host transfer launch");
     }
     LayoutParams p{};
     uint64_t strides[1][kMaxLead] = {};
@@ -388,8 +516,8 @@ extern "C" int iomb_copy(const iomb_view* source, const iomb_view* destination, 
             return fail(IOMB_ERR_INVALID_ARGUMENT, "copy views must have identical leaf type");
         }
         const uint32_t bits = iomb_dtype_bits(source->dtype);
-        if (bits != 0 && bits % 8 != 0) {
-            return fail(IOMB_ERR_UNSUPPORTED, "copy: sub-byte leaves are not implemented");
+        if (bits != 0 && bits % 8 != 0 && !narrow_leaf(bits)) {
+            return fail(IOMB_ERR_UNSUPPORTED, "copy: BOOL is not implemented");
         }
     }
     ViewFacts fs{}, fd{};

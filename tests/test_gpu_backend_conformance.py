@@ -58,7 +58,8 @@ def same(owners):
 
 @pytest.mark.parametrize("dtype", [DataType.I32, DataType.U32, DataType.F32, DataType.BF16,
                                    DataType.I8, DataType.U16, DataType.I64, DataType.F16,
-                                   DataType.F8_E4M3FN, DataType.F8_E5M2])
+                                   DataType.F8_E4M3FN, DataType.F8_E5M2, DataType.U4,
+                                   DataType.F6_E2M3])
 @pytest.mark.parametrize("op", [0, 1, 2, 3])
 @pytest.mark.parametrize("shapes", [
     ((2, 17, 33), (2, 17, 33), (2, 17, 33)), ((2, 1, 33), (1, 17, 1), (2, 17, 33)),
@@ -68,7 +69,7 @@ def test_binary(pair, dtype, op, shapes):
     rng = np.random.default_rng(5)
     lhs, rhs, out = (both(pair, s, dtype, rng) for s in shapes)
     integer_division = op == 3 and dtype not in (DataType.F32, DataType.BF16, DataType.F16,
-                                                 DataType.F8_E4M3FN, DataType.F8_E5M2)
+                                                 DataType.F8_E4M3FN, DataType.F8_E5M2, DataType.F6_E2M3)
     for i, ref in enumerate(pair):
         token = ref.lib.iomref_binary(ref.queue, op, lhs[i].view().handle, rhs[i].view().handle,
                                       out[i].view().handle)

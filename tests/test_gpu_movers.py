@@ -19,7 +19,8 @@ def seeded(shape, dtype, rng, poison=0xA5, kind="uniform"):
     return t
 
 
-@pytest.mark.parametrize("dtype", [DataType.BF16, DataType.F32, DataType.U8, DataType.I64, DataType.F16])
+@pytest.mark.parametrize("dtype", [DataType.BF16, DataType.F32, DataType.U8, DataType.I64, DataType.F16,
+                                   DataType.I2, DataType.U4, DataType.F4_E2M1, DataType.F6_E2M3])
 def test_copy_parity(gpu, dtype):
     device, queue = gpu
     rng = np.random.default_rng(11)
@@ -231,7 +232,8 @@ def test_sumsq(gpu, dtype, shape):
     assert abs(values[0] - truth) <= 1e-6 * truth     # FP32 vs FP64 evaluation
 
 
-@pytest.mark.parametrize("dtype", [DataType.BF16, DataType.F32, DataType.U8, DataType.I64])
+@pytest.mark.parametrize("dtype", [DataType.BF16, DataType.F32, DataType.U8, DataType.I64,
+                                   DataType.U2, DataType.I4, DataType.F6_E3M2])
 def test_host_transfers(gpu, dtype):
     device, queue = gpu
     rng = np.random.default_rng(23)
