@@ -297,6 +297,7 @@ struct NarrowParams {
     Leading leading;
     unsigned char* logical;   // payload (scatter: source, gather: destination)
     uint32_t rows, cols, tile_rows, tile_cols, bits;
+    uint32_t dst_row_offset;  // cache_append: source row r lands on destination row offset + r
     uint64_t items;
 };
 
@@ -328,7 +329,8 @@ narrow_rows_kernel(const NarrowParams p) {
         const uint32_t row = static_cast<uint32_t>(rest % p.rows);
         const uint64_t index = rest / p.rows;
         const uint32_t live = min(kTile, p.cols - tc * kTile);
-        unsigned char* out = p.dst.base + narrow_slot(p.dst, p.leading, index, row, tc * kTile) * p.bits / 8;
+        unsigned char* out = p.dst.base
+                + narrow_slot(p.dst, p.leading, index, row + p.dst_row_offset, tc * kTile) * p.bits / 8;
         unsigned __int128 packed = 0;
         for (uint32_t b = 0; b < row_bytes; ++b) packed |= static_cast<unsigned __int128>(out[b]) << (8 * b);
         for (uint32_t c = 0; c < live; ++c) {
@@ -372,6 +374,32 @@ narrow_gather_kernel(const NarrowParams p) {
 }
 
 static bool narrow_leaf(uint32_t bits) { return bits == 2 || bits == 4 || bits == 6; }
+
+// cache_append of a 2-, 4- or 6-bit leaf: the row copy of narrow_rows_kernel with the
+// destination rows shifted by `a` (both views validated by the caller).
+int narrow_append(const iomb_view& source, const ViewFacts& fs, const iomb_view& destination,
+                  const ViewFacts& fd, uint64_t a, cudaStream_t stream) {
+    if (!narrow_leaf(fs.bits)) return fail(IOMB_ERR_UNSUPPORTED, "cache_append: BOOL is not implemented");
+    NarrowParams n{};
+    uint64_t strides[2][kMaxLead] = {};
+    for (uint32_t axis = 0; axis < fs.leading; ++axis) {
+        strides[0][axis] = source.plane_strides[axis];
+        strides[1][axis] = destination.plane_strides[axis];
+    }
+    collapse_leading(fs.leading, source.dims, strides, 2, &n.leading);
+    n.src = make_operand(source, fs, strides[0], n.leading, false, false);
+    n.dst = make_operand(destination, fd, strides[1], n.leading, false, false);
+    n.rows = static_cast<uint32_t>(fs.rows);
+    n.cols = static_cast<uint32_t>(fs.cols);
+    n.tile_rows = static_cast<uint32_t>(fs.tile_rows);
+    n.tile_cols = static_cast<uint32_t>(fs.tile_cols);
+    n.bits = fs.bits;
+    n.dst_row_offset = static_cast<uint32_t>(a);
+    n.items = n.leading.planes * fs.rows * fs.tile_cols;
+    narrow_rows_kernel<false><<<grid_for((n.items + kCopyThreads - 1) / kCopyThreads, 8), kCopyThreads, 0,
+                                stream>>>(n);
+    return check_launch("cache_append launch");
+}
 
 static int move_dispatch(const iomb_view* source, const iomb_view* destination, Move move,
                          void* stream) {

@@ -249,11 +249,14 @@ static int append_dispatch(const iomb_view* source, const iomb_view* destination
     if (storage_overlaps(*source, fs, *destination, fd)) {
         return fail(IOMB_ERR_INVALID_ARGUMENT, "cache_append source and destination storage overlap");
     }
-    if (fs.bytes == 0) {
-        return fail(IOMB_ERR_UNSUPPORTED, "cache_append: sub-byte leaves are not implemented");
-    }
-    if (fs.rows > 0xFFFFFFFFull || fs.cols > 0xFFFFFFFFull) {
+    if (fs.rows > 0xFFFFFFFFull || fs.cols > 0xFFFFFFFFull || fd.rows > 0xFFFFFFFFull) {
         return fail(IOMB_ERR_UNSUPPORTED, "cache_append: matrix extent exceeds the kernel limit");
+    }
+    if (fs.bytes == 0) {
+        if (positions != nullptr) {
+            return fail(IOMB_ERR_UNSUPPORTED, "cache_append_batched: sub-byte leaves are not implemented");
+        }
+        return narrow_append(*source, fs, *destination, fd, a, static_cast<cudaStream_t>(stream));
     }
     AppendParams p{};
     uint64_t strides[2][kMaxLead] = {};

@@ -56,4 +56,8 @@ unsigned grid_for(uint64_t work_items, unsigned ctas_per_sm);
 // Grid with one CTA per work item (kernels still loop, so the cap is harmless).
 unsigned grid_one_shot(uint64_t work_items);
 
+// cache_append for the leaves of 2, 4 and 6 bits (defined beside the other narrow-leaf movers).
+int narrow_append(const iomb_view& source, const ViewFacts& fs, const iomb_view& destination,
+                  const ViewFacts& fd, uint64_t a, cudaStream_t stream);
+
 }  // namespace iomb

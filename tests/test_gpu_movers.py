@@ -147,7 +147,8 @@ def test_embedding_decode_shape(gpu):
 
 
 @pytest.mark.parametrize("a", [0, 5, 29])
-@pytest.mark.parametrize("dtype", [DataType.BF16, DataType.F32, DataType.U8])
+@pytest.mark.parametrize("dtype", [DataType.BF16, DataType.F32, DataType.U8, DataType.U4, DataType.F6_E3M2,
+                                   DataType.I2])
 def test_cache_append_parity(gpu, a, dtype):
     device, queue = gpu
     rng = np.random.default_rng(17)

@@ -170,7 +170,8 @@ def test_rmsnorm_special_rows(ref, dtype, specials):
         assert np.array_equal(out.storage, rout.storage)
 
 
-@pytest.mark.parametrize("dtype", [DataType.BF16, DataType.F32, DataType.U8, DataType.I64])
+@pytest.mark.parametrize("dtype", [DataType.BF16, DataType.F32, DataType.U8, DataType.I64,
+                                   DataType.I2, DataType.U4, DataType.F4_E2M1, DataType.F6_E2M3])
 def test_copy_matches_reference(ref, dtype):
     rng = np.random.default_rng(11)
     src, rsrc = mirror(ref, (3, 4, 17, 33), dtype, rng)
@@ -292,11 +293,12 @@ def test_embedding_matches_reference(ref, index_dtype):
     assert np.array_equal(out.storage, before) and np.array_equal(rout.storage, before)
 
 
+@pytest.mark.parametrize("dtype", [DataType.BF16, DataType.U4, DataType.F6_E3M2, DataType.I2])
 @pytest.mark.parametrize("a", [0, 5, 29])
-def test_cache_append_matches_reference(ref, a):
+def test_cache_append_matches_reference(ref, a, dtype):
     rng = np.random.default_rng(17)
-    src, rsrc = mirror(ref, (2, 3, 3, 40), DataType.BF16, rng)
-    dst, rdst = mirror(ref, (2, 3, 32, 40), DataType.BF16, rng)
+    src, rsrc = mirror(ref, (2, 3, 3, 40), dtype, rng)
+    dst, rdst = mirror(ref, (2, 3, 32, 40), dtype, rng)
     token = ref.lib.iomref_cache_append(ref.queue, rsrc.view().handle, rdst.view().handle, a)
     assert ref.run(token) == 0, ref.error()
     assert oracle().iomo_cache_append(abi(src.view()), abi(dst.view()), a) == 0
