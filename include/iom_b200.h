@@ -237,7 +237,8 @@ int iomb_embedding(const iomb_view* table, const iomb_view* indices,
  * destination[..., h, a + r, d] = source[..., h, r, d] (raw bits); only the
  * appended rows are touched.
  * Replaces cache_append_kernel (src/cuda/copy.cu:111-338); admission
- * src/device_ops_cache_append.cpp:157-269 (a <= C, R <= C - a).
+ * src/device_ops_cache_append.cpp:157-269 (a <= C, R <= C - a). Byte-multiple leaves and the
+ * leaves of 2, 4 and 6 bits.
  */
 int iomb_cache_append(const iomb_view* source, const iomb_view* destination,
                       uint64_t a, void* stream);

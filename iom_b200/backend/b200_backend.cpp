@@ -645,7 +645,7 @@ protected:
 
     [[nodiscard]] WorkspaceRequirements cache_append_workspace_requirements(
             const CacheAppendRequest& request) override {
-        if (detail::leaf_bits(request.source.data_type) % 8 != 0) {
+        if (detail::leaf_bits(request.source.data_type) == 1) {   // BOOL: one bit per slot
             throw detail::UnsupportedOperation();
         }
         return {0, 1};

@@ -171,6 +171,21 @@ def test_copy_embedding_cache_append(pair):
             assert ref.lib.iomref_cache_append(ref.queue, s[i].view().handle, d[i].view().handle, 30) == -1
         same(d)
 
+    # the leaves of 2, 4 and 6 bits: copy through transformed views and cache_append
+    for dtype in (DataType.U4, DataType.F6_E2M3, DataType.I2):
+        src = both(pair, (3, 4, 17, 33), dtype, rng)
+        dst = both(pair, (4, 3, 17, 33), dtype, rng)
+        sv = views(src, [("slice", (1, 0, 2, 2))])
+        dv = views(dst, [("permute", ([1, 0],)), ("slice", (1, 1, 2, 2))])
+        s = both(pair, (2, 3, 3, 40), dtype, rng)
+        d = both(pair, (2, 3, 32, 40), dtype, rng)
+        for i, ref in enumerate(pair):
+            assert ref.run(ref.lib.iomref_copy(ref.queue, sv[i].handle, dv[i].handle)) == 0
+            assert ref.run(ref.lib.iomref_cache_append(ref.queue, s[i].view().handle,
+                                                       d[i].view().handle, 7)) == 0
+        same(dst)
+        same(d)
+
 
 def test_silu_and_fused_gate(pair):
     """SiLU behind the facade: BF16 equals the reference CPU backend on every code;
