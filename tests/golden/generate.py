@@ -82,6 +82,43 @@ def binary_cases(ref, out):
             out[key + "_out"] = res.storage.copy()
 
 
+SMALL_FLOATS = ((DataType.F8_E4M3FN, 8), (DataType.F8_E5M2, 8), (DataType.F6_E2M3, 6),
+                (DataType.F6_E3M2, 6), (DataType.F4_E2M1, 4))
+
+
+def pack_codes(codes, bits):
+    """LSB-first bit stream of `codes` (the logical host form of a leaf narrower than a byte)."""
+    flat = np.asarray(codes, dtype=np.uint64).reshape(-1)
+    stream = np.zeros((flat.size * bits + 7) // 8, dtype=np.uint8)
+    for k in range(bits):
+        position = np.arange(flat.size, dtype=np.uint64) * bits + k
+        bit = ((flat >> np.uint64(k)) & np.uint64(1)).astype(np.uint8)
+        np.bitwise_or.at(stream, (position >> np.uint64(3)).astype(np.int64), bit << (position & np.uint64(7)).astype(np.uint8))
+    return stream
+
+
+def every_pair_cases(ref, out):
+    """All pairs of codes of the 8-, 6- and 4-bit floating leaves, four operations each: an
+    [N, N] tensor with N = 2^bits, lhs[i, j] = i, rhs[i, j] = j."""
+    for dtype, bits in SMALL_FLOATS:
+        n = 1 << bits
+        codes = np.arange(n, dtype=np.uint8)
+        first, second = np.repeat(codes, n), np.tile(codes, n)
+        if bits < 8:
+            first, second = pack_codes(first, bits), pack_codes(second, bits)
+        zeros = np.zeros_like(first)
+        for op, code in (("add", 0), ("mul", 1), ("sub", 2), ("div", 3)):
+            lhs, rhs, res = owner(ref, (n, n), dtype, first), owner(ref, (n, n), dtype, second), \
+                owner(ref, (n, n), dtype, zeros)
+            token = ref.lib.iomref_binary(ref.queue, code, lhs.view().handle, rhs.view().handle,
+                                          res.view().handle)
+            assert ref.run(token) == 0, ref.error()
+            key = f"pairs_{op}_{dtype.name}"
+            out[key + "_lhs"] = lhs.storage.copy()
+            out[key + "_rhs"] = rhs.storage.copy()
+            out[key + "_out"] = res.storage.copy()
+
+
 def rmsnorm_cases(ref, out, tag):
     for dtype in (DataType.BF16, DataType.F32):
         for i, shape in enumerate([(1, 1), (15, 17), (17, 33), (2, 3, 16, 31), (4, 256), (18, 1040)]):
@@ -191,6 +228,7 @@ def main():
     mover_cases(portable, fixtures)
     silu_cases(portable, fixtures, "portable")
     rope_cases(portable, fixtures, "portable")
+    every_pair_cases(portable, fixtures)
     portable.close()
     avx = Reference("avx512")
     assert avx.lib.iomref_avx512_bf16_active() == 1, "this host cannot run the AVX-512 BF16 build"

@@ -73,6 +73,25 @@ def test_special_values_golden(dtype, op):
         assert np.array_equal(out.storage, GOLDEN[key + "_out"])
 
 
+SMALL_FLOATS = [(DataType.F8_E4M3FN, 256), (DataType.F8_E5M2, 256), (DataType.F6_E2M3, 64),
+                (DataType.F6_E3M2, 64), (DataType.F4_E2M1, 16)]
+
+
+@pytest.mark.parametrize("dtype,n", SMALL_FLOATS)
+@pytest.mark.parametrize("op", ["add", "mul", "sub", "div"])
+def test_every_pair_of_the_small_floats_golden(dtype, n, op):
+    """Every pair of codes, recorded from the reference CPU backend: the oracle's codec and
+    its binary32 form both reproduce it."""
+    key = f"pairs_{op}_{dtype.name}"
+    lhs = host_from(GOLDEN[key + "_lhs"], (n, n), dtype)
+    rhs = host_from(GOLDEN[key + "_rhs"], (n, n), dtype)
+    for ieee in (0, 1):
+        out = HostTensor((n, n), dtype)
+        assert oracle().iomo_binary(OP_CODES[op], abi(lhs.view()), abi(rhs.view()),
+                                    abi(out.view()), ieee) == 0
+        assert np.array_equal(out.storage, GOLDEN[key + "_out"])
+
+
 @pytest.mark.parametrize("build,order", [("portable", 1), ("avx512", 0)])
 @pytest.mark.parametrize("dtype", [DataType.BF16, DataType.F32])
 @pytest.mark.parametrize("case", range(6))

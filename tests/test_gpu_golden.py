@@ -7,7 +7,7 @@ from iom_b200.device import RMS_LANES16, RMS_SEQUENTIAL
 from iom_b200.tensor import DataType
 from gpu_support import download, gpu, like, run, upload  # noqa: F401
 from support import HostTensor
-from test_golden import GOLDEN, host_from, split_shapes, view_from
+from test_golden import GOLDEN, SMALL_FLOATS, host_from, split_shapes, view_from
 
 pytestmark = pytest.mark.gpu
 
@@ -26,6 +26,21 @@ def test_binary_golden_gpu(gpu, dtype, op):
         do = upload(device, host_from(GOLDEN[key + "_out_before"], os_, dtype))
         run(queue, getattr(queue, op)(dl.view(), dr.view(), do.view()))
         assert np.array_equal(download(do), GOLDEN[key + "_out"]), key
+
+
+@pytest.mark.parametrize("dtype,n", SMALL_FLOATS)
+def test_every_pair_of_the_small_floats_golden_gpu(gpu, dtype, n):
+    """Every pair of codes of the 8-, 6- and 4-bit floating leaves against the reference's record."""
+    device, queue = gpu
+    for op in ("add", "mul", "sub", "div"):
+        key = f"pairs_{op}_{dtype.name}"
+        dl = upload(device, host_from(GOLDEN[key + "_lhs"], (n, n), dtype))
+        dr = upload(device, host_from(GOLDEN[key + "_rhs"], (n, n), dtype))
+        do = upload(device, HostTensor((n, n), dtype))
+        run(queue, getattr(queue, op)(dl.view(), dr.view(), do.view()))
+        assert np.array_equal(download(do), GOLDEN[key + "_out"]), key
+        for t in (dl, dr, do):
+            t.close()
 
 
 @pytest.mark.parametrize("build,order", [("portable", RMS_SEQUENTIAL), ("avx512", RMS_LANES16)])
