@@ -291,8 +291,7 @@ int iomb_sumsq_static(const iomb_view* x, float* result, void* stream);
  * loops (src/shared/standard_tiled_copy.inl:286-441). `staging` is a device
  * buffer holding the view's logical row-major payload (exactly
  * logical_nbytes, LSB-first packed; include/iom/tensor.hpp:330-342).
- * Byte-multiple leaves and the leaves of 2, 4 and 6 bits (BOOL, whose host form is one byte
- * per value, is not implemented).
+ * Byte-multiple leaves (BOOL is one byte per value) and the leaves of 2, 4 and 6 bits.
  */
 int iomb_scatter(const iomb_view* destination, const void* staging, void* stream);
 int iomb_gather(const iomb_view* source, void* staging, void* stream);

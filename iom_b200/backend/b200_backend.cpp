@@ -645,9 +645,7 @@ protected:
 
     [[nodiscard]] WorkspaceRequirements cache_append_workspace_requirements(
             const CacheAppendRequest& request) override {
-        if (detail::leaf_bits(request.source.data_type) == 1) {   // BOOL: one bit per slot
-            throw detail::UnsupportedOperation();
-        }
+        (void)request;   // every leaf width (8..64 bits, and 2, 4, 6 bits) has a kernel
         return {0, 1};
     }
 

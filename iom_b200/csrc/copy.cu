@@ -379,7 +379,7 @@ static bool narrow_leaf(uint32_t bits) { return bits == 2 || bits == 4 || bits =
 // destination rows shifted by `a` (both views validated by the caller).
 int narrow_append(const iomb_view& source, const ViewFacts& fs, const iomb_view& destination,
                   const ViewFacts& fd, uint64_t a, cudaStream_t stream) {
-    if (!narrow_leaf(fs.bits)) return fail(IOMB_ERR_UNSUPPORTED, "cache_append: BOOL is not implemented");
+    if (!narrow_leaf(fs.bits)) return fail(IOMB_ERR_UNSUPPORTED, "cache_append: leaf width is not 2, 4 or 6 bits");
     NarrowParams n{};
     uint64_t strides[2][kMaxLead] = {};
     for (uint32_t axis = 0; axis < fs.leading; ++axis) {
@@ -480,7 +480,7 @@ static int layout_dispatch(const iomb_view* view, void* logical, bool to_tiled, 
     if (status != IOMB_OK) return status;
     if (logical == nullptr) return fail(IOMB_ERR_INVALID_ARGUMENT, "staging buffer is null");
     if (f.bytes == 0 && !narrow_leaf(f.bits)) {
-        return fail(IOMB_ERR_UNSUPPORTED, "host transfer: BOOL is not implemented");
+        return fail(IOMB_ERR_UNSUPPORTED, "host transfer: leaf width is neither a byte multiple nor 2, 4 or 6 bits");
     }
     if (f.rows > 0xFFFFFFFFull || f.cols > 0xFFFFFFFFull) {
         return fail(IOMB_ERR_UNSUPPORTED, "host transfer: matrix extent exceeds the kernel limit");
@@ -545,7 +545,7 @@ extern "C" int iomb_copy(const iomb_view* source, const iomb_view* destination, 
         }
         const uint32_t bits = iomb_dtype_bits(source->dtype);
         if (bits != 0 && bits % 8 != 0 && !narrow_leaf(bits)) {
-            return fail(IOMB_ERR_UNSUPPORTED, "copy: BOOL is not implemented");
+            return fail(IOMB_ERR_UNSUPPORTED, "copy: leaf width is neither a byte multiple nor 2, 4 or 6 bits");
         }
     }
     ViewFacts fs{}, fd{};
