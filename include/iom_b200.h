@@ -228,7 +228,7 @@ int iomb_rope(const iomb_view* x, const iomb_view* out, uint64_t a, const float*
  * device word inside the caller's {32,32} workspace: the call resets it to 0 in
  * stream order and the kernel sets it to 1 when any index is negative or >= V;
  * such rows are not written and no table address is formed for them.
- * Payload: byte-multiple leaves. Index: I8..U64.
+ * Payload: byte-multiple leaves and the leaves of 2, 4 and 6 bits. Index: I8..U64.
  */
 int iomb_embedding(const iomb_view* table, const iomb_view* indices,
                    const iomb_view* out, uint32_t* status, void* stream);

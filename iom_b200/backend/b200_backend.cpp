@@ -609,8 +609,7 @@ protected:
 
     [[nodiscard]] WorkspaceRequirements embedding_workspace_requirements_impl(
             const TensorView& table, const TensorView& indices, const TensorView&) override {
-        if (detail::leaf_bits(table.spec().data_type) % 8 != 0
-                || detail::leaf_bits(indices.spec().data_type) % 8 != 0) {
+        if (detail::leaf_bits(indices.spec().data_type) % 8 != 0) {
             throw detail::UnsupportedOperation();
         }
         // First u32 of the range is the status word (0 ok / 1 invalid id),

@@ -297,6 +297,50 @@ static int append_dispatch(const iomb_view* source, const iomb_view* destination
     return check_launch("cache_append launch");
 }
 
+// Payload leaves of 2, 4 and 6 bits: one thread per (plane, output row, tile column) moves
+// the 4, 8 or 12 bytes of one tile row; in the last tile column only the logical columns are
+// replaced, so the bits of padding slots survive. Ids are read and checked as above.
+__global__ void __launch_bounds__(kRowThreads)
+embedding_narrow_kernel(const EmbeddingParams p, uint32_t bits, uint32_t cols, uint64_t items) {
+    const uint64_t stride = static_cast<uint64_t>(gridDim.x) * kRowThreads;
+    const uint32_t row_bytes = 2 * bits;
+    const uint32_t tile_cols = p.out.tile_cols;
+    for (uint64_t item = static_cast<uint64_t>(blockIdx.x) * kRowThreads + threadIdx.x; item < items;
+         item += stride) {
+        const uint32_t tc = static_cast<uint32_t>(item % tile_cols);
+        const uint64_t rest = item / tile_cols;
+        const uint32_t r = static_cast<uint32_t>(rest % p.run);
+        const uint64_t index = rest / p.run;
+        const unsigned char* id_address = p.indices.base
+                + ((operand_plane(p.indices, p.leading, index) * p.indices.tile_rows) * p.indices.tile_cols
+                   + r / kTile) * static_cast<uint64_t>(kTileSlots) * p.index_bytes
+                + (r % kTile) * p.index_bytes;
+        uint64_t id = 0;
+        switch (p.index_bytes) {
+            case 1: id = *id_address; break;
+            case 2: id = *reinterpret_cast<const uint16_t*>(id_address); break;
+            case 4: id = *reinterpret_cast<const uint32_t*>(id_address); break;
+            default: id = *reinterpret_cast<const uint64_t*>(id_address); break;
+        }
+        const bool negative = p.index_signed && ((id >> (p.index_bytes * 8 - 1)) & 1u);
+        if (negative || id >= p.vocabulary) {
+            if (tc == 0) atomicOr(p.status, 1u);
+            continue;
+        }
+        const uint64_t src_tile = (p.table.plane0 * p.table.tile_rows + id / kTile) * p.table.tile_cols + tc;
+        const uint64_t dst_tile = (operand_plane(p.out, p.leading, index) * p.out.tile_rows + r / kTile)
+                * p.out.tile_cols + tc;
+        const unsigned char* src = p.table.base + (src_tile * kTileSlots + (id % kTile) * kTile) * bits / 8;
+        unsigned char* dst = p.out.base + (dst_tile * kTileSlots + (r % kTile) * kTile) * bits / 8;
+        const uint32_t live_bits = min(kTile, cols - tc * kTile) * bits;
+        for (uint32_t b = 0; b < row_bytes; ++b) {
+            if (8 * b >= live_bits) break;
+            const uint32_t keep = live_bits - 8 * b >= 8 ? 0u : 0xffu << (live_bits - 8 * b);   // padding bits
+            dst[b] = static_cast<unsigned char>((src[b] & ~keep) | (dst[b] & keep));
+        }
+    }
+}
+
 }  // namespace iomb
 
 extern "C" int iomb_embedding(const iomb_view* table, const iomb_view* indices,
@@ -341,12 +385,10 @@ extern "C" int iomb_embedding(const iomb_view* table, const iomb_view* indices,
         default:
             return fail(IOMB_ERR_UNSUPPORTED, "embedding: index leaf is not integral");
     }
-    if (ft.bytes == 0) {
-        return fail(IOMB_ERR_UNSUPPORTED, "embedding: sub-byte payload leaves are not implemented");
-    }
     if (fo.rows > 0xFFFFFFFFull || fo.cols > 0xFFFFFFFFull) {
         return fail(IOMB_ERR_UNSUPPORTED, "embedding: matrix extent exceeds the kernel limit");
     }
+    const bool narrow_payload = ft.bytes == 0;
     EmbeddingParams p{};
     uint64_t strides[2][kMaxLead] = {};
     for (uint32_t axis = 0; axis < fo.leading; ++axis) {
@@ -359,7 +401,7 @@ extern "C" int iomb_embedding(const iomb_view* table, const iomb_view* indices,
     Leading none{};
     none.planes = 1;
     p.table = make_operand(*table, ft, strides[0], none, false, false);
-    p.row = row_geometry(ft);
+    if (!narrow_payload) p.row = row_geometry(ft);
     p.run = static_cast<uint32_t>(fo.rows);
     p.index_bytes = fi.bytes;
     p.index_signed = index_signed ? 1u : 0u;
@@ -372,6 +414,12 @@ extern "C" int iomb_embedding(const iomb_view* table, const iomb_view* indices,
     // (src/shared/gpu_queue_operations.inl:899-914).
     if (cudaMemsetAsync(status, 0, sizeof(uint32_t), s) != cudaSuccess) {
         return check_launch("embedding status reset");
+    }
+    if (narrow_payload) {
+        const uint64_t items = p.leading.planes * fo.rows * fo.tile_cols;
+        embedding_narrow_kernel<<<grid_for((items + kRowThreads - 1) / kRowThreads, 8), kRowThreads, 0, s>>>(
+                p, ft.bits, static_cast<uint32_t>(fo.cols), items);
+        return check_launch("embedding launch");
     }
     const unsigned grid = grid_one_shot((p.items + kRowWarps - 1) / kRowWarps);
     embedding_kernel<<<grid, kRowThreads, 0, s>>>(p);

@@ -92,7 +92,8 @@ def test_cast_all_bf16_codes(gpu):
 
 
 @pytest.mark.parametrize("index_dtype", [DataType.U32, DataType.I64, DataType.U8, DataType.I16])
-@pytest.mark.parametrize("payload", [DataType.BF16, DataType.F32, DataType.U8])
+@pytest.mark.parametrize("payload", [DataType.BF16, DataType.F32, DataType.U8, DataType.U4, DataType.F6_E2M3,
+                                     DataType.I2])
 def test_embedding_parity(gpu, index_dtype, payload):
     device, queue = gpu
     rng = np.random.default_rng(13)

@@ -261,16 +261,17 @@ def test_rope_views_and_rejections_match_reference(ref):
     assert oracle().iomo_rope(abi(odd.view()), abi(odd2.view()), 0, 10000.0) == 1
 
 
+@pytest.mark.parametrize("payload", [DataType.BF16, DataType.U4, DataType.F6_E2M3, DataType.I2])
 @pytest.mark.parametrize("index_dtype", [DataType.U32, DataType.I64, DataType.U8, DataType.I16])
-def test_embedding_matches_reference(ref, index_dtype):
+def test_embedding_matches_reference(ref, index_dtype, payload):
     rng = np.random.default_rng(13)
     vocab, feat, run = 50, 37, 19
-    table, rtable = mirror(ref, (vocab, feat), DataType.BF16, rng)
+    table, rtable = mirror(ref, (vocab, feat), payload, rng)
     ids = rng.integers(0, vocab, size=(2, 1, run)).astype(
         {DataType.U32: np.uint32, DataType.I64: np.int64, DataType.U8: np.uint8,
          DataType.I16: np.int16}[index_dtype])
     idx, ridx = mirror(ref, (2, 1, run), index_dtype, rng, payload=ids)
-    out, rout = mirror(ref, (2, run, feat), DataType.BF16, rng)
+    out, rout = mirror(ref, (2, run, feat), payload, rng)
     token = ref.lib.iomref_embedding(ref.queue, rtable.view().handle, ridx.view().handle,
                                      rout.view().handle)
     assert ref.run(token) == 0, ref.error()
