@@ -185,6 +185,14 @@ def test_copy_embedding_cache_append(pair):
                                                        d[i].view().handle, 7)) == 0
         same(dst)
         same(d)
+        table = both(pair, (50, 37), dtype, rng)
+        idx = both(pair, (2, 1, 19), DataType.U32, rng, payload=ids)
+        out = both(pair, (2, 19, 37), dtype, rng)
+        for i, ref in enumerate(pair):
+            token = ref.lib.iomref_embedding(ref.queue, table[i].view().handle, idx[i].view().handle,
+                                             out[i].view().handle)
+            assert ref.run(token) == 0, ref.error()
+        same(out)
 
 
 def test_silu_and_fused_gate(pair):
