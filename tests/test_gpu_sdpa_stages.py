@@ -187,6 +187,39 @@ def test_fused_stage_equals_the_two_launches(gpu, geometry, keep):
         ds.close()
 
 
+def test_stages_replay_from_a_captured_sequence(gpu):
+    """The stage entry points neither allocate nor synchronise: a captured sequence of the fused
+    stage and the output canonicalisation replays on new scores with the eager results."""
+    from iom_b200.device import OID_CAPTURED
+    device, queue = gpu
+    geometry = (2, 4, 2, 37, 64, 16, 5, 45)
+    first, second = random_case(41, *geometry), random_case(42, *geometry)
+    eager, graph = DeviceStages(device, second), DeviceStages(device, first)
+    negative_zeros = HostTensor((2, 37, 64), DataType.BF16).poison(0x80)
+    negative_zeros.view().copy_from_host(np.full((2, 37, 64), 0x8000, dtype=np.uint16))
+    out = upload(device, negative_zeros)
+    run(queue, queue.sdpa_scale_mask_softmax(eager.stages))
+    with queue.capture() as step:
+        assert queue.sdpa_scale_mask_softmax(graph.stages) == OID_CAPTURED
+        assert queue.sdpa_canonicalize_output(out.view()) == OID_CAPTURED
+    run(queue, step.replay())
+    want_first = DeviceStages(device, first)
+    run(queue, queue.sdpa_scale_mask_softmax(want_first.stages))
+    assert np.array_equal(graph.probability(), want_first.probability())
+    # new scores in the same buffers, same recorded launches
+    graph.workspace.tensor()[:second.scores.nbytes].copy_(
+        torch.from_numpy(second.scores.view(np.uint8).reshape(-1).copy()))
+    torch.cuda.synchronize()
+    run(queue, step.replay())
+    assert np.array_equal(graph.probability(), eager.probability())
+    cleaned = HostTensor((2, 37, 64), DataType.BF16).poison(0x80)
+    cleaned.view().copy_from_host(np.zeros((2, 37, 64), dtype=np.uint16))
+    assert np.array_equal(download(out), cleaned.storage)      # -0 became +0, padding untouched
+    for ds in (eager, graph, want_first):
+        ds.close()
+    out.close()
+
+
 def special_codes(rng, shape):
     codes = rng.integers(0, 65536, size=shape, dtype=np.uint16)
     flat = codes.reshape(-1)
