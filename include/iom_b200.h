@@ -117,15 +117,34 @@ uint64_t iomb_plane_slot(uint64_t rows, uint64_t columns, uint64_t plane,
  * admission rules of DeviceOps::validate_binary (src/device_ops_binary.cpp:102-181).
  * Leaves: I32/U32, F32, BF16 on the vector kernels; I8/U8, I16/U16, I64/U64, F16, F8_E4M3FN and
  * F8_E5M2 on a per-element kernel; I2/U2, I4/U4, F4_E2M1, F6_E2M3, F6_E3M2 on a kernel that
- * owns whole tile rows (padding bits survive). Every numeric leaf of the reference except F64.
+ * owns whole tile rows (padding bits survive); F64 on the per-element kernel. Every numeric
+ * leaf of the reference.
  * Integers wrap and have no division (src/device_ops_binary.cpp:46-57).
  * Arithmetic equals the scalar codec (src/shared/scalar_binary_codec.hpp:120-178):
  * IEEE binary32 op (division correctly rounded), one RNE encode, every NaN result is
- * the positive quiet NaN (0x7FC00000 / 0x7FC0).
+ * the positive quiet NaN (0x7FC00000 / 0x7FC0). BF16 ADD/SUB/MUL may run as packed
+ * BF16 instructions (exact result, one rounding): the same codes.
+ * F64: one IEEE binary64 operation, the carrier of the reference's GPU kernels
+ * (src/shared/standard_tiled_add.inl:110-116); the reference CPU backend's x87 carrier
+ * rounds twice and can differ from it by one code.
  * Exact in-place alias (out is the same view as an input) is allowed.
  */
 int iomb_binary(int op, const iomb_view* lhs, const iomb_view* rhs,
                 const iomb_view* out, void* stream);
+
+/* 1 when iomb_binary serves the leaf (every numeric leaf: all but BOOL and F8_E8M0), else 0.
+ * Lets a backend's binary_impl refuse a leaf before a sequence is taken
+ * (src/device_ops_binary.cpp:170-177). */
+int iomb_binary_supported(uint32_t dtype);
+
+/*
+ * One-time set-up of the library on the current device, on `stream`: raises the
+ * shared-memory limits of the kernels that need it and builds the BF16 SiLU table, so that
+ * no later call does either. Optional (every entry point still does its own set-up on first
+ * use); a backend calls it when it constructs its device, before any stream capture. No
+ * counterpart in the reference (its kernels need no set-up).
+ */
+int iomb_prepare_device(void* stream);
 
 /*
  * out[..., r, :] = x[..., r, :] / sqrt(mean(x[..., r, :]^2) + eps) * scale[0, :]
@@ -228,7 +247,8 @@ int iomb_rope(const iomb_view* x, const iomb_view* out, uint64_t a, const float*
  * device word inside the caller's {32,32} workspace: the call resets it to 0 in
  * stream order and the kernel sets it to 1 when any index is negative or >= V;
  * such rows are not written and no table address is formed for them.
- * Payload: byte-multiple leaves and the leaves of 2, 4 and 6 bits. Index: I8..U64.
+ * Payload: byte-multiple leaves and the leaves of 2, 4 and 6 bits. Index: every integer leaf
+ * (I2/U2, I4/U4, I8..U64), compared at full width (src/device_ops_embedding.cpp:27-46).
  */
 int iomb_embedding(const iomb_view* table, const iomb_view* indices,
                    const iomb_view* out, uint32_t* status, void* stream);

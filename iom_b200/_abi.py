@@ -6,10 +6,13 @@ nothing in this package computes on the CPU instead.
 from __future__ import annotations
 
 import ctypes
+import os
 from pathlib import Path
 
 PACKAGE_DIR = Path(__file__).resolve().parent
-LIBRARY_PATH = PACKAGE_DIR / "libiom_b200.so"
+# IOMB_LIBRARY names another build of the same library (a variant compiled with other
+# flags, for side-by-side measurements); the default is the in-tree build.
+LIBRARY_PATH = Path(os.environ.get("IOMB_LIBRARY") or PACKAGE_DIR / "libiom_b200.so")
 
 MAX_RANK = 8
 MAX_LEADING = 6
@@ -52,6 +55,8 @@ PROTOTYPES = {
     "iomb_logical_nbytes": (ctypes.c_int, [_U64P, ctypes.c_uint32, ctypes.c_uint32, _U64P]),
     "iomb_plane_slot": (ctypes.c_uint64, [ctypes.c_uint64] * 5),
     "iomb_binary": (ctypes.c_int, [ctypes.c_int, _VIEW, _VIEW, _VIEW, ctypes.c_void_p]),
+    "iomb_binary_supported": (ctypes.c_int, [ctypes.c_uint32]),
+    "iomb_prepare_device": (ctypes.c_int, [ctypes.c_void_p]),
     "iomb_rmsnorm": (ctypes.c_int, [_VIEW, _VIEW, _VIEW, ctypes.c_float, ctypes.c_int, ctypes.c_void_p]),
     "iomb_add_rmsnorm": (ctypes.c_int, [_VIEW, _VIEW, _VIEW, _VIEW, _VIEW, ctypes.c_float,
                                         ctypes.c_int, ctypes.c_void_p]),

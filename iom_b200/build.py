@@ -16,7 +16,7 @@ from pathlib import Path
 PACKAGE_DIR = Path(__file__).resolve().parent
 CSRC = PACKAGE_DIR / "csrc"
 LIBRARY = PACKAGE_DIR / "libiom_b200.so"
-SOURCES = ["host.cu", "binary.cu", "rmsnorm.cu", "copy.cu", "gather.cu", "sumsq.cu", "silu.cu", "rope.cu", "sdpa.cu"]
+SOURCES = ["host.cu", "binary.cu", "rmsnorm.cu", "rmsnorm_long.cu", "copy.cu", "gather.cu", "sumsq.cu", "silu.cu", "rope.cu", "sdpa.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -45,18 +45,21 @@ def is_stale() -> bool:
     return any(path.stat().st_mtime > built for path in inputs)
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
-    if not force and not is_stale():
-        return LIBRARY
+def build(force: bool = False, verbose: bool = False, defines: tuple = (),
+          library: Path = LIBRARY, build_dir_name: str = "build") -> Path:
+    """`defines` (e.g. ("IOMB_PACKED_BF16=1",)) with another `library` / `build_dir_name`
+    gives a variant build beside the default one."""
+    if not force and not defines and not is_stale():
+        return library
     nvcc = find_nvcc()
     objects = []
-    build_dir = PACKAGE_DIR / "build"
+    build_dir = PACKAGE_DIR / build_dir_name
     build_dir.mkdir(exist_ok=True)
     procs = []
     for source in sources():
         obj = build_dir / (source.stem + ".o")
         objects.append(obj)
-        command = [nvcc, *NVCC_FLAGS, "-c", str(source), "-o", str(obj)]
+        command = [nvcc, *NVCC_FLAGS, *[f"-D{d}" for d in defines], "-c", str(source), "-o", str(obj)]
         if verbose:
             command[1:1] = ["-Xptxas", "-v"]
             print(" ".join(command), flush=True)
@@ -72,12 +75,20 @@ def build(force: bool = False, verbose: bool = False) -> Path:
             print(f"nvcc failed on {source}", file=sys.stderr)
     if failed:
         raise RuntimeError("libiom_b200.so build failed")
-    link = [nvcc, "-shared", "-o", str(LIBRARY), *map(str, objects),
+    link = [nvcc, "-shared", "-o", str(library), *map(str, objects),
             "-gencode", "arch=compute_100a,code=sm_100a", "-Xcompiler", "-fPIC"]
     subprocess.run(link, check=True)
-    return LIBRARY
+    return library
 
 
 if __name__ == "__main__":
-    path = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv)
+    variant = [a.split("=", 1)[1] for a in sys.argv if a.startswith("--variant=")]
+    if variant:
+        # --variant=name:DEFINE=1[,DEFINE2=..] builds libiom_b200_<name>.so with those defines
+        name, _, defs = variant[0].partition(":")
+        path = build(force=True, verbose="--verbose" in sys.argv,
+                     defines=tuple(d for d in defs.split(",") if d),
+                     library=PACKAGE_DIR / f"libiom_b200_{name}.so", build_dir_name=f"build_{name}")
+    else:
+        path = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv)
     print(path)

@@ -49,6 +49,9 @@ __device__ __forceinline__ uint32_t apply_word(uint32_t a, uint32_t b) {
     } else if constexpr (L == Leaf::F32) {
         return f32_canonical_bits(apply_f32<OP>(__uint_as_float(a), __uint_as_float(b)));
     } else {
+        if constexpr (OP == IOMB_ADD) return add_bf16x2_canonical(a, b);
+        if constexpr (OP == IOMB_SUB) return sub_bf16x2_canonical(a, b);
+        if constexpr (OP == IOMB_MUL) return mul_bf16x2_canonical(a, b);
         return pack_bf16x2_canonical(apply_f32<OP>(bf16_lo(a), bf16_lo(b)),
                                      apply_f32<OP>(bf16_hi(a), bf16_hi(b)));
     }
@@ -417,12 +420,13 @@ static int launch_op(int op, const BinaryParams& params, bool linear,
 // path, so the kernel is the simple one: thread e owns logical element e of the
 // result, reads its two inputs through the same tile map the fast kernels use and
 // writes one element; broadcast operands read their row 0 / column 0.
-enum class Wide : int { Int8 = 0, Int16 = 1, Int64 = 2, Half = 3, F8E4M3 = 4, F8E5M2 = 5 };
+enum class Wide : int { Int8 = 0, Int16 = 1, Int64 = 2, Half = 3, F8E4M3 = 4, F8E5M2 = 5, Double = 6 };
 
 template <Wide W>
 struct WideTraits {
     static constexpr int kBytes =
-            (W == Wide::Int8 || W == Wide::F8E4M3 || W == Wide::F8E5M2) ? 1 : W == Wide::Int64 ? 8 : 2;
+            (W == Wide::Int8 || W == Wide::F8E4M3 || W == Wide::F8E5M2) ? 1
+            : (W == Wide::Int64 || W == Wide::Double) ? 8 : 2;
 };
 
 template <int BYTES>
@@ -525,6 +529,17 @@ __device__ __forceinline__ uint64_t apply_wide(uint64_t a, uint64_t b) {
         const float r = apply_f32<OP>(Format::decode(static_cast<uint32_t>(a)),
                                       Format::decode(static_cast<uint32_t>(b)));
         return Format::encode(r);
+    } else if constexpr (W == Wide::Double) {
+        // One IEEE binary64 operation, correctly rounded: the carrier of the reference's own
+        // GPU kernels (src/shared/standard_tiled_add.inl:110-116). The reference CPU backend
+        // computes in x87 extended precision and rounds a second time, which can differ in
+        // the last place (64 < 2 * 53 + 2); the bound is one code, measured in the tests.
+        const double x = __longlong_as_double(static_cast<long long>(a));
+        const double y = __longlong_as_double(static_cast<long long>(b));
+        const double r = OP == IOMB_ADD ? __dadd_rn(x, y) : OP == IOMB_MUL ? __dmul_rn(x, y)
+                : OP == IOMB_SUB ? __dsub_rn(x, y) : __ddiv_rn(x, y);
+        if (r != r) return 0x7FF8000000000000ull;
+        return static_cast<uint64_t>(__double_as_longlong(r));
     } else if constexpr (W == Wide::Half) {
         const float x = __half2float(__ushort_as_half(static_cast<unsigned short>(a)));
         const float y = __half2float(__ushort_as_half(static_cast<unsigned short>(b)));
@@ -657,7 +672,8 @@ static int launch_element(int op, const BinaryParams& params, cudaStream_t strea
         case IOMB_MUL: binary_element_kernel<W, IOMB_MUL><<<grid, kTiledThreads, 0, stream>>>(params, elements); break;
         case IOMB_SUB: binary_element_kernel<W, IOMB_SUB><<<grid, kTiledThreads, 0, stream>>>(params, elements); break;
         default:
-            if constexpr (W == Wide::Half || W == Wide::F8E4M3 || W == Wide::F8E5M2) {
+            if constexpr (W == Wide::Half || W == Wide::F8E4M3 || W == Wide::F8E5M2
+                          || W == Wide::Double) {
                 binary_element_kernel<W, IOMB_DIV><<<grid, kTiledThreads, 0, stream>>>(params, elements);
             } else {
                 return fail(IOMB_ERR_UNSUPPORTED, "binary: integer division is not admitted");
@@ -667,6 +683,10 @@ static int launch_element(int op, const BinaryParams& params, cudaStream_t strea
 }
 
 }  // namespace iomb
+
+extern "C" int iomb_binary_supported(uint32_t dtype) {
+    return dtype != IOMB_BOOL && dtype != IOMB_F8_E8M0 && iomb_dtype_bits(dtype) != 0 ? 1 : 0;
+}
 
 extern "C" int iomb_binary(int op, const iomb_view* lhs, const iomb_view* rhs,
                            const iomb_view* out, void* stream) {
@@ -756,9 +776,9 @@ extern "C" int iomb_binary(int op, const iomb_view* lhs, const iomb_view* rhs,
         case IOMB_F16: wide = static_cast<int>(Wide::Half); break;
         case IOMB_F8_E4M3FN: wide = static_cast<int>(Wide::F8E4M3); break;
         case IOMB_F8_E5M2: wide = static_cast<int>(Wide::F8E5M2); break;
+        case IOMB_F64: wide = static_cast<int>(Wide::Double); break;
         default:
-            return fail(IOMB_ERR_UNSUPPORTED,
-                        "binary: leaf is BOOL, F8_E8M0 or F64");
+            return fail(IOMB_ERR_UNSUPPORTED, "binary: leaf is BOOL or F8_E8M0");
     }
 
     BinaryParams params{};
@@ -795,6 +815,7 @@ extern "C" int iomb_binary(int op, const iomb_view* lhs, const iomb_view* rhs,
             case Wide::Int64: return launch_element<Wide::Int64>(op, params, element_stream);
             case Wide::F8E4M3: return launch_element<Wide::F8E4M3>(op, params, element_stream);
             case Wide::F8E5M2: return launch_element<Wide::F8E5M2>(op, params, element_stream);
+            case Wide::Double: return launch_element<Wide::Double>(op, params, element_stream);
             default: return launch_element<Wide::Half>(op, params, element_stream);
         }
     }

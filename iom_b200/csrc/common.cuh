@@ -74,20 +74,61 @@ __device__ __forceinline__ float bf16_hi(uint32_t word) {
     return __uint_as_float(word & 0xFFFF0000u);
 }
 
+// Every NaN half of a packed BF16 pair becomes the positive quiet NaN 0x7FC0 (the
+// reference's canonical encoding, src/shared/scalar_binary_codec.hpp:79-85); other halves
+// pass. One packed unordered compare gives an all-ones mask per NaN half, one logic
+// operation selects: no branch.
+__device__ __forceinline__ uint32_t canonical_bf16x2(uint32_t word) {
+    uint32_t nan_halves;
+    asm("set.nan.u32.bf16x2 %0, %1, %1;" : "=r"(nan_halves) : "r"(word));
+    return (word & ~nan_halves) | (nan_halves & 0x7FC07FC0u);
+}
+
 // Two binary32 values -> packed BF16 pair, round-to-nearest-even, overflow to
-// infinity, gradual underflow; every NaN becomes the positive quiet NaN 0x7FC0
-// (the reference's canonical encoding, src/shared/scalar_binary_codec.hpp:79-85).
+// infinity, gradual underflow; every NaN becomes 0x7FC0.
 __device__ __forceinline__ uint32_t pack_bf16x2_canonical(float lo, float hi) {
     const __nv_bfloat162 packed = __floats2bfloat162_rn(lo, hi);
-    uint32_t word = *reinterpret_cast<const uint32_t*>(&packed);
-    // A half is a NaN exactly when (half & 0x7FFF) > 0x7F80; adding 0x7F then
-    // carries into bit 15 of that half and never into the neighbouring half.
-    const uint32_t probe = (word & 0x7FFF7FFFu) + 0x007F007Fu;
-    if (probe & 0x80008000u) {
-        if (probe & 0x00008000u) word = (word & 0xFFFF0000u) | 0x00007FC0u;
-        if (probe & 0x80000000u) word = (word & 0x0000FFFFu) | 0x7FC00000u;
-    }
-    return word;
+    return canonical_bf16x2(*reinterpret_cast<const uint32_t*>(&packed));
+}
+
+// Packed BF16 arithmetic: the sm_100a packed instructions (add/sub/mul.rn.bf16x2: the
+// exact result rounded once to BF16, subnormals kept). Building with
+// -DIOMB_PACKED_BF16=0 gives each half one binary32 operation and one RNE narrowing
+// instead. Both are the reference codec's result: the binary32 detour is a double
+// rounding that cannot change a BF16 result (24 >= 2*8 + 2); the tests run every pair of
+// BF16 codes through the kernels against the codec.
+#ifndef IOMB_PACKED_BF16
+#define IOMB_PACKED_BF16 1
+#endif
+__device__ __forceinline__ uint32_t add_bf16x2_canonical(uint32_t a, uint32_t b) {
+#if IOMB_PACKED_BF16
+    uint32_t r;
+    asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return canonical_bf16x2(r);
+#else
+    return pack_bf16x2_canonical(__fadd_rn(bf16_lo(a), bf16_lo(b)),
+                                 __fadd_rn(bf16_hi(a), bf16_hi(b)));
+#endif
+}
+__device__ __forceinline__ uint32_t sub_bf16x2_canonical(uint32_t a, uint32_t b) {
+#if IOMB_PACKED_BF16
+    uint32_t r;
+    asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return canonical_bf16x2(r);
+#else
+    return pack_bf16x2_canonical(__fsub_rn(bf16_lo(a), bf16_lo(b)),
+                                 __fsub_rn(bf16_hi(a), bf16_hi(b)));
+#endif
+}
+__device__ __forceinline__ uint32_t mul_bf16x2_canonical(uint32_t a, uint32_t b) {
+#if IOMB_PACKED_BF16
+    uint32_t r;
+    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return canonical_bf16x2(r);
+#else
+    return pack_bf16x2_canonical(__fmul_rn(bf16_lo(a), bf16_lo(b)),
+                                 __fmul_rn(bf16_hi(a), bf16_hi(b)));
+#endif
 }
 
 // Plain RNE pack for values known not to be NaN.

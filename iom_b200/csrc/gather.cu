@@ -61,12 +61,37 @@ struct EmbeddingParams {
     RowGeometry row;
     uint32_t run;             // R: rows per plane
     uint32_t run_tiles;       // ceil(R / 16)
-    uint32_t index_bytes;     // 1, 2, 4 or 8
+    uint32_t index_bits;      // 2, 4, 8, 16, 32 or 64
     uint32_t index_signed;
     uint64_t vocabulary;
     uint64_t items;           // planes * run_tiles * ceil(tile_cols / kTilesPerItem)
     uint32_t* status;
 };
+
+// indices[b, 0, r]: tile column r / 16, in-tile row 0, column r % 16 of the index plane;
+// slots are packed LSB first, so an id of 2 or 4 bits never straddles a byte. Compared at
+// full width against the vocabulary (src/shared/standard_tiled_embedding.inl:160-172):
+// false for a negative id or one at or beyond the table's rows.
+__device__ __forceinline__ bool read_index(const EmbeddingParams& p, uint64_t index_plane,
+                                           uint32_t r, uint64_t* id_out) {
+    const uint64_t slot = ((index_plane * p.indices.tile_rows) * p.indices.tile_cols + r / kTile)
+                    * static_cast<uint64_t>(kTileSlots)
+            + r % kTile;
+    const uint64_t bit = slot * p.index_bits;
+    const unsigned char* address = p.indices.base + (bit >> 3);
+    uint64_t id = 0;
+    switch (p.index_bits) {
+        case 2: id = (*address >> (bit & 7u)) & 0x3u; break;
+        case 4: id = (*address >> (bit & 7u)) & 0xFu; break;
+        case 8: id = *address; break;
+        case 16: id = *reinterpret_cast<const uint16_t*>(address); break;
+        case 32: id = *reinterpret_cast<const uint32_t*>(address); break;
+        default: id = *reinterpret_cast<const uint64_t*>(address); break;
+    }
+    const bool negative = p.index_signed && ((id >> (p.index_bits - 1)) & 1u);
+    *id_out = id;
+    return !negative && id < p.vocabulary;
+}
 
 __global__ void __launch_bounds__(kRowThreads)
 embedding_kernel(const EmbeddingParams p) {
@@ -95,19 +120,8 @@ embedding_kernel(const EmbeddingParams p) {
             if (r >= p.run) continue;
             const uint32_t cv = k % vectors_per_row;
             // indices[b, 0, r]: tile column r / 16, in-tile row 0, column r % 16.
-            const unsigned char* id_address = p.indices.base
-                    + ((index_plane * p.indices.tile_rows) * p.indices.tile_cols + r / kTile)
-                            * static_cast<uint64_t>(kTileSlots) * p.index_bytes
-                    + (r % kTile) * p.index_bytes;
             uint64_t id = 0;
-            switch (p.index_bytes) {
-                case 1: id = *id_address; break;
-                case 2: id = *reinterpret_cast<const uint16_t*>(id_address); break;
-                case 4: id = *reinterpret_cast<const uint32_t*>(id_address); break;
-                default: id = *reinterpret_cast<const uint64_t*>(id_address); break;
-            }
-            const bool negative = p.index_signed && ((id >> (p.index_bytes * 8 - 1)) & 1u);
-            if (negative || id >= p.vocabulary) {
+            if (!read_index(p, index_plane, r, &id)) {
                 // Never form a table address from an invalid id
                 // (standard_tiled_embedding.inl:167-172); one report per row.
                 if (group == 0 && cv == 0) atomicOr(p.status, 1u);
@@ -311,19 +325,8 @@ embedding_narrow_kernel(const EmbeddingParams p, uint32_t bits, uint32_t cols, u
         const uint64_t rest = item / tile_cols;
         const uint32_t r = static_cast<uint32_t>(rest % p.run);
         const uint64_t index = rest / p.run;
-        const unsigned char* id_address = p.indices.base
-                + ((operand_plane(p.indices, p.leading, index) * p.indices.tile_rows) * p.indices.tile_cols
-                   + r / kTile) * static_cast<uint64_t>(kTileSlots) * p.index_bytes
-                + (r % kTile) * p.index_bytes;
         uint64_t id = 0;
-        switch (p.index_bytes) {
-            case 1: id = *id_address; break;
-            case 2: id = *reinterpret_cast<const uint16_t*>(id_address); break;
-            case 4: id = *reinterpret_cast<const uint32_t*>(id_address); break;
-            default: id = *reinterpret_cast<const uint64_t*>(id_address); break;
-        }
-        const bool negative = p.index_signed && ((id >> (p.index_bytes * 8 - 1)) & 1u);
-        if (negative || id >= p.vocabulary) {
+        if (!read_index(p, operand_plane(p.indices, p.leading, index), r, &id)) {
             if (tc == 0) atomicOr(p.status, 1u);
             continue;
         }
@@ -378,10 +381,10 @@ extern "C" int iomb_embedding(const iomb_view* table, const iomb_view* indices,
     }
     bool index_signed = false;
     switch (indices->dtype) {
+        case IOMB_I2: case IOMB_I4:
         case IOMB_I8: case IOMB_I16: case IOMB_I32: case IOMB_I64: index_signed = true; break;
+        case IOMB_U2: case IOMB_U4:
         case IOMB_U8: case IOMB_U16: case IOMB_U32: case IOMB_U64: break;
-        case IOMB_I2: case IOMB_U2: case IOMB_I4: case IOMB_U4:
-            return fail(IOMB_ERR_UNSUPPORTED, "embedding: sub-byte index leaves are not implemented");
         default:
             return fail(IOMB_ERR_UNSUPPORTED, "embedding: index leaf is not integral");
     }
@@ -403,7 +406,7 @@ extern "C" int iomb_embedding(const iomb_view* table, const iomb_view* indices,
     p.table = make_operand(*table, ft, strides[0], none, false, false);
     if (!narrow_payload) p.row = row_geometry(ft);
     p.run = static_cast<uint32_t>(fo.rows);
-    p.index_bytes = fi.bytes;
+    p.index_bits = fi.bits;
     p.index_signed = index_signed ? 1u : 0u;
     p.vocabulary = ft.rows;
     p.run_tiles = static_cast<uint32_t>(fo.tile_rows);

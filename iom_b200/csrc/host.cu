@@ -4,6 +4,10 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <mutex>
+#include <set>
+#include <utility>
+
 namespace iomb {
 
 namespace {
@@ -46,6 +50,27 @@ int sm_count() {
         cached[device] = count;
     }
     return cached[device];
+}
+
+int allow_full_shared_memory(const void* kernel) {
+    static std::mutex guard;
+    static std::set<std::pair<const void*, int>> prepared;
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess) return check_launch("current device");
+    const std::lock_guard<std::mutex> lock(guard);
+    if (prepared.count({kernel, device}) != 0) return IOMB_OK;
+    // Static and dynamic shared memory share the 227 KiB.
+    cudaFuncAttributes facts{};
+    if (cudaFuncGetAttributes(&facts, kernel) != cudaSuccess) {
+        return check_launch("kernel attributes");
+    }
+    const int dynamic = 227 * 1024 - static_cast<int>(facts.sharedSizeBytes);
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dynamic)
+            != cudaSuccess) {
+        return check_launch("shared-memory attribute");
+    }
+    prepared.insert({kernel, device});
+    return IOMB_OK;
 }
 
 unsigned grid_for(uint64_t work_items, unsigned ctas_per_sm) {
@@ -255,7 +280,16 @@ extern "C" {
 
 const char* iomb_last_error(void) { return iomb::g_error; }
 
-uint32_t iomb_abi_version(void) { return 1; }
+uint32_t iomb_abi_version(void) { return 2; }
+
+int iomb_prepare_device(void* stream) {
+    if (iomb::sm_count() <= 0) return iomb::fail(IOMB_ERR_DEVICE, "no CUDA device is current");
+    int status = iomb::prepare_rmsnorm_kernels();
+    if (status == IOMB_OK) status = iomb::prepare_rmsnorm_long_kernels();
+    if (status == IOMB_OK) status = iomb::prepare_sdpa_kernels();
+    if (status == IOMB_OK) status = iomb::prepare_silu(static_cast<cudaStream_t>(stream));
+    return status;
+}
 
 uint32_t iomb_dtype_bits(uint32_t dtype) {
     switch (dtype) {

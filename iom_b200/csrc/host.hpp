@@ -49,6 +49,18 @@ Operand make_operand(const iomb_view& view, const ViewFacts& facts,
 // Streaming multiprocessors of the current device (0 when it cannot be read).
 int sm_count();
 
+// Raises a kernel's dynamic shared-memory limit to the 227 KiB an SM offers, once per
+// kernel and device (the attribute belongs to the function, not to a launch, so it is
+// never lowered again: queues on other threads may be launching the same kernel).
+int allow_full_shared_memory(const void* kernel);
+
+// One-time set-up of each translation unit's kernels on the current device (behind
+// iomb_prepare_device): shared-memory limits, the BF16 SiLU table.
+int prepare_rmsnorm_kernels();
+int prepare_rmsnorm_long_kernels();
+int prepare_silu(cudaStream_t stream);
+int prepare_sdpa_kernels();
+
 // Grid size for grid-stride kernels: enough CTAs to fill every SM
 // `ctas_per_sm` times, never more than `work_items`.
 unsigned grid_for(uint64_t work_items, unsigned ctas_per_sm);

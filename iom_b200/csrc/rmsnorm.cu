@@ -20,147 +20,14 @@
 //   SEQUENTIAL  one accumulator per row in feature order (the portable build).
 // Rows holding an infinity or a NaN give the same result in either order, so
 // the reference's per-row fallback (reduction.cpp:109-129) needs no branch.
-#include "host.hpp"
+#include "rmsnorm.cuh"
+
+#include <stdlib.h>
 
 namespace iomb {
 
 constexpr int kRmsThreads = 256;
 constexpr uint32_t kUnitCapBytes = 64 * 1024;
-
-struct RmsParams {
-    Operand x;
-    Operand residual;   // fused only
-    Operand sum;        // fused only
-    Operand out;
-    const unsigned char* scale_row;   // first tile of the [1,F] scale plane
-    Leading leading;
-    uint32_t rows;
-    uint32_t cols;
-    uint32_t tile_rows;
-    uint32_t tile_cols;
-    uint32_t group_rows;        // g
-    uint32_t groups_per_band;   // 16 / g
-    uint64_t units;
-    float eps;
-    uint32_t order;
-};
-
-__device__ __forceinline__ void cp_async_16(void* shared_dst, const void* global_src) {
-    const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(shared_dst));
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(global_src)
-                 : "memory");
-}
-__device__ __forceinline__ void cp_async_wait_all() {
-    asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory");
-}
-
-
-template <int ELEM>
-__device__ __forceinline__ float decode_element(const unsigned char* bytes) {
-    if constexpr (ELEM == 2) {
-        return __uint_as_float(
-                static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(bytes)) << 16);
-    } else {
-        return *reinterpret_cast<const float*>(bytes);
-    }
-}
-
-// sum + x*x with both operations rounded (never contracted).
-__device__ __forceinline__ float accumulate_square(float sum, float value) {
-    return __fadd_rn(sum, __fmul_rn(value, value));
-}
-
-template <int ELEM>
-__device__ __forceinline__ uint4 add_vectors(uint4 a, uint4 b) {
-    if constexpr (ELEM == 2) {
-        auto word = [](uint32_t p, uint32_t q) {
-            return pack_bf16x2_canonical(__fadd_rn(bf16_lo(p), bf16_lo(q)),
-                                         __fadd_rn(bf16_hi(p), bf16_hi(q)));
-        };
-        return make_uint4(word(a.x, b.x), word(a.y, b.y), word(a.z, b.z), word(a.w, b.w));
-    } else {
-        auto word = [](uint32_t p, uint32_t q) {
-            return f32_canonical_bits(__fadd_rn(__uint_as_float(p), __uint_as_float(q)));
-        };
-        return make_uint4(word(a.x, b.x), word(a.y, b.y), word(a.z, b.z), word(a.w, b.w));
-    }
-}
-
-// Normalises one 16-byte vector: x from shared memory, w raw from shared memory.
-template <int ELEM>
-__device__ __forceinline__ uint4 normalize_vector(uint4 x, const unsigned char* w, float inv) {
-    if constexpr (ELEM == 2) {
-        const uint4 s = *reinterpret_cast<const uint4*>(w);
-        auto word = [inv](uint32_t xv, uint32_t sv) {
-            const float lo = __fmul_rn(__fmul_rn(bf16_lo(xv), inv), bf16_lo(sv));
-            const float hi = __fmul_rn(__fmul_rn(bf16_hi(xv), inv), bf16_hi(sv));
-            return pack_bf16x2_canonical(lo, hi);
-        };
-        return make_uint4(word(x.x, s.x), word(x.y, s.y), word(x.z, s.z), word(x.w, s.w));
-    } else {
-        const uint4 s = *reinterpret_cast<const uint4*>(w);
-        auto word = [inv](uint32_t xv, uint32_t sv) {
-            return f32_canonical_bits(
-                    __fmul_rn(__fmul_rn(__uint_as_float(xv), inv), __uint_as_float(sv)));
-        };
-        return make_uint4(word(x.x, s.x), word(x.y, s.y), word(x.z, s.z), word(x.w, s.w));
-    }
-}
-
-// (x * inv) * w for one 16-byte vector of x with the widened scale values at
-// `w`; `fast` skips the canonical-NaN fix-up for rows that cannot produce one.
-template <int ELEM>
-__device__ __forceinline__ uint4 normalize_with_scale(uint4 xv, const float* w, float inv,
-                                                      bool fast) {
-    const float4 w0 = *reinterpret_cast<const float4*>(w);
-    if constexpr (ELEM == 2) {
-        const float4 w1 = *reinterpret_cast<const float4*>(w + 4);
-        const float r0 = __fmul_rn(__fmul_rn(bf16_lo(xv.x), inv), w0.x);
-        const float r1 = __fmul_rn(__fmul_rn(bf16_hi(xv.x), inv), w0.y);
-        const float r2 = __fmul_rn(__fmul_rn(bf16_lo(xv.y), inv), w0.z);
-        const float r3 = __fmul_rn(__fmul_rn(bf16_hi(xv.y), inv), w0.w);
-        const float r4 = __fmul_rn(__fmul_rn(bf16_lo(xv.z), inv), w1.x);
-        const float r5 = __fmul_rn(__fmul_rn(bf16_hi(xv.z), inv), w1.y);
-        const float r6 = __fmul_rn(__fmul_rn(bf16_lo(xv.w), inv), w1.z);
-        const float r7 = __fmul_rn(__fmul_rn(bf16_hi(xv.w), inv), w1.w);
-        if (fast) {
-            return make_uint4(pack_bf16x2(r0, r1), pack_bf16x2(r2, r3), pack_bf16x2(r4, r5),
-                              pack_bf16x2(r6, r7));
-        }
-        return make_uint4(pack_bf16x2_canonical(r0, r1), pack_bf16x2_canonical(r2, r3),
-                          pack_bf16x2_canonical(r4, r5), pack_bf16x2_canonical(r6, r7));
-    } else {
-        const float r0 = __fmul_rn(__fmul_rn(__uint_as_float(xv.x), inv), w0.x);
-        const float r1 = __fmul_rn(__fmul_rn(__uint_as_float(xv.y), inv), w0.y);
-        const float r2 = __fmul_rn(__fmul_rn(__uint_as_float(xv.z), inv), w0.z);
-        const float r3 = __fmul_rn(__fmul_rn(__uint_as_float(xv.w), inv), w0.w);
-        if (fast) {
-            return make_uint4(__float_as_uint(r0), __float_as_uint(r1), __float_as_uint(r2),
-                              __float_as_uint(r3));
-        }
-        return make_uint4(f32_canonical_bits(r0), f32_canonical_bits(r1), f32_canonical_bits(r2),
-                          f32_canonical_bits(r3));
-    }
-}
-
-template <int ELEM>
-__device__ __forceinline__ void store_vector_masked(
-        unsigned char* address, uint4 value, uint32_t valid) {
-    constexpr uint32_t kPerVector = 16 / ELEM;
-    if (valid >= kPerVector) {
-        store_u4_stream(address, value);
-        return;
-    }
-    const uint32_t words[4] = {value.x, value.y, value.z, value.w};
-    for (uint32_t e = 0; e < valid; ++e) {
-        if constexpr (ELEM == 4) {
-            reinterpret_cast<uint32_t*>(address)[e] = words[e];
-        } else {
-            reinterpret_cast<uint16_t*>(address)[e] =
-                    static_cast<uint16_t>(words[e / 2] >> ((e & 1u) * 16));
-        }
-    }
-}
 
 // Shared memory of one CTA:
 //   [unit : tile_cols * G * 16 * ELEM bytes]  the staged rows of x, tile by tile
@@ -345,13 +212,7 @@ rmsnorm_kernel(const RmsParams p) {
         if (tid < G) {
             float sum;
             if (p.order == IOMB_RMS_LANES16) {
-                const float* l = lanes + tid * kTile;
-                float total[4];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    total[j] = __fadd_rn(__fadd_rn(__fadd_rn(l[j], l[j + 4]), l[j + 8]), l[j + 12]);
-                }
-                sum = __fadd_rn(__fadd_rn(total[0], total[2]), __fadd_rn(total[1], total[3]));
+                sum = combine_lanes(lanes + tid * kTile);
             } else {
                 const unsigned char* cursor = unit + tid * kRowBytes;
                 sum = 0.0f;
@@ -366,14 +227,8 @@ rmsnorm_kernel(const RmsParams p) {
                     sum = accumulate_square(sum, decode_element<ELEM>(cursor + c * ELEM));
                 }
             }
-            const float mean = __fdiv_rn(sum, static_cast<float>(p.cols));
-            const float root = __fsqrt_rn(__fadd_rn(mean, p.eps));
-            inverse[tid] = __fdiv_rn(1.0f, root);
-            // With a finite, not vanishing sum every |x * inv| stays near
-            // sqrt(F) at most, so (x * inv) * w cannot be a NaN for finite w and
-            // the canonical-NaN fix-up can be skipped for the whole row.
-            clean[tid] = (sum >= 5.421010862e-20f && sum <= 3.402823466e+38f && scale_finite)
-                    ? 1u : 0u;
+            inverse[tid] = row_inverse(sum, p.cols, p.eps);
+            clean[tid] = row_is_clean(sum, scale_finite) ? 1u : 0u;
         }
         __syncthreads();
 
@@ -407,36 +262,7 @@ rmsnorm_kernel(const RmsParams p) {
                         w[2] = __uint_as_float(raw.z); w[3] = __uint_as_float(raw.w);
                     }
                 }
-                uint4 y;
-                if constexpr (ELEM == 2) {
-                    const float r0 = __fmul_rn(__fmul_rn(bf16_lo(xv.x), inv), w[0]);
-                    const float r1 = __fmul_rn(__fmul_rn(bf16_hi(xv.x), inv), w[1]);
-                    const float r2 = __fmul_rn(__fmul_rn(bf16_lo(xv.y), inv), w[2]);
-                    const float r3 = __fmul_rn(__fmul_rn(bf16_hi(xv.y), inv), w[3]);
-                    const float r4 = __fmul_rn(__fmul_rn(bf16_lo(xv.z), inv), w[4]);
-                    const float r5 = __fmul_rn(__fmul_rn(bf16_hi(xv.z), inv), w[5]);
-                    const float r6 = __fmul_rn(__fmul_rn(bf16_lo(xv.w), inv), w[6]);
-                    const float r7 = __fmul_rn(__fmul_rn(bf16_hi(xv.w), inv), w[7]);
-                    if (fast) {
-                        y = make_uint4(pack_bf16x2(r0, r1), pack_bf16x2(r2, r3),
-                                       pack_bf16x2(r4, r5), pack_bf16x2(r6, r7));
-                    } else {
-                        y = make_uint4(pack_bf16x2_canonical(r0, r1), pack_bf16x2_canonical(r2, r3),
-                                       pack_bf16x2_canonical(r4, r5), pack_bf16x2_canonical(r6, r7));
-                    }
-                } else {
-                    const float r0 = __fmul_rn(__fmul_rn(__uint_as_float(xv.x), inv), w[0]);
-                    const float r1 = __fmul_rn(__fmul_rn(__uint_as_float(xv.y), inv), w[1]);
-                    const float r2 = __fmul_rn(__fmul_rn(__uint_as_float(xv.z), inv), w[2]);
-                    const float r3 = __fmul_rn(__fmul_rn(__uint_as_float(xv.w), inv), w[3]);
-                    if (fast) {
-                        y = make_uint4(__float_as_uint(r0), __float_as_uint(r1),
-                                       __float_as_uint(r2), __float_as_uint(r3));
-                    } else {
-                        y = make_uint4(f32_canonical_bits(r0), f32_canonical_bits(r1),
-                                       f32_canonical_bits(r2), f32_canonical_bits(r3));
-                    }
-                }
+                const uint4 y = normalize_vector<ELEM>(xv, w, inv, fast);
                 store_vector_masked<ELEM>(out_cursor + static_cast<size_t>(tile) * kTileBytes, y,
                                           valid);
             };
@@ -449,6 +275,79 @@ rmsnorm_kernel(const RmsParams p) {
         __syncthreads();   // the unit buffer is reused by the next iteration
     }
     cp_async_wait_all();
+}
+
+// Rows too long for any staging (hundreds of KiB each): one CTA per row walks it twice
+// in global memory. The 16 column accumulators (or the single one of the sequential
+// order) are carried by sixteen threads (one) reading 2 or 4 bytes per tile, which is
+// slow and only keeps every row length admissible, as the reference admits them all
+// (src/device_ops_rmsnorm.cpp:75-127 has no feature limit).
+template <int ELEM>
+__global__ void __launch_bounds__(kRmsThreads)
+rmsnorm_unstaged_kernel(const RmsParams p) {
+    constexpr uint32_t kTileBytes = kTileSlots * ELEM;
+    constexpr uint32_t kRowBytes = kTile * ELEM;
+    constexpr uint32_t kVectorsPerRow = kRowBytes / 16;
+    constexpr uint32_t kPerVector = 16 / ELEM;
+    __shared__ float lanes[kTile];
+    __shared__ float inverse;
+    const uint32_t tid = threadIdx.x;
+    const uint32_t full_tiles = p.cols / kTile;
+    const uint32_t tail_cols = p.cols % kTile;
+    for (uint64_t u = blockIdx.x; u < p.units; u += gridDim.x) {
+        const RmsUnit at = rms_locate<1>(p, u);
+        if (!at.valid) continue;                              // uniform per CTA
+        const unsigned char* row = rms_unit_base<ELEM>(p, p.x, at);
+        unsigned char* out_row = rms_unit_base<ELEM>(p, p.out, at);
+        if (p.order == IOMB_RMS_LANES16) {
+            if (tid < kTile) {
+                float acc = 0.0f;
+                const unsigned char* cursor = row + tid * ELEM;
+                for (uint32_t tile = 0; tile < full_tiles; ++tile) {
+                    acc = accumulate_square(acc, decode_element<ELEM>(cursor));
+                    cursor += kTileBytes;
+                }
+                if (tid < tail_cols) acc = accumulate_square(acc, decode_element<ELEM>(cursor));
+                lanes[tid] = acc;
+            }
+            __syncthreads();
+        }
+        if (tid == 0) {
+            float sum = 0.0f;
+            if (p.order == IOMB_RMS_LANES16) {
+                sum = combine_lanes(lanes);
+            } else {
+                const unsigned char* cursor = row;
+                for (uint32_t tile = 0; tile <= full_tiles; ++tile) {
+                    const uint32_t live = tile < full_tiles ? kTile : tail_cols;
+                    for (uint32_t c = 0; c < live; ++c) {
+                        sum = accumulate_square(sum, decode_element<ELEM>(cursor + c * ELEM));
+                    }
+                    cursor += kTileBytes;
+                }
+            }
+            inverse = row_inverse(sum, p.cols, p.eps);
+        }
+        __syncthreads();
+        const float inv = inverse;
+        // One 16-byte vector per thread and step; the canonical-NaN path always.
+        const uint32_t vectors = p.tile_cols * kVectorsPerRow;
+        for (uint32_t k = tid; k < vectors; k += kRmsThreads) {
+            const uint32_t tile = k / kVectorsPerRow, cv = k % kVectorsPerRow;
+            const uint32_t col = tile * kTile + cv * kPerVector;
+            if (col >= p.cols) continue;
+            const uint4 xv = *reinterpret_cast<const uint4*>(
+                    row + static_cast<size_t>(tile) * kTileBytes + cv * 16);
+            const uint4 raw = __ldg(reinterpret_cast<const uint4*>(
+                    p.scale_row + static_cast<size_t>(tile) * kTileBytes + cv * 16));
+            float w[kPerVector];
+            widen_vector<ELEM>(raw, w);
+            store_vector_masked<ELEM>(out_row + static_cast<size_t>(tile) * kTileBytes + cv * 16,
+                                      normalize_vector<ELEM>(xv, w, inv, false),
+                                      min(kPerVector, p.cols - col));
+        }
+        __syncthreads();
+    }
 }
 
 using RmsKernel = void (*)(const RmsParams);
@@ -472,6 +371,38 @@ static RmsKernel pick_kernel(uint32_t g, bool fused, bool scale_smem) {
     return scale_smem ? pick_kernel<ELEM, false, true>(g) : pick_kernel<ELEM, false, false>(g);
 }
 
+
+template <int ELEM, bool FUSED, bool SCALE_SMEM>
+static int prepare_family() {
+    for (uint32_t g = 1; g <= kTile; g *= 2) {
+        const int status = allow_full_shared_memory(
+                reinterpret_cast<const void*>(pick_kernel<ELEM, FUSED, SCALE_SMEM>(g)));
+        if (status != IOMB_OK) return status;
+    }
+    return IOMB_OK;
+}
+
+int prepare_rmsnorm_kernels() {
+    int status = prepare_family<2, false, false>();
+    if (status == IOMB_OK) status = prepare_family<2, false, true>();
+    if (status == IOMB_OK) status = prepare_family<2, true, false>();
+    if (status == IOMB_OK) status = prepare_family<2, true, true>();
+    if (status == IOMB_OK) status = prepare_family<4, false, false>();
+    if (status == IOMB_OK) status = prepare_family<4, false, true>();
+    if (status == IOMB_OK) status = prepare_family<4, true, false>();
+    if (status == IOMB_OK) status = prepare_family<4, true, true>();
+    return status;
+}
+
+// IOMB_RMS_LONG=0 in the environment keeps long rows on the staged kernel above (for
+// side-by-side measurements); read once.
+static bool long_rows_enabled() {
+    static const bool enabled = [] {
+        const char* text = getenv("IOMB_RMS_LONG");
+        return text == nullptr || text[0] != '0';
+    }();
+    return enabled;
+}
 
 static int rms_dispatch(const iomb_view* x, const iomb_view* residual, const iomb_view* scale,
                         const iomb_view* sum, const iomb_view* out, float eps, int order,
@@ -529,6 +460,36 @@ static int rms_dispatch(const iomb_view* x, const iomb_view* residual, const iom
     }
     const uint32_t elem = fx.bytes;
     const uint64_t row_bytes = fx.tile_cols * kTile * elem;   // one row of a band
+    RmsParams p{};
+    const iomb_view* views[4] = {x, out, residual, sum};
+    uint64_t strides[4][kMaxLead] = {};
+    const uint32_t count = fused ? 4 : 2;
+    for (uint32_t k = 0; k < count; ++k) {
+        for (uint32_t axis = 0; axis < fx.leading; ++axis) {
+            strides[k][axis] = views[k]->plane_strides[axis];
+        }
+    }
+    collapse_leading(fx.leading, x->dims, strides, count, &p.leading);
+    p.x = make_operand(*x, fx, strides[0], p.leading, false, false);
+    p.out = make_operand(*out, fo, strides[1], p.leading, false, false);
+    if (fused) {
+        p.residual = make_operand(*residual, fr, strides[2], p.leading, false, false);
+        p.sum = make_operand(*sum, fm, strides[3], p.leading, false, false);
+    }
+    p.scale_row = static_cast<const unsigned char*>(scale->base) + scale->plane_offset * fs.plane_bytes;
+    p.rows = static_cast<uint32_t>(fx.rows);
+    p.cols = static_cast<uint32_t>(fx.cols);
+    p.tile_rows = static_cast<uint32_t>(fx.tile_rows);
+    p.tile_cols = static_cast<uint32_t>(fx.tile_cols);
+    p.eps = eps;
+    p.order = static_cast<uint32_t>(order);
+    // Rows of more than 2048 values in the lane order take the pipelined kernel.
+    if (order == IOMB_RMS_LANES16 && fx.tile_cols > 128 && long_rows_enabled()) {
+        bool launched = false;
+        const int status = launch_rmsnorm_long(p, elem, fused, row_bytes, p.leading.planes * p.tile_rows,
+                                               static_cast<cudaStream_t>(stream), &launched);
+        if (launched || status != IOMB_OK) return status;
+    }
     // Rows per unit: the staged rows (of x, and of the residual when fused) must
     // fit the staging capacity. (Prefetching the next unit into a second buffer
     // was measured 5-25 % slower: the units halve.) The widened
@@ -564,7 +525,16 @@ static int rms_dispatch(const iomb_view* x, const iomb_view* residual, const iom
     }
     const uint64_t staged_bytes = static_cast<uint64_t>(operands) * g * row_bytes;
     if (staged_bytes > 160 * 1024) {
-        return fail(IOMB_ERR_UNSUPPORTED, "rmsnorm: feature extent exceeds the staging capacity");
+        // A single row beyond the staging capacity (more than 81 920 BF16 or 40 960 F32
+        // values): the unstaged kernel, one CTA per row, both passes from global memory.
+        // g == 1 here, so the fused form has already been split into add + rmsnorm above.
+        p.group_rows = 1;
+        p.groups_per_band = kTile;
+        p.units = p.leading.planes * p.tile_rows * kTile;
+        const unsigned rows_grid = grid_for(p.units, 8);
+        if (elem == 2) rmsnorm_unstaged_kernel<2><<<rows_grid, kRmsThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+        else rmsnorm_unstaged_kernel<4><<<rows_grid, kRmsThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+        return check_launch("rmsnorm launch");
     }
     const uint64_t fixed_bytes = (kTile * kTile + 2 * kTile) * sizeof(float);
     const uint64_t scale_bytes = fx.tile_cols * kTile * sizeof(float);
@@ -572,39 +542,14 @@ static int rms_dispatch(const iomb_view* x, const iomb_view* residual, const iom
     const bool scale_smem = staged_bytes + scale_bytes + fixed_bytes <= per_cta_budget;
     const uint64_t smem_bytes = staged_bytes + (scale_smem ? scale_bytes : 0) + fixed_bytes;
 
-    RmsParams p{};
-    const iomb_view* views[4] = {x, out, residual, sum};
-    uint64_t strides[4][kMaxLead] = {};
-    const uint32_t count = fused ? 4 : 2;
-    for (uint32_t k = 0; k < count; ++k) {
-        for (uint32_t axis = 0; axis < fx.leading; ++axis) {
-            strides[k][axis] = views[k]->plane_strides[axis];
-        }
-    }
-    collapse_leading(fx.leading, x->dims, strides, count, &p.leading);
-    p.x = make_operand(*x, fx, strides[0], p.leading, false, false);
-    p.out = make_operand(*out, fo, strides[1], p.leading, false, false);
-    if (fused) {
-        p.residual = make_operand(*residual, fr, strides[2], p.leading, false, false);
-        p.sum = make_operand(*sum, fm, strides[3], p.leading, false, false);
-    }
-    p.scale_row = static_cast<const unsigned char*>(scale->base) + scale->plane_offset * fs.plane_bytes;
-    p.rows = static_cast<uint32_t>(fx.rows);
-    p.cols = static_cast<uint32_t>(fx.cols);
-    p.tile_rows = static_cast<uint32_t>(fx.tile_rows);
-    p.tile_cols = static_cast<uint32_t>(fx.tile_cols);
     p.group_rows = g;
     p.groups_per_band = kTile / g;
     p.units = p.leading.planes * p.tile_rows * p.groups_per_band;
-    p.eps = eps;
-    p.order = static_cast<uint32_t>(order);
 
     RmsKernel kernel = elem == 2 ? pick_kernel<2>(g, fused, scale_smem)
                                  : pick_kernel<4>(g, fused, scale_smem);
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             static_cast<int>(smem_bytes)) != cudaSuccess) {
-        return check_launch("rmsnorm shared-memory attribute");
-    }
+    const int prepared = allow_full_shared_memory(reinterpret_cast<const void*>(kernel));
+    if (prepared != IOMB_OK) return prepared;
     // Persistent CTAs, as many per SM as shared memory allows: the scale row is
     // staged once per CTA and a CTA's phases overlap with its neighbours'.
     unsigned per_sm = static_cast<unsigned>((227 * 1024) / (smem_bytes + 1024));

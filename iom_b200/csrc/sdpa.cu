@@ -766,15 +766,24 @@ int softmax_launch(const iomb_sdpa_stages* stages, bool scale, bool keep, void* 
     constexpr int kTileBytes = 2 * kGroupRows * kRowStride * static_cast<int>(sizeof(float));
     auto kernel = !scale ? softmax_kernel<false, false>
                          : (keep ? softmax_kernel<true, true> : softmax_kernel<true, false>);
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTileBytes)
-        != cudaSuccess) {
-        return check_launch("sdpa softmax shared-memory attribute");
-    }
+    const int prepared = allow_full_shared_memory(reinterpret_cast<const void*>(kernel));
+    if (prepared != IOMB_OK) return prepared;
     kernel<<<grid, kSoftmaxThreads, kTileBytes, s>>>(p);
     return check_launch("sdpa softmax launch");
 }
 
 }  // namespace
+
+int prepare_sdpa_kernels() {
+    const void* kernels[3] = {reinterpret_cast<const void*>(softmax_kernel<false, false>),
+                              reinterpret_cast<const void*>(softmax_kernel<true, true>),
+                              reinterpret_cast<const void*>(softmax_kernel<true, false>)};
+    for (const void* kernel : kernels) {
+        const int status = allow_full_shared_memory(kernel);
+        if (status != IOMB_OK) return status;
+    }
+    return IOMB_OK;
+}
 
 }  // namespace iomb
 

@@ -393,10 +393,8 @@ static int silu_dispatch(const iomb_view* x, const iomb_view* up, const iomb_vie
         const bool staged = bf16 && vectors * 16 >= (16ull << 20);
         if (staged) {
             auto kernel = fused ? silu_stream_kernel<2, true, true> : silu_stream_kernel<2, false, true>;
-            if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     static_cast<int>(kSiluTableBytes)) != cudaSuccess) {
-                return check_launch("silu shared-memory attribute");
-            }
+            const int prepared = allow_full_shared_memory(reinterpret_cast<const void*>(kernel));
+            if (prepared != IOMB_OK) return prepared;
             const uint64_t per_cta = static_cast<uint64_t>(kSiluStagedThreads) * kSiluUnroll;
             kernel<<<grid_for((vectors + per_cta - 1) / per_cta, 1), kSiluStagedThreads,
                      kSiluTableBytes, s>>>(xs, us, as, os, vectors, table);
@@ -422,6 +420,20 @@ static int silu_dispatch(const iomb_view* x, const iomb_view* up, const iomb_vie
         }
     }
     return check_launch("silu launch");
+}
+
+int prepare_silu(cudaStream_t stream) {
+    const uint16_t* table = nullptr;
+    int status = silu_table(stream, &table);
+    if (status == IOMB_OK) {
+        status = allow_full_shared_memory(
+                reinterpret_cast<const void*>(silu_stream_kernel<2, true, true>));
+    }
+    if (status == IOMB_OK) {
+        status = allow_full_shared_memory(
+                reinterpret_cast<const void*>(silu_stream_kernel<2, false, true>));
+    }
+    return status;
 }
 
 }  // namespace iomb

@@ -34,6 +34,11 @@ OID_INTERNAL_ERROR = -6
 ADD, MUL, SUB, DIV = 0, 1, 2, 3
 RMS_LANES16, RMS_SEQUENTIAL = 0, 1
 
+
+def facade_order(data_type) -> int:
+    """Accumulation order an operation takes when the caller names none."""
+    return RMS_SEQUENTIAL if data_type == DataType.F32 else RMS_LANES16
+
 _ALIGNMENT = 256          # arena suballocation granularity (the contract needs 32)
 _MAX_QUEUES = 4           # src/device_ops.cpp:210-218
 _SEQUENCE_BITS = 55       # token = (queue_id << 55) | sequence
@@ -743,10 +748,15 @@ class B200Queue:
         return self._binary(DIV, lhs, rhs, out)
 
     def rmsnorm(self, x: TensorView, scale: TensorView, out: TensorView, eps: float,
-                workspace: Optional[RawWorkspaceView] = None, order: int = RMS_LANES16) -> int:
+                workspace: Optional[RawWorkspaceView] = None, order: Optional[int] = None) -> int:
+        """`order` None takes the facade's choice: the lane order for BF16 (the reference's
+        AVX-512 BF16 build, bit for bit), the sequential order for F32 (the only F32 order
+        the reference has, src/cpu/queue.cpp:1187-1196, bit for bit)."""
         try:
             for view, what in ((x, "x"), (scale, "scale"), (out, "out")):
                 self._check_view(view, what)
+            if order is None:
+                order = facade_order(x.spec.data_type)
             if workspace is not None and not workspace.empty():
                 raise ValueError("rmsnorm takes no workspace")
             a, b, c = x.as_abi(), scale.as_abi(), out.as_abi()
@@ -759,12 +769,14 @@ class B200Queue:
 
     def add_rmsnorm(self, x: TensorView, residual: TensorView, scale: TensorView,
                     total: TensorView, out: TensorView, eps: float,
-                    order: int = RMS_LANES16) -> int:
+                    order: Optional[int] = None) -> int:
         """Extension: residual ADD fused into the following RMSNorm."""
         try:
             views = (x, residual, scale, total, out)
             for view in views:
                 self._check_view(view, "add_rmsnorm")
+            if order is None:
+                order = facade_order(x.spec.data_type)
             abis = [v.as_abi() for v in views]
         except BaseException as error:
             return _exception_to_oid(error)

@@ -404,51 +404,80 @@ std::int64_t iomref_cast(void* queue, void* source, void* destination) {
     return iom::b200::cast(ops_of(queue), view_of(source), view_of(destination));
 }
 
-// positions: host array of `count` row offsets; staged into a workspace of the device
-// together with the status word. Returns the token; *status_out receives the status
-// word after completion.
+// positions: host array of `count` row offsets, staged into a control workspace of the
+// device (status word first, offsets from byte 32). Returns the token; *status_out receives
+// the status word after completion.
 std::int64_t iomref_cache_append_batched(void* queue, void* source, void* destination,
                                          const std::uint32_t* positions, std::uint32_t count,
                                          std::uint32_t* status_out) {
-    std::uint32_t* device_words = nullptr;
-    if (cudaMalloc(reinterpret_cast<void**>(&device_words), (count + 8) * sizeof(std::uint32_t))
-            != cudaSuccess) {
+    auto* box = static_cast<QueueBox*>(queue);
+    std::unique_ptr<iom::RawWorkspace> control;
+    try {
+        control = box->device->device->create_workspace(iom::b200::batched_control_bytes(count));
+    } catch (...) {
         return -4;
     }
-    cudaMemcpy(device_words + 8, positions, count * sizeof(std::uint32_t), cudaMemcpyHostToDevice);
+    auto* words = static_cast<std::uint32_t*>(
+            iom::detail::WorkspaceValidation::address(control->view()));
+    cudaMemcpy(words + 8, positions, count * sizeof(std::uint32_t), cudaMemcpyHostToDevice);
     const std::int64_t token = iom::b200::cache_append_batched(
-            ops_of(queue), view_of(source), view_of(destination), device_words + 8, device_words);
+            ops_of(queue), view_of(source), view_of(destination), control->view());
     if (token > 0) {
         try {
             ops_of(queue).wait(token);
         } catch (...) {
         }
-        cudaMemcpy(status_out, device_words, sizeof(std::uint32_t), cudaMemcpyDeviceToHost);
+        cudaMemcpy(status_out, words, sizeof(std::uint32_t), cudaMemcpyDeviceToHost);
     }
-    cudaFree(device_words);
     return token;
 }
 
 std::int64_t iomref_sumsq(void* queue, void* x, float* value_out) {
-    void* scratch = nullptr;
-    if (cudaMalloc(&scratch, iom::b200::sumsq_scratch_bytes() + 32) != cudaSuccess) return -4;
-    float* result = reinterpret_cast<float*>(static_cast<unsigned char*>(scratch)
-                                             + iom::b200::sumsq_scratch_bytes());
-    const std::int64_t token = iom::b200::sumsq(ops_of(queue), view_of(x), scratch, result);
+    auto* box = static_cast<QueueBox*>(queue);
+    std::unique_ptr<iom::RawWorkspace> workspace;
+    try {
+        workspace = box->device->device->create_workspace(iom::b200::sumsq_workspace_bytes());
+    } catch (...) {
+        return -4;
+    }
+    const std::int64_t token = iom::b200::sumsq(ops_of(queue), view_of(x), workspace->view());
     if (token > 0) {
         try {
             ops_of(queue).wait(token);
         } catch (...) {
         }
-        cudaMemcpy(value_out, result, sizeof(float), cudaMemcpyDeviceToHost);
+        cudaMemcpy(value_out, iom::detail::WorkspaceValidation::address(workspace->view()),
+                   sizeof(float), cudaMemcpyDeviceToHost);
     }
-    cudaFree(scratch);
     return token;
 }
 
-// stage 0..3 as B200Queue::sdpa_stage, 4 = canonicalise `out`; device pointers from the caller.
+// A workspace of the device for callers that place buffers themselves (the attention
+// stage segments); returns the owner and writes its device address.
+void* iomref_workspace_create(void* device, std::uint64_t bytes, void** address_out) {
+    return guarded_pointer([&]() -> void* {
+        auto* box = static_cast<DeviceBox*>(device);
+        box->workspaces.push_back(box->device->create_workspace(bytes));
+        *address_out = iom::detail::WorkspaceValidation::address(box->workspaces.back()->view());
+        return box->workspaces.back().get();
+    });
+}
+
+// Plain copies between host memory and a device address (synchronous).
+int iomref_memcpy_b200(void* destination, const void* source, std::uint64_t bytes, int to_device) {
+    if (cudaDeviceSynchronize() != cudaSuccess
+            || cudaMemcpy(destination, source, bytes,
+                          to_device ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToHost) != cudaSuccess) {
+        g_last_error = "cudaMemcpy failed";
+        return 5;
+    }
+    return 0;
+}
+
+// stage 0..3 as B200Queue::sdpa_stage, 4 = canonicalise `out`; scores and probability are
+// device addresses inside `workspace` (an owner from iomref_workspace_create).
 std::int64_t iomref_sdpa_stage_b200(void* queue, int stage, void* scores, void* probability,
-                                    const std::uint64_t* geometry, void* out) {
+                                    const std::uint64_t* geometry, void* out, void* workspace) {
     std::int64_t token;
     if (stage == 4) {
         token = iom::b200::sdpa_canonicalize_output(ops_of(queue), view_of(out));
@@ -458,9 +487,10 @@ std::int64_t iomref_sdpa_stage_b200(void* queue, int stage, void* scores, void* 
         s.probability = probability;
         s.planes = geometry[0]; s.Hq = geometry[1]; s.Hkv = geometry[2]; s.R = geometry[3];
         s.C = geometry[4]; s.D = geometry[5]; s.a = geometry[6]; s.L = geometry[7];
-        if (stage == 0) token = iom::b200::sdpa_scale_mask(ops_of(queue), s);
-        else if (stage == 1) token = iom::b200::sdpa_softmax(ops_of(queue), s);
-        else token = iom::b200::sdpa_scale_mask_softmax(ops_of(queue), s, stage == 3);
+        const iom::RawWorkspaceView range = static_cast<iom::RawWorkspace*>(workspace)->view();
+        if (stage == 0) token = iom::b200::sdpa_scale_mask(ops_of(queue), s, range);
+        else if (stage == 1) token = iom::b200::sdpa_softmax(ops_of(queue), s, range);
+        else token = iom::b200::sdpa_scale_mask_softmax(ops_of(queue), s, stage == 3, range);
     }
     if (token > 0) {
         try {
@@ -470,6 +500,38 @@ std::int64_t iomref_sdpa_stage_b200(void* queue, int stage, void* scores, void* 
         }
     }
     return token;
+}
+
+// Host-side failure injection of the B200 backend: the ordinal of b200::SubmissionFault.
+void iomref_inject_fault_b200(int fault) {
+    iom::b200::inject_submission_fault_for_testing(static_cast<iom::b200::SubmissionFault>(fault));
+}
+
+std::uint64_t iomref_quarantined_events_b200(void* queue) {
+    return iom::b200::quarantined_event_count(ops_of(queue));
+}
+
+void iomref_tensor_destroy_b200(void* tensor) { delete static_cast<TensorBox*>(tensor); }
+
+// Recording and replay of a fixed sequence.
+int iomref_capture_begin_b200(void* queue) {
+    return guarded_status([&] { iom::b200::capture_begin(ops_of(queue)); });
+}
+
+void* iomref_capture_end_b200(void* queue) {
+    return guarded_pointer([&]() -> void* {
+        return new std::shared_ptr<iom::b200::CapturedSequence>(
+                iom::b200::capture_end(ops_of(queue)));
+    });
+}
+
+std::int64_t iomref_replay_b200(void* queue, void* recording) {
+    return iom::b200::replay(
+            ops_of(queue), *static_cast<std::shared_ptr<iom::b200::CapturedSequence>*>(recording));
+}
+
+void iomref_recording_destroy_b200(void* recording) {
+    delete static_cast<std::shared_ptr<iom::b200::CapturedSequence>*>(recording);
 }
 #endif
 

@@ -15,7 +15,7 @@ from support import HostTensor
 def gpu():
     if not torch.cuda.is_available():
         pytest.fail("GPU test selected but no CUDA device is visible")
-    device = make_b200_device(0, DeviceMemoryConfig(1 << 30))
+    device = make_b200_device(0, DeviceMemoryConfig(2 << 30))
     queue = device.create_ops()
     yield device, queue
     queue.close()

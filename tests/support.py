@@ -282,7 +282,15 @@ class Reference:
                                                                  ctypes.POINTER(ctypes.c_uint32)]),
                 "iomref_sumsq": (ctypes.c_int64, [vp, vp, ctypes.POINTER(ctypes.c_float)]),
                 "iomref_sdpa_stage_b200": (ctypes.c_int64, [vp, ctypes.c_int, vp, vp,
-                                                            ctypes.POINTER(ctypes.c_uint64), vp]),
+                                                            ctypes.POINTER(ctypes.c_uint64), vp, vp]),
+                "iomref_workspace_create": (vp, [vp, u64, ctypes.POINTER(vp)]),
+                "iomref_memcpy_b200": (ctypes.c_int, [vp, vp, u64, ctypes.c_int]),
+                "iomref_inject_fault_b200": (None, [ctypes.c_int]),
+                "iomref_quarantined_events_b200": (u64, [vp]),
+                "iomref_capture_begin_b200": (ctypes.c_int, [vp]),
+                "iomref_capture_end_b200": (vp, [vp]),
+                "iomref_replay_b200": (ctypes.c_int64, [vp, vp]),
+                "iomref_recording_destroy_b200": (None, [vp]),
             })
         for name, (restype, argtypes) in spec.items():
             fn = getattr(lib, name)

@@ -97,11 +97,11 @@ def test_binary_views_alias_and_rejections(pair):
         # the facade's own rejections arrive unchanged through the new backend
         assert ref.lib.iomref_binary(ref.queue, 0, ov[i].handle, other[i].handle, lv[i].handle) == -1
     same(out)
-    # leaves this backend does not serve: explicit Unsupported, never a fallback
+    # leaves no backend serves: explicit rejection, never a fallback
     cpu, gpu = pair
-    f64 = gpu.tensor((16, 16), DataType.F64)
-    assert gpu.lib.iomref_binary(gpu.queue, 0, f64.view().handle, f64.view().handle,
-                                 f64.view().handle) == -2
+    flag = gpu.tensor((16, 16), DataType.BOOL)
+    assert gpu.lib.iomref_binary(gpu.queue, 0, flag.view().handle, flag.view().handle,
+                                 flag.view().handle) < 0
     # a view of the other device is rejected by device identity
     foreign = cpu.tensor((2, 3, 17, 33), DataType.F32)
     assert gpu.lib.iomref_binary(gpu.queue, 0, foreign.view().handle, rv[1].handle, ov[1].handle) == -1
@@ -321,26 +321,53 @@ def test_attention_stage_extensions_of_the_cpp_backend(pair):
     raw_scores = host.scores.copy()
     packed = (ctypes.c_uint64 * 8)(*geometry)
 
-    def device_copy():
-        return (torch.from_numpy(raw_scores.copy()).cuda(),
-                torch.from_numpy(host.probability.astype(np.int16).copy()).cuda())
+    score_bytes = (raw_scores.nbytes + 31) // 32 * 32
+    probability_codes = host.probability.astype(np.uint16)
 
-    s2, p2 = device_copy()
+    class Segments:
+        """Scores and probabilities inside one workspace of the device, as the backend's
+        attention path would place them."""
+
+        def __init__(self):
+            address = ctypes.c_void_p()
+            self.owner = gpu.lib.iomref_workspace_create(
+                gpu.device, score_bytes + probability_codes.nbytes, ctypes.byref(address))
+            assert self.owner, gpu.error()
+            self.scores = address.value
+            self.probability = address.value + score_bytes
+            source = raw_scores.copy()
+            assert gpu.lib.iomref_memcpy_b200(self.scores, source.ctypes.data, source.nbytes, 1) == 0
+            assert gpu.lib.iomref_memcpy_b200(self.probability, probability_codes.ctypes.data,
+                                              probability_codes.nbytes, 1) == 0
+
+        def stage(self, number):
+            return gpu.lib.iomref_sdpa_stage_b200(gpu.queue, number, self.scores, self.probability,
+                                                  packed, None, self.owner)
+
+        def read(self):
+            scores = np.empty_like(raw_scores)
+            codes = np.empty_like(probability_codes)
+            assert gpu.lib.iomref_memcpy_b200(scores.ctypes.data, self.scores, scores.nbytes, 0) == 0
+            assert gpu.lib.iomref_memcpy_b200(codes.ctypes.data, self.probability, codes.nbytes, 0) == 0
+            return scores, codes
+
+    two = Segments()
     for stage in (0, 1):
-        assert gpu.lib.iomref_sdpa_stage_b200(gpu.queue, stage, s2.data_ptr(), p2.data_ptr(), packed, None) > 0
-    s1, p1 = device_copy()
-    assert gpu.lib.iomref_sdpa_stage_b200(gpu.queue, 3, s1.data_ptr(), p1.data_ptr(), packed, None) > 0
-    s0, p0 = device_copy()
-    assert gpu.lib.iomref_sdpa_stage_b200(gpu.queue, 2, s0.data_ptr(), p0.data_ptr(), packed, None) > 0
-    torch.cuda.synchronize()
-    assert torch.equal(p1, p2) and torch.equal(p0, p2)
-    assert torch.equal(s1.view(torch.int32), s2.view(torch.int32))
-    assert np.array_equal(s0.cpu().numpy().view(np.uint32), raw_scores.view(np.uint32))   # only read
+        assert two.stage(stage) > 0
+    kept = Segments()
+    assert kept.stage(3) > 0
+    read_only = Segments()
+    assert read_only.stage(2) > 0
+    s2, p2 = two.read()
+    s1, p1 = kept.read()
+    s0, p0 = read_only.read()
+    assert np.array_equal(p1, p2) and np.array_equal(p0, p2)
+    assert np.array_equal(s1.view(np.uint32), s2.view(np.uint32))
+    assert np.array_equal(s0.view(np.uint32), raw_scores.view(np.uint32))   # only read
     host.scale_mask().softmax()
-    got_scores = s2.cpu().numpy()
-    same = (got_scores.view(np.uint32) == host.scores.view(np.uint32)) | (np.isnan(got_scores) & np.isnan(host.scores))
+    same = (s2.view(np.uint32) == host.scores.view(np.uint32)) | (np.isnan(s2) & np.isnan(host.scores))
     assert same.all()
-    distance = np.abs(p2.cpu().numpy().view(np.uint16).astype(np.int32) - host.probability.astype(np.int32))
+    distance = np.abs(p2.astype(np.int32) - host.probability.astype(np.int32))
     assert distance.max() <= 1 and (distance != 0).mean() <= 2e-3
 
     rng = np.random.default_rng(32)
@@ -348,7 +375,7 @@ def test_attention_stage_extensions_of_the_cpp_backend(pair):
     codes[0, 0, :4] = [0x8000, 0x7FFF, 0xFF81, 0x3F80]
     out = gpu.tensor((3, 19, 40), DataType.BF16)
     out.view().from_host(codes)
-    assert gpu.lib.iomref_sdpa_stage_b200(gpu.queue, 4, None, None, packed, out.view().handle) > 0
+    assert gpu.lib.iomref_sdpa_stage_b200(gpu.queue, 4, None, None, packed, out.view().handle, None) > 0
     got = out.view().to_host()
     expected = codes.copy()
     zero = (codes & 0x7FFF) == 0

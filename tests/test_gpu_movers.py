@@ -128,6 +128,50 @@ def test_embedding_parity(gpu, index_dtype, payload):
     assert np.array_equal(download(do), out.storage)
 
 
+def pack_lsb_first(values, bits):
+    """Logical payload of a leaf narrower than a byte: codes packed LSB first, row-major."""
+    flat = np.asarray(values, dtype=np.uint64).reshape(-1)
+    out = np.zeros((flat.size * bits + 7) // 8, dtype=np.uint8)
+    for i, code in enumerate(flat):
+        bit = i * bits
+        out[bit >> 3] |= np.uint8((int(code) << (bit & 7)) & 0xFF)
+    return out
+
+
+@pytest.mark.parametrize("index_dtype,bits,signed", [(DataType.U2, 2, False), (DataType.I2, 2, True),
+                                                     (DataType.U4, 4, False), (DataType.I4, 4, True)])
+@pytest.mark.parametrize("payload", [DataType.BF16, DataType.U4])
+def test_embedding_index_leaves_narrower_than_a_byte(gpu, index_dtype, bits, signed, payload):
+    """Ids of 2 and 4 bits (src/device_ops_embedding.cpp:27-46 admits every integer leaf):
+    compared at full width, a set sign bit is a negative id."""
+    device, queue = gpu
+    rng = np.random.default_rng(bits * 10 + signed)
+    largest = (1 << (bits - 1)) - 1 if signed else (1 << bits) - 1
+    vocab, feat, run_len = largest, 37, 21         # the largest positive code is out of range
+    table = seeded((vocab, feat), payload, rng)
+    ids = rng.integers(0, vocab, size=(2, 1, run_len))
+    idx = HostTensor((2, 1, run_len), index_dtype).poison()
+    idx.view().copy_from_host(pack_lsb_first(ids, bits))
+    out = seeded((2, run_len, feat), payload, rng)
+    dt, di, do = upload(device, table), upload(device, idx), upload(device, out)
+    ws = device.create_workspace(32)
+    run(queue, queue.embedding(dt.view(), di.view(), do.view(), ws.view()))
+    status = ctypes.c_uint32(9)
+    assert oracle().iomo_embedding(abi(table.view()), abi(idx.view()), abi(out.view()),
+                                   ctypes.byref(status)) == 0
+    assert status.value == 0
+    assert np.array_equal(download(do), out.storage)
+    for bad_code in ([vocab] + ([(1 << bits) - 1] if signed else [])):   # too large; negative
+        bad = ids.copy()
+        bad[1, 0, 4] = bad_code
+        idx.view().copy_from_host(pack_lsb_first(bad, bits))
+        di2 = upload(device, idx)
+        token = queue.embedding(dt.view(), di2.view(), do.view(), ws.view())
+        assert token > 0
+        with pytest.raises(ValueError):
+            queue.wait(token)
+
+
 def test_embedding_decode_shape(gpu):
     """TinyLlama decode geometry: [32000,2048] BF16 table, 64 ids."""
     device, queue = gpu
