@@ -1,17 +1,26 @@
 #!/usr/bin/env python
-"""Benchmark of the hot path: fused residual ADD + RMSNorm on tiled BF16 storage.
+"""Benchmark of the hot path: residual ADD fused into RMSNorm on tiled BF16 storage.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-A step is one pass of iomb_add_rmsnorm over one batch of synthetic input: 16
-planes of the TinyLlama prefill shape (rows 8192, hidden 2048, BF16, eps 1e-5),
-one launch, 2.1 GB of algorithmic traffic, so every step streams from HBM (the
-batch is 17 times the L2 capacity). With N > 1 every rank runs the same batch on
-its own GPU (row shards are independent: no data-path collective) and rank 0
-prints the aggregate. One JSON line is printed; see the keys below.
+The workload is the large sharded configuration: BF16 [262144, 8192] residual ADD +
+RMSNorm (eps 1e-6, x, r ~ N(0,1), scale ~ N(1, 0.02)), 17.2 GB of algorithmic traffic per
+step. With N GPUs (one process per GPU, torchrun) the rows are cut on 16-row band
+boundaries (iom_b200.sharding.shard_rows): rank k owns rows/N rows in its own GPU's
+memory, the scale row is replicated, and no data-path collective exists ("scaling":
+"strong"). A step is one iomb_add_rmsnorm launch over the rank's shard, issued through
+the C++ backend (libiom_b200_backend.so, b200::add_rmsnorm on a device from
+make_b200_device) and timed with CUDA events on the queue's stream, max over ranks. The
+one exchange of the path, the whole-tensor FP32 sum of squares, is timed separately:
+per-rank iomb_sumsq, NCCL all_gather of one float per rank, rank-ordered FP32 addition.
 
-`--impl reference` times the reference's own CPU backend (oracle/_ref when the
-shim is built, else the plain-C oracle port) on the host cores.
+`e2e` is the same step through the reference's public interface with host buffers:
+TensorView::copy_from_host(x), copy_from_host(residual), add_rmsnorm, wait,
+copy_to_host(out), pinned host memory in the logical row-major layout, every step.
+
+`--impl reference` times the reference's own CPU backend (oracle/_ref when the shim is
+built, else the plain-C oracle port) on the host cores, on bounded row shards of the same
+workload.
 """
 from __future__ import annotations
 
@@ -30,28 +39,32 @@ for entry in (str(ROOT), str(ROOT / "tests")):
     if entry not in sys.path:
         sys.path.insert(0, entry)
 
-PLANES, ROWS, HIDDEN, EPS = 16, 8192, 2048, 1e-5
+ROWS, HIDDEN, EPS = 262144, 8192, 1e-6
 ELEM = 2
-ELEMENTS = PLANES * ROWS * HIDDEN
-# x and residual read, rounded sum and normalised output written, scale read once
-ALGORITHMIC_BYTES = 4 * ELEMENTS * ELEM + HIDDEN * ELEM
-METRIC = "achieved HBM GB/s, fused residual ADD + RMSNorm (BF16, TinyLlama prefill shape)"
-WORKLOAD = (f"C2 x{PLANES}: BF16 [{PLANES},{ROWS},{HIDDEN}] residual ADD + RMSNorm, eps 1e-5, "
-            "x,r ~ N(0,1), w ~ N(1,0.02)")
-# dram__bytes_read.sum + dram__bytes_write.sum of one rmsnorm_kernel launch, from
-# the ncu capture summarised in profiles/ (taken on a [2,8192,2048] case; traffic
-# is proportional to the rows processed, so it is scaled by the plane count).
-NCU_TRAFFIC_BYTES_PER_PLANE = 213.98e6 / 2     # 134.32 MB read + 79.66 MB written, 2 planes
+METRIC = "achieved HBM GB/s, fused residual ADD + RMSNorm (BF16 [262144,8192], row-sharded)"
+# dram__bytes_read.sum / dram__bytes_write.sum of one launch of the kernel the step runs,
+# per row, from the ncu capture summarised in profiles/add_rmsnorm_bf16_long_rows.md
+# (taken on a [32768,8192] shard: 2.1 GB per launch, 17 times the L2, so the written
+# lines cannot stay in the cache; traffic is proportional to the rows processed).
+NCU_READ_BYTES_PER_ROW = None
+NCU_WRITE_BYTES_PER_ROW = None
 
 
-def configure(planes: int) -> None:
-    """Resizes the batch (the default is the benchmark's; profiler captures shrink it)."""
-    global PLANES, ELEMENTS, ALGORITHMIC_BYTES, WORKLOAD
-    PLANES = planes
-    ELEMENTS = PLANES * ROWS * HIDDEN
-    ALGORITHMIC_BYTES = 4 * ELEMENTS * ELEM + HIDDEN * ELEM
-    WORKLOAD = (f"C2 x{PLANES}: BF16 [{PLANES},{ROWS},{HIDDEN}] residual ADD + RMSNorm, "
-                "eps 1e-5, x,r ~ N(0,1), w ~ N(1,0.02)")
+def configure(rows: int) -> None:
+    """Resizes the tensor (the default is the benchmark's; profiler captures shrink it)."""
+    global ROWS
+    ROWS = rows
+
+
+def workload(world: int) -> str:
+    per_rank = f"{ROWS // world} rows per rank on {world} rank(s)" if world > 1 else "one GPU holds all rows"
+    return (f"C5: BF16 [{ROWS},{HIDDEN}] residual ADD + RMSNorm, eps 1e-6, x,r ~ N(0,1) seed 2, "
+            f"w ~ N(1,0.02), row-sharded on band boundaries; {per_rank}")
+
+
+def step_bytes(rows: int) -> int:
+    """x and residual read, rounded sum and normalised output written, scale read once."""
+    return 4 * rows * HIDDEN * ELEM + HIDDEN * ELEM
 
 
 def measured_peak():
@@ -122,20 +135,20 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(clocks)}
 
 
-def synthetic_inputs(seed: int):
-    """Seeded logical payloads (BF16 codes) of the batch; C2's distributions."""
-    import numpy as np
+def fill_normal_bf16(storage, seed: int, mean: float = 0.0, deviation: float = 1.0) -> None:
+    """Fills a tiled BF16 owner (uint8 torch view of its storage) with seeded normal values,
+    a gigabyte at a time. The tiled layout of independent samples is independent samples, so
+    the values go straight into storage."""
+    import torch
 
-    def f32_to_bf16_bits(values):
-        bits = np.ascontiguousarray(values, dtype=np.float32).view(np.uint32).astype(np.uint64)
-        return ((bits + 0x7FFF + ((bits >> 16) & 1)) >> 16).astype(np.uint16)
-
-    rng = np.random.default_rng(seed)
-    shape = (PLANES, ROWS, HIDDEN)
-    x = f32_to_bf16_bits(rng.standard_normal(shape, dtype=np.float32))
-    r = f32_to_bf16_bits(rng.standard_normal(shape, dtype=np.float32))
-    w = f32_to_bf16_bits((1.0 + 0.02 * rng.standard_normal((1, HIDDEN))).astype(np.float32))
-    return x, r, w
+    generator = torch.Generator(device=storage.device)
+    generator.manual_seed(seed)
+    words = storage.view(torch.bfloat16)
+    chunk = 1 << 27
+    for start in range(0, words.numel(), chunk):
+        part = words[start:start + chunk]
+        part.copy_(torch.randn(part.numel(), device=storage.device, generator=generator,
+                               dtype=torch.float32).mul_(deviation).add_(mean))
 
 
 def run_ours(args) -> dict:
@@ -143,8 +156,9 @@ def run_ours(args) -> dict:
     import torch
     import torch.distributed as dist
 
-    from iom_b200.device import DeviceMemoryConfig, make_b200_device
-    from iom_b200.tensor import DataType, TensorSpec
+    from iom_b200 import _abi, backend_driver as bd
+    from iom_b200.sharding import all_gather_sum, shard_rows
+    from iom_b200.tensor import DataType
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -160,35 +174,29 @@ def run_ours(args) -> dict:
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
-    arena = max(5 * PLANES * ROWS * HIDDEN * ELEM + 7 * ROWS * HIDDEN * ELEM + (64 << 20),
-                0 if args.no_ops else 5 << 30)
-    device = make_b200_device(local_rank, DeviceMemoryConfig(arena // 32 * 32))
-    queue = device.create_ops()
-    shape = (PLANES, ROWS, HIDDEN)
-    spec = TensorSpec(shape, DataType.BF16)
-    x, r, total, out = (device.create_tensor(spec) for _ in range(4))
-    scale = device.create_tensor(TensorSpec((1, HIDDEN), DataType.BF16))
-    logical_bytes = spec.logical_nbytes()
-    staging = device.create_workspace(logical_bytes + 64)
+    first_row, rows = shard_rows(ROWS, world, rank)
+    elements = rows * HIDDEN
+    tensor_bytes = elements * ELEM
+    kernel_lib = _abi.load_library()
+    # Arena: the shard's four tensors, the host-transfer staging range, small change.
+    arena = 4 * tensor_bytes + (0 if args.no_e2e else tensor_bytes + (1 << 20)) + (256 << 20)
+    backend = bd.Backend(local_rank, arena)
+    x, r, total, out = (backend.tensor((rows, HIDDEN), DataType.BF16) for _ in range(4))
+    scale = backend.tensor((1, HIDDEN), DataType.BF16)
+    vx, vr, vt, vo, vw = (backend.view(t) for t in (x, r, total, out, scale))
+    # Seeded inputs, generated on the device (seed 2, one stream per rank and operand).
+    fill_normal_bf16(backend.storage(x), seed=2 + 1000 * rank)
+    fill_normal_bf16(backend.storage(r), seed=2 + 1000 * rank + 500)
+    rng = np.random.default_rng(2)
+    w_host = (1.0 + 0.02 * rng.standard_normal((1, HIDDEN))).astype(np.float32)
+    w_bits = ((w_host.view(np.uint32).astype(np.uint64) + 0x7FFF
+               + ((w_host.view(np.uint32) >> 16) & 1)) >> 16).astype(np.uint16)
+    small = backend.workspace(1 << 20)
+    backend.run([bd.Backend.op(bd.FROM_HOST, [vw], workspace=small, host=w_bits.ctypes.data,
+                               host_bytes=w_bits.nbytes)])
+    torch.cuda.synchronize()
 
-    # Seeded inputs live in pinned host memory in the logical row-major layout the
-    # reference's copy_from_host takes.
-    x_host, r_host, w_host = synthetic_inputs(seed=1000 + rank)
-    pinned = {}
-    for name, array in (("x", x_host), ("r", r_host)):
-        buffer = torch.empty(array.size, dtype=torch.int16, pin_memory=True)
-        buffer.numpy().view(np.uint16)[:] = array.reshape(-1)
-        pinned[name] = buffer
-    out_host = torch.empty(ELEMENTS, dtype=torch.int16, pin_memory=True)
-    scale.view().copy_from_host(w_host, staging.view())
-    x.view().copy_from_host(pinned["x"].numpy(), staging.view())
-    r.view().copy_from_host(pinned["r"].numpy(), staging.view())
-
-    def step():
-        token = queue.add_rmsnorm(x.view(), r.view(), scale.view(), total.view(), out.view(), EPS)
-        if token <= 0:
-            raise RuntimeError(f"add_rmsnorm rejected with oid {token}")
-        return token
+    step = [bd.Backend.op(bd.ADD_RMSNORM, [vx, vr, vw, vt, vo], eps=EPS)]
 
     def barrier():
         if world > 1:
@@ -196,115 +204,76 @@ def run_ours(args) -> dict:
         torch.cuda.synchronize()
 
     # ---- device-resident throughput (`value`) -----------------------------
-    for _ in range(args.warmup):
-        token = step()
-    queue.wait(token)
+    backend.run(step, passes=args.warmup)
+    kernel_name = (kernel_lib.iomb_last_launch() or b"").decode()
     barrier()
-    start = torch.cuda.Event(enable_timing=True)
-    stop = torch.cuda.Event(enable_timing=True)
     with ClockSampler(local_rank) as sampler:
-        start.record(queue.stream)
-        for _ in range(args.steps):
-            token = step()
-        stop.record(queue.stream)
-        queue.wait(token)
+        timing = backend.run(step, passes=args.steps)
         barrier()
-    elapsed_ms = start.elapsed_time(stop)
+    elapsed_ms = float(timing.device_ms)
     clocks = sampler.summary()
 
-    # ---- end to end through the public API with host buffers (`e2e`) -------
-    e2e_steps = max(1, min(args.steps, 3))
-
-    def e2e_step():
-        x.view().copy_from_host(pinned["x"].numpy(), staging.view())
-        r.view().copy_from_host(pinned["r"].numpy(), staging.view())
-        queue.wait(step())
-        out.view().copy_to_host(out_host.numpy(), staging.view())
-
-    # The same step with the asynchronous transfer operations: the batch goes plane by
-    # plane through two queues (streams), so that one queue's device-to-host copy
-    # runs while the other's host-to-device copies do (both PCIe directions busy).
-    plane_bytes = ROWS * HIDDEN * ELEM
-    lanes = []
-
-    def e2e_pipelined_step():
-        if not lanes:
-            for q in (queue, device.create_ops()):
-                lanes.append((q, [device.create_workspace(plane_bytes + 64) for _ in range(3)]))
-        tokens = [None, None]
-        for plane in range(PLANES):
-            q, (sx, sr, so) = lanes[plane % 2]
-            chunk = slice(plane * ROWS * HIDDEN, (plane + 1) * ROWS * HIDDEN)
-            xv, rv = x.view().select(0, plane), r.view().select(0, plane)
-            tv, ov = total.view().select(0, plane), out.view().select(0, plane)
-            for token in (q.upload(xv, pinned["x"].numpy()[chunk], sx.view()),
-                          q.upload(rv, pinned["r"].numpy()[chunk], sr.view()),
-                          q.add_rmsnorm(xv, rv, scale.view(), tv, ov, EPS)):
-                if token <= 0:
-                    raise RuntimeError(f"pipelined step rejected with oid {token}")
-            tokens[plane % 2] = q.download(ov, out_host.numpy()[chunk], so.view())
-            if tokens[plane % 2] <= 0:
-                raise RuntimeError(f"download rejected with oid {tokens[plane % 2]}")
-        for (q, _), token in zip(lanes, tokens):
-            q.wait(token)
-
+    # ---- end to end through the public interface with host buffers (`e2e`) -------
     e2e_ms = float("nan")
-    e2e_sync_ms = float("nan")
+    e2e_submit_us = None
     if not args.no_e2e:
-        e2e_step()
+        pinned = {name: torch.empty(tensor_bytes, dtype=torch.uint8, pin_memory=True)
+                  for name in ("x", "r", "out")}
+        # Host copies of the inputs in the logical row-major layout (any seeded values do:
+        # the timing does not depend on them, the device-resident leg's values are used).
+        pinned["x"].copy_(backend.storage(x))
+        pinned["r"].copy_(backend.storage(r))
+        staging = backend.workspace(tensor_bytes + 64)
+        e2e_program = [
+            bd.Backend.op(bd.FROM_HOST, [vx], workspace=staging, host=pinned["x"].data_ptr(),
+                          host_bytes=tensor_bytes),
+            bd.Backend.op(bd.FROM_HOST, [vr], workspace=staging, host=pinned["r"].data_ptr(),
+                          host_bytes=tensor_bytes),
+            bd.Backend.op(bd.ADD_RMSNORM, [vx, vr, vw, vt, vo], eps=EPS),
+            bd.Backend.op(bd.WAIT),
+            bd.Backend.op(bd.TO_HOST, [vo], workspace=staging, host=pinned["out"].data_ptr(),
+                          host_bytes=tensor_bytes),
+        ]
+        backend.run(e2e_program, passes=1)
         barrier()
-        t0 = time.perf_counter()
-        for _ in range(e2e_steps):
-            e2e_step()
-        torch.cuda.synchronize()
-        e2e_sync_ms = (time.perf_counter() - t0) * 1e3
-        reference_out = out_host.clone()
-        out_host.zero_()
-        e2e_pipelined_step()
+        e2e_timing = backend.run(e2e_program, passes=args.steps)
         barrier()
-        if not torch.equal(reference_out, out_host):
-            raise RuntimeError("pipelined end-to-end step and synchronous step disagree")
-        t0 = time.perf_counter()
-        for _ in range(e2e_steps):
-            e2e_pipelined_step()
-        torch.cuda.synchronize()
-        e2e_ms = (time.perf_counter() - t0) * 1e3
+        e2e_ms = e2e_timing.host_seconds * 1e3
 
     # ---- whole-tensor sum of squares across ranks (the one exchange step) ----
-    sumsq_info = None
+    sumsq_bytes = 32 + int(kernel_lib.iomb_sumsq_scratch_bytes())
+    sumsq_workspace = backend.workspace(sumsq_bytes)
+    # the workspace is leased for each call: wait before the next one names it again
+    sumsq_program = [bd.Backend.op(bd.SUMSQ, [vt], workspace=sumsq_workspace), bd.Backend.op(bd.WAIT)]
+    backend.run(sumsq_program, passes=2)
+    barrier()
+    sumsq_timing = backend.run(sumsq_program, passes=5)
+    local = backend.workspace_memory(sumsq_workspace, 4).view(torch.float32)
+    sumsq_info = {"kernel_ms_per_rank": float(sumsq_timing.device_ms) / 5,
+                  "bytes_read_per_rank": tensor_bytes,
+                  "kernel_GB/s_per_rank": tensor_bytes / (float(sumsq_timing.device_ms) / 5) / 1e6}
     if world > 1:
-        from iom_b200.sharding import all_gather_sum
-        scratch = device.create_workspace(int(device._lib.iomb_sumsq_scratch_bytes()))
-        local = torch.zeros(1, dtype=torch.float32, device=device.torch_device)
-
-        def sumsq_step():
-            token = queue.sumsq(total.view(), scratch.view(), local.data_ptr())
-            if token <= 0:
-                raise RuntimeError(f"sumsq rejected with oid {token}")
-            queue.wait(token)
-            return all_gather_sum(local)
-
-        combined = sumsq_step()
+        combined = all_gather_sum(local.clone())
         barrier()
         t0 = time.perf_counter()
         for _ in range(5):
-            combined = sumsq_step()
+            backend.run(sumsq_program, passes=1)
+            combined = all_gather_sum(local.clone())
         torch.cuda.synchronize()
-        sumsq_ms = (time.perf_counter() - t0) * 1e3 / 5
+        sumsq_info["ms_with_combine"] = (time.perf_counter() - t0) * 1e3 / 5
         gathered = [torch.empty_like(combined.reshape(1)) for _ in range(world)]
         dist.all_gather(gathered, combined.reshape(1))
-        sumsq_info = {"value": float(combined), "ms": sumsq_ms,
-                      "identical_on_all_ranks": all(torch.equal(gathered[0], g) for g in gathered),
-                      "bytes_read_per_rank": ELEMENTS * ELEM,
-                      "combine": "all_gather of one FP32 partial per rank, added in rank order"}
-        scratch.close()
+        sumsq_info.update({
+            "value": float(combined),
+            "identical_on_all_ranks": all(torch.equal(gathered[0], g) for g in gathered),
+            "combine": "all_gather of one FP32 partial per rank, added in rank order"})
+    else:
+        sumsq_info["value"] = float(local.cpu()[0])
 
+    backend.close()
     table = None
     if world == 1 and not args.no_ops:
-        for t in (x, r, total, out, scale):
-            t.close()
-        staging.close()
-        table = ops_table(device, queue)
+        table = ops_table_all(local_rank)
 
     times = torch.tensor([elapsed_ms, e2e_ms], dtype=torch.float64, device="cuda")
     if world > 1:
@@ -315,50 +284,149 @@ def run_ours(args) -> dict:
     if rank == 0:
         peak, peak_kind = measured_peak()
         per_launch_ms = elapsed_ms / args.steps
-        achieved = ALGORITHMIC_BYTES / per_launch_ms / 1e6
+        total_bytes = step_bytes(ROWS) + (world - 1) * HIDDEN * ELEM
+        achieved = step_bytes(rows) / per_launch_ms / 1e6        # this rank's kernel
+        traffic = None
+        if NCU_READ_BYTES_PER_ROW is not None:
+            traffic = (NCU_READ_BYTES_PER_ROW + NCU_WRITE_BYTES_PER_ROW) * rows
         result = {
             "metric": METRIC,
-            "value": world * ALGORITHMIC_BYTES * args.steps / elapsed_ms / 1e6,
+            "value": total_bytes * args.steps / elapsed_ms / 1e6,
             "unit": "GB/s",
             "n_gpus": world,
             "steps": args.steps,
             "warmup": args.warmup,
             "ms_per_step": per_launch_ms,
             "higher_is_better": True,
-            "scaling": "weak",
+            "scaling": "strong",
             "vs_baseline": None,
             "dtype": "f32 accumulate, bf16 storage",
-            "data": "synthetic (seeded normal, the TinyLlama prefill configuration's distributions)",
-            "config": {"workload": WORKLOAD, "launches_per_step": 1,
-                       "algorithmic_bytes_per_step": ALGORITHMIC_BYTES,
-                       "l2": f"inputs larger than L2 ({ALGORITHMIC_BYTES / 1e9:.2f} GB touched "
-                             "per step, L2 is 126 MB)",
-                       "order": "LANES16", "pct_of_8TBps": None},
+            "data": "synthetic (seeded normal, the large sharded configuration's distributions)",
+            "config": {"workload": workload(world), "launches_per_step": 1,
+                       "rows_per_rank": rows, "first_row_of_rank_0": first_row,
+                       "algorithmic_bytes_per_step": total_bytes,
+                       "l2": f"inputs larger than L2 ({step_bytes(rows) / 1e9:.2f} GB touched per rank "
+                             "and step, L2 is 126 MB)",
+                       "order": "LANES16 (the reference's AVX-512 BF16 order)",
+                       "host_layer": "C++ backend (libiom_b200_backend.so: b200::add_rmsnorm on a device "
+                                     "from make_b200_device), launches issued from C++",
+                       "timing": f"{args.steps} launches back to back between one pair of CUDA events "
+                                 "on the queue's stream, max over ranks",
+                       "pct_of_8TBps_per_gpu": 100.0 * achieved / 8000.0},
             "clocks": clocks,
-            "e2e": {"value": world * ALGORITHMIC_BYTES * e2e_steps / e2e_ms / 1e6, "unit": "GB/s",
-                    "h2d_bytes_per_step": 2 * logical_bytes, "d2h_bytes_per_step": logical_bytes,
-                    "steps": e2e_steps,
-                    "path": "per plane, alternating over two queues: upload(x), upload(r), "
-                            "add_rmsnorm, download(out); pinned host buffers in the logical layout",
-                    "synchronous_value": world * ALGORITHMIC_BYTES * e2e_steps / e2e_sync_ms / 1e6,
-                    "synchronous_path": "copy_from_host(x), copy_from_host(r), add_rmsnorm, "
-                                        "copy_to_host(out)"},
+            "e2e": {"value": total_bytes * args.steps / e2e_ms / 1e6 if e2e_ms == e2e_ms else None,
+                    "unit": "GB/s",
+                    "h2d_bytes_per_step": 2 * ROWS * HIDDEN * ELEM,
+                    "d2h_bytes_per_step": ROWS * HIDDEN * ELEM,
+                    "steps": args.steps,
+                    "path": "C++ backend through the reference's public interface, every step: "
+                            "TensorView::copy_from_host(x), copy_from_host(residual), "
+                            "b200::add_rmsnorm, wait, copy_to_host(out); pinned host buffers in the "
+                            "logical row-major layout; host wall clock, max over ranks"},
             "gpu_launches": args.steps,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES_PER_PLANE * PLANES,
-                         "peak_source": f"of {peak_kind}", "kernel": "rmsnorm_kernel<2,16,true>",
-                         "algorithmic_bytes_per_launch": ALGORITHMIC_BYTES},
+                         "frac": achieved / peak, "traffic": traffic,
+                         "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one "
+                                           "launch on a [32768,8192] shard, scaled by rows "
+                                           "(profiles/add_rmsnorm_bf16_long_rows.md)",
+                         "peak_source": f"of {peak_kind}", "kernel": kernel_name,
+                         "algorithmic_bytes_per_launch": step_bytes(rows), "per": "GPU (rank 0's shard)"},
+            "sumsq_across_ranks": sumsq_info,
         }
-        result["config"]["pct_of_8TBps"] = 100.0 * achieved / 8000.0
         if table is not None:
             result["ops"] = table
-        if sumsq_info is not None:
-            result["sumsq_across_ranks"] = sumsq_info
-    queue.close()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
     return result
+
+
+def ops_table_all(ordinal: int) -> dict:
+    """Per-operation supporting numbers: kernel-level GB/s through the Python mirror (several
+    launches per event pair, so that its submission time hides behind the queue), and
+    launch-bound sequences through the C++ backend."""
+    from iom_b200.device import DeviceMemoryConfig, make_b200_device
+
+    device = make_b200_device(ordinal, DeviceMemoryConfig(5 << 30))
+    queue = device.create_ops()
+    table = ops_table(device, queue)
+    queue.close()
+    del queue, device
+    try:
+        table.update(backend_sequences(ordinal))
+    except Exception as error:      # the table is supporting material: report, do not fail the line
+        table["cpp_backend_sequences"] = {"error": str(error)}
+    return table
+
+
+def backend_sequences(ordinal: int) -> dict:
+    """Launch-bound work issued from C++ through the reference's facade on the B200 backend:
+    the small sizes of the elementwise sweep (device time per launch and host time per
+    submission), and one decode step's tensor operations (TinyLlama geometry, 64 sequences,
+    22 layers) issued one by one and replayed from a recording."""
+    import torch
+
+    from iom_b200 import backend_driver as bd
+    from iom_b200.tensor import DataType
+
+    results = {}
+    backend = bd.Backend(ordinal, 2 << 30)
+    n = 2048
+    for exponent in range(16, 23):
+        m = (1 << exponent) // n
+        a, b, o = (backend.tensor((m, n), DataType.F32) for _ in range(3))
+        views = [backend.view(t) for t in (a, b, o)]
+        timing = backend.run([bd.Backend.op(bd.MUL, views)], passes=200, warmup=20)
+        nbytes = 3 * (1 << exponent) * 4
+        results[f"mul_f32_full_2^{exponent}_cpp"] = {
+            "us": timing.device_ms * 1e3 / 200, "GB/s": nbytes / (timing.device_ms / 200) / 1e6,
+            "host_us_per_submission": timing.submit_seconds * 1e6 / 200,
+            "note": "200 launches back to back from C++; sizes below the 126 MB L2 run out of cache"}
+    batch, hidden, inter, layers, heads = 64, 2048, 5632, 22, 4
+    table = backend.tensor((32000, hidden), DataType.BF16)
+    ids = backend.tensor((1, batch), DataType.U32)
+    backend.storage(ids).zero_()
+    h, normed, attn, total = (backend.tensor((batch, hidden), DataType.BF16) for _ in range(4))
+    w = backend.tensor((1, hidden), DataType.BF16)
+    gate, up, prod = (backend.tensor((batch, inter), DataType.BF16) for _ in range(3))
+    k, v = (backend.tensor((batch, heads, 1, 64), DataType.BF16) for _ in range(2))
+    k_cache, v_cache = (backend.tensor((batch, heads, 512, 64), DataType.BF16) for _ in range(2))
+    for t in (table, h, attn, w, gate, up, k, v):
+        storage = backend.storage(t)
+        storage.view(torch.bfloat16).copy_(torch.randn(storage.numel() // 2, device=storage.device))
+    status_ws = backend.workspace(32)
+    control = backend.workspace(32 + 4 * batch)
+    backend.workspace_memory(control, 32 + 4 * batch).view(torch.int32)[8:].copy_(
+        torch.randint(0, 511, (batch,), dtype=torch.int32))
+    V = {name: backend.view(t) for name, t in (
+        ("table", table), ("ids", ids), ("h", h), ("normed", normed), ("attn", attn), ("total", total),
+        ("w", w), ("gate", gate), ("up", up), ("prod", prod), ("k", k), ("v", v),
+        ("k_cache", k_cache), ("v_cache", v_cache))}
+    op = bd.Backend.op
+    program = [op(bd.EMBEDDING, [V["table"], V["ids"], V["h"]], workspace=status_ws)]
+    for _ in range(layers):
+        program += [
+            op(bd.RMSNORM, [V["h"], V["w"], V["normed"]], eps=1e-5),
+            op(bd.CACHE_APPEND_BATCHED, [V["k"], V["k_cache"]], workspace=control),
+            op(bd.CACHE_APPEND_BATCHED, [V["v"], V["v_cache"]], workspace=control),
+            op(bd.ADD_RMSNORM, [V["h"], V["attn"], V["w"], V["total"], V["normed"]], eps=1e-5),
+            op(bd.SILU_MUL, [V["gate"], V["up"], V["prod"]]),
+            op(bd.ADD, [V["total"], V["attn"], V["h"]]),
+        ]
+    program.append(op(bd.RMSNORM, [V["h"], V["w"], V["normed"]], eps=1e-5))
+    launches = sum(1 for record in program if record.opcode != bd.WAIT)
+    for name, mode in (("decode_step_eager_cpp", bd.EAGER), ("decode_step_recorded_cpp", bd.RECORDED)):
+        plain = [record for record in program if record.opcode != bd.WAIT] if mode == bd.RECORDED else program
+        timing = backend.run(plain, passes=50, warmup=5, mode=mode)
+        results[name] = {
+            "us": timing.device_ms * 1e3 / 50,
+            "host_us_per_step": timing.host_seconds * 1e6 / 50,
+            "host_us_per_submission": timing.submit_seconds * 1e6 / max(1, timing.operations),
+            "launches": launches,
+            "note": f"{launches} facade operations per step issued from C++"
+                    + (", recorded once and replayed as one submission" if mode == bd.RECORDED else "")}
+    backend.close()
+    return results
 
 
 # ---- per-operation table (supporting numbers beside the headline) ------------------
@@ -424,13 +492,33 @@ def ops_table(device, queue, only=None, iters: int = 10) -> dict:
 
     results = {}
 
+    peak, peak_kind = measured_peak()
+
     def record(name, nbytes, launch, shape, inner=1):
         if only is not None and name != only:
             return
         ms = timed(launch, inner)
         results[name] = {"GB/s": nbytes / ms / 1e6, "us": ms * 1e3, "bytes": nbytes,
-                         "pct_of_8TBps": nbytes / ms / 1e6 / 80.0, "shape": shape}
+                         "pct_of_8TBps": nbytes / ms / 1e6 / 80.0,
+                         f"frac_of_{peak_kind}_peak": nbytes / ms / 1e6 / peak, "shape": shape,
+                         "timing": "one launch per CUDA-event pair, median" if inner == 1 else
+                                   f"{inner} launches back to back per CUDA-event pair, median per launch"}
 
+    if only is None or only == "add_f32_row_config1":
+        # Configuration 1 as stated: F32 A[4096,2048] + bias[2048] -> C. One set is 64 MiB,
+        # half the L2, so eight sets of (A, C) rotate: every launch streams from HBM.
+        bias = tensor((1, 2048), DataType.F32)
+        sets = [(tensor((4096, 2048), DataType.F32), tensor((4096, 2048), DataType.F32))
+                for _ in range(8)]
+        turn = [0]
+
+        def config1():
+            a_, c_ = sets[turn[0] % len(sets)]
+            turn[0] += 1
+            return ok(queue.add(a_.view(), bias.view(), c_.view()))
+        record("add_f32_row_config1", (2 * 4096 * 2048 + 2048) * 4, config1,
+               "[4096,2048] + [1,2048], eight rotating buffer sets", inner=8)
+        release()
     M, N = 131072, 2048          # 2^28 elements: far beyond L2
     E = M * N
     for dtype, name, b in ((DataType.BF16, "bf16", 2), (DataType.F32, "f32", 4),
@@ -711,28 +799,35 @@ def elementwise_sweep(device, queue, iters: int = 5) -> dict:
 
 # ---- CPU side: the reference's own CPU backend (or the oracle port) ---------------
 
-def _cpu_arm(threads: int, repeats: int, warmup: int) -> dict:
-    """Times add(x, r, s) followed by rmsnorm(s, w, n) — the reference's contract
-    path for this step — on `threads` independent row shards, one reference
-    device + queue (one worker thread) per shard. Bytes are counted like the GPU
-    arm's (fused-equivalent algorithmic bytes for the rows processed) so the two
-    GB/s figures describe the same amount of work."""
-    import ctypes
-
-    import numpy as np
+def _reference_kind():
+    """'avx512' when that build of the reference shim exists and this host can run it,
+    'portable' when only that one exists, None when no shim was built."""
     import support
-    from iom_b200.tensor import DataType
 
-    kind = None
     for candidate in ("avx512", "portable"):
         if support.REF_LIBS[candidate].exists():
             probe = support.Reference(candidate)
             active = probe.lib.iomref_avx512_bf16_active() == 1
             probe.close()
             if candidate == "portable" or active:
-                kind = candidate
-                break
-    rng = np.random.default_rng(7)
+                return candidate
+    return None
+
+
+def _cpu_arm(threads: int, repeats: int, warmup: int, force_kind=None) -> dict:
+    """Times add(x, r, s) followed by rmsnorm(s, w, n) — the reference's contract
+    path for this step — on `threads` independent row shards of the benchmark's tensor
+    ([rows, 8192] BF16 each), one reference device + queue (one worker thread) per shard.
+    Bytes are counted like the GPU arm's (fused-equivalent algorithmic bytes for the rows
+    processed) so the two GB/s figures describe the same amount of work."""
+    import ctypes
+
+    import numpy as np
+    import support
+    from iom_b200.tensor import DataType
+
+    kind = force_kind or _reference_kind()
+    rng = np.random.default_rng(2)
 
     def payloads(rows):
         x = support.f32_to_bf16_bits(rng.standard_normal((rows, HIDDEN), dtype=np.float32))
@@ -743,7 +838,7 @@ def _cpu_arm(threads: int, repeats: int, warmup: int) -> dict:
 
     if kind is None:
         # Oracle port: scalar plain-C restatement, one core.
-        rows, threads = 128, 1
+        rows, threads = 32, 1
         x, r, w = payloads(rows)
         hosts = {}
         for name, data in (("x", x), ("r", r), ("w", w), ("s", x), ("n", x)):
@@ -759,7 +854,9 @@ def _cpu_arm(threads: int, repeats: int, warmup: int) -> dict:
                                     support.abi(hosts["n"].view()), EPS, 1) == 0
         label, sample_kind = "oracle port (plain C, scalar codec)", "port"
     else:
-        rows = 4096 if kind == "avx512" else 128
+        # The AVX-512 BF16 build runs ~1 GB/s per core: 1024 rows (67 MB touched) per shard
+        # and step; the portable build's bit-serial codec needs a 32-row slice.
+        rows = 1024 if kind == "avx512" else 32
         shards = []
         for _ in range(threads):
             ref = support.Reference(kind)
@@ -792,13 +889,120 @@ def _cpu_arm(threads: int, repeats: int, warmup: int) -> dict:
         once()
         samples.append(time.perf_counter() - t0)
     seconds = statistics.median(samples)
-    elements = threads * rows * HIDDEN
-    bytes_per_step = 4 * elements * ELEM + threads * HIDDEN * ELEM
+    total_rows = threads * rows
+    bytes_per_step = 4 * total_rows * HIDDEN * ELEM + threads * HIDDEN * ELEM
     return {"value": bytes_per_step / seconds / 1e9, "unit": "GB/s", "cores": threads,
             "kind": sample_kind,
-            "sample": f"{label}: add + rmsnorm on {threads} shard(s) of [{rows},{HIDDEN}] BF16, "
-                      f"median of {repeats} runs, {seconds * 1e3:.1f} ms per run",
+            "sample": f"{label}: add then rmsnorm on {threads} row shard(s) of [{rows},{HIDDEN}] BF16 "
+                      f"({total_rows} of the tensor's {ROWS} rows per step; rows are independent, so the "
+                      f"rate extrapolates), median of {repeats} runs, {seconds * 1e3:.1f} ms per run",
+            "rows_per_step": total_rows,
             "ms_per_step": seconds * 1e3}
+
+
+def cpu_per_op(threads: int) -> dict:
+    """The five named operations on the reference CPU backend: steady clock around
+    operation + wait, one warm-up and five samples, median (the method of
+    test/cpu/test_cpu_bench.cpp:63-83), on `threads` shards in parallel queues and on one."""
+    import ctypes
+
+    import numpy as np
+    import support
+    from iom_b200.tensor import DataType
+
+    kind = _reference_kind()
+    if kind is None:
+        return {"unavailable": "the reference CPU backend shim is not built"}
+    rows = 1024 if kind == "avx512" else 16
+    rng = np.random.default_rng(3)
+    results = {"build": kind, "rows_per_shard": rows}
+
+    def measure(make_shard, nbytes_per_shard, name, count):
+        shards = [make_shard() for _ in range(count)]
+
+        def once():
+            pending = [(ref, launch()) for ref, launch in shards]
+            for ref, token in pending:
+                assert token > 0, ref.error()
+                assert ref.lib.iomref_wait(ref.queue, token) == 0, ref.error()
+        once()
+        samples = []
+        for _ in range(5):
+            t0 = time.perf_counter()
+            once()
+            samples.append(time.perf_counter() - t0)
+        seconds = statistics.median(samples)
+        results[f"{name}_{count}core"] = {"GB/s": count * nbytes_per_shard / seconds / 1e9,
+                                          "ms": seconds * 1e3, "cores": count}
+        for ref, _ in shards:
+            ref.close()
+
+    def bf16(shape):
+        return support.f32_to_bf16_bits(rng.standard_normal(shape, dtype=np.float32))
+
+    def binary_shard(op, dtype, rhs_shape):
+        def make():
+            ref = support.Reference(kind)
+            shape = (rows, 2048)
+            if dtype == DataType.BF16:
+                a, b = bf16(shape), bf16(rhs_shape)
+            elif dtype == DataType.F32:
+                a = rng.uniform(-1, 1, shape).astype(np.float32)
+                b = rng.uniform(-1, 1, rhs_shape).astype(np.float32)
+            else:
+                a = rng.integers(-(1 << 20), 1 << 20, shape).astype(np.int32)
+                b = rng.integers(-(1 << 20), 1 << 20, rhs_shape).astype(np.int32)
+            ta, tb, to = ref.tensor(shape, dtype), ref.tensor(rhs_shape, dtype), ref.tensor(shape, dtype)
+            ta.view().from_host(a)
+            tb.view().from_host(b)
+            va, vb, vo = ta.view(), tb.view(), to.view()
+            return ref, lambda: ref.lib.iomref_binary(ref.queue, op, va.handle, vb.handle, vo.handle)
+        return make
+
+    elem = {DataType.BF16: 2, DataType.F32: 4, DataType.I32: 4}
+    for count in sorted({1, threads}):
+        measure(binary_shard(0, DataType.F32, (1, 2048)), (2 * rows * 2048 + 2048) * 4,
+                "add_f32_row_broadcast", count)
+        measure(binary_shard(1, DataType.F32, (rows, 2048)), 3 * rows * 2048 * 4, "mul_f32_full", count)
+        measure(binary_shard(0, DataType.BF16, (rows, 2048)), 3 * rows * 2048 * 2, "add_bf16_full", count)
+        measure(binary_shard(0, DataType.I32, (rows, 2048)), 3 * rows * 2048 * 4, "add_i32_full", count)
+
+        def rmsnorm_shard():
+            ref = support.Reference(kind)
+            tx, tw, to = (ref.tensor((rows, HIDDEN), DataType.BF16), ref.tensor((1, HIDDEN), DataType.BF16),
+                          ref.tensor((rows, HIDDEN), DataType.BF16))
+            tx.view().from_host(bf16((rows, HIDDEN)))
+            tw.view().from_host(bf16((1, HIDDEN)))
+            vx, vw, vo = tx.view(), tw.view(), to.view()
+            return ref, lambda: ref.lib.iomref_rmsnorm(ref.queue, vx.handle, vw.handle, vo.handle,
+                                                       ctypes.c_float(EPS))
+        measure(rmsnorm_shard, (2 * rows * HIDDEN + HIDDEN) * 2, "rmsnorm_bf16_8192", count)
+
+        def copy_shard():
+            ref = support.Reference(kind)
+            ts, td = ref.tensor((rows, 2048), DataType.BF16), ref.tensor((rows, 2048), DataType.BF16)
+            ts.view().from_host(bf16((rows, 2048)))
+            vs, vd = ts.view(), td.view()
+            return ref, lambda: ref.lib.iomref_copy(ref.queue, vs.handle, vd.handle)
+        measure(copy_shard, 2 * rows * 2048 * 2, "copy_bf16", count)
+
+        def embedding_shard():
+            ref = support.Reference(kind)
+            table, ids, out = (ref.tensor((32000, 2048), DataType.BF16), ref.tensor((1, 64), DataType.U32),
+                               ref.tensor((64, 2048), DataType.BF16))
+            ids.view().from_host(rng.integers(0, 32000, (1, 64)).astype(np.uint32))
+            vt, vi, vo = table.view(), ids.view(), out.view()
+            return ref, lambda: ref.lib.iomref_embedding(ref.queue, vt.handle, vi.handle, vo.handle)
+        measure(embedding_shard, 2 * 64 * 2048 * 2 + 64 * 4, "embedding_decode", count)
+
+        def append_shard():
+            ref = support.Reference(kind)
+            k, cache = ref.tensor((4, 1, 64), DataType.BF16), ref.tensor((4, 2048, 64), DataType.BF16)
+            k.view().from_host(bf16((4, 1, 64)))
+            vk, vc = k.view(), cache.view()
+            return ref, lambda: ref.lib.iomref_cache_append(ref.queue, vk.handle, vc.handle, 1000)
+        measure(append_shard, 2 * 4 * 64 * 2, "cache_append_decode_one_sequence", count)
+    return results
 
 
 def run_reference(args) -> dict | None:
@@ -818,11 +1022,12 @@ def run_reference(args) -> dict | None:
         "warmup": args.warmup,
         "ms_per_step": cpu["ms_per_step"],
         "higher_is_better": True,
-        "scaling": "weak",
+        "scaling": "strong",
         "vs_baseline": None,
         "dtype": "f32 accumulate, bf16 storage",
-        "data": "synthetic (seeded normal, the TinyLlama prefill configuration's distributions)",
-        "config": {"workload": WORKLOAD, "sample": cpu["sample"]},
+        "data": "synthetic (seeded normal, the large sharded configuration's distributions)",
+        "config": {"workload": workload(world), "sample": cpu["sample"],
+                   "rows_per_step": cpu["rows_per_step"]},
         "cpu_baseline": {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")},
         "e2e": {"value": cpu["value"], "unit": "GB/s", "h2d_bytes_per_step": 0,
                 "d2h_bytes_per_step": 0},
@@ -846,11 +1051,11 @@ def main() -> None:
                         help="run the elementwise size sweep and print its table")
     parser.add_argument("--no-e2e", action="store_true",
                         help="skip the host-buffer leg (used for profiler captures)")
-    parser.add_argument("--planes", type=int, default=PLANES,
-                        help="planes of [8192,2048] per step; smaller values give the "
-                             "small case profiler captures use")
+    parser.add_argument("--rows", type=int, default=ROWS,
+                        help="rows of the [rows, 8192] tensor; smaller values give the small "
+                             "case profiler captures use")
     args = parser.parse_args()
-    configure(args.planes)
+    configure(args.rows)
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.sweep:
         from iom_b200.device import DeviceMemoryConfig, make_b200_device
@@ -878,6 +1083,12 @@ def main() -> None:
         if result is not None and result["n_gpus"] == 1 and not args.no_cpu_baseline:
             cpu = _cpu_arm(1, repeats=3, warmup=1)
             result["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
+            if not args.no_ops:
+                threads = max(1, min(os.cpu_count() or 1, 16))
+                try:
+                    result["cpu_baseline"]["per_op"] = cpu_per_op(threads)
+                except Exception as error:
+                    result["cpu_baseline"]["per_op"] = {"error": str(error)}
     restore = getattr(args, "_restore_stdout", None)
     if restore is not None:
         sys.stdout.flush()

@@ -98,6 +98,11 @@ typedef enum iomb_rms_order {
 
 const char* iomb_last_error(void);
 
+/* The kernel instance the calling thread's most recent iomb_rmsnorm / iomb_add_rmsnorm
+ * launched, with the template arguments its dispatcher chose (for benchmark records);
+ * empty before the first such call. No counterpart in the reference. */
+const char* iomb_last_launch(void);
+
 /* Library/ABI version, bumped when a struct or signature changes. */
 uint32_t iomb_abi_version(void);
 

@@ -63,7 +63,9 @@ oid cast(DeviceOps& queue, const TensorView& source, TensorView& destination);
 // batched_control_bytes(dims[0]) bytes of this device: its first u32 is the status word
 // (reset to 0 by the call, 1 when some offset overruns its cache, that sequence being
 // skipped), the u32 row offsets start at byte 32. The caller fills the offsets (device
-// memory) before the call and reads the status after the token completes.
+// memory) before the call and reads the status after the token completes. The range is
+// registered like an operand, not leased exclusively: several appends in flight on one
+// queue (K and V of every layer of a step) may name the same offsets.
 oid cache_append_batched(DeviceOps& queue, const TensorView& source, TensorView& destination,
                          RawWorkspaceView control);
 [[nodiscard]] std::size_t batched_control_bytes(std::size_t sequences);

@@ -49,6 +49,7 @@ _VIEW = ctypes.POINTER(IombView)
 _U64P = ctypes.POINTER(ctypes.c_uint64)
 PROTOTYPES = {
     "iomb_last_error": (ctypes.c_char_p, []),
+    "iomb_last_launch": (ctypes.c_char_p, []),
     "iomb_abi_version": (ctypes.c_uint32, []),
     "iomb_dtype_bits": (ctypes.c_uint32, [ctypes.c_uint32]),
     "iomb_tiled_storage_nbytes": (ctypes.c_int, [_U64P, ctypes.c_uint32, ctypes.c_uint32, _U64P]),

@@ -209,6 +209,9 @@ public:
 
     ~B200Device() override {
         if (transfer_stream_ != nullptr) (void)cudaStreamDestroy(transfer_stream_);
+        // Parked storage goes back to the allocator while the allocator still exists
+        // (src/cuda/device.cpp:106-116).
+        registry_state_.quarantine.drain();
         allocator_.reset();
         if (rotary_ != nullptr) (void)cudaFree(rotary_);
         if (arena_ != nullptr) (void)cudaFree(arena_);
@@ -315,7 +318,24 @@ B200Workspace::B200Workspace(B200Device& device, void* address, std::size_t byte
         : RawWorkspace(device, bytes), device_(device), address_(address) {}
 
 B200Workspace::~B200Workspace() {
-    if (address_ != nullptr) device_.release(address_);
+    if (address_ == nullptr) return;
+    // A range that unproven work may still use is parked like tensor storage.
+    detail::RegistryState& state = device_.registry_state();
+    const std::size_t bytes = byte_size();
+    detail::release_or_quarantine(
+            state.registry, address_,
+            [this, bytes, &state]() noexcept {
+                try {
+                    state.quarantine.emplace<detail::AllocatorCleanupAction>(
+                            device_.data_allocator(), address_, bytes);
+                } catch (...) {
+                }
+                address_ = nullptr;
+            },
+            [this]() noexcept {
+                device_.release(address_);
+                address_ = nullptr;
+            });
 }
 
 // Checks the {staging, 32} host-transfer workspace the contract makes mandatory
@@ -435,7 +455,7 @@ std::unique_ptr<Tensor> B200Device::create_tensor(const TensorSpec& spec) {
 
 // ---- operation queue ----------------------------------------------------------
 
-constexpr std::size_t kMaxOwners = 6;
+constexpr std::size_t kMaxOwners = 8;
 constexpr std::size_t kMaxLeases = 2;
 constexpr std::uint32_t kCaptureCells = 64;   // embedding status cells recordings may use
 
@@ -445,6 +465,12 @@ struct OwnerList {
     void add(const TensorView& view) {
         owners[count++] = detail::BinaryOwnerRegistration{
                 view.owner_identity(), const_cast<void*>(view.native_handle())};
+    }
+    // A workspace range several operations in flight may read at once (control words):
+    // registered like a tensor owner rather than leased exclusively.
+    void add(const RawWorkspaceView& workspace) {
+        owners[count++] = detail::BinaryOwnerRegistration{
+                workspace.owner_identity(), detail::WorkspaceValidation::address(workspace)};
     }
 };
 
@@ -516,6 +542,7 @@ class B200Queue final : public DeviceOps {
         std::uint32_t event_slot = 0;
         Proof proof = Proof::event;
         bool has_status = false;            // embedding: the slot's pinned status cell
+        bool launch_failed = false;         // the native step threw: slot_failures_[event_slot]
         std::uint32_t capture_first = 0;    // replay: status cells of the recording
         std::uint32_t capture_count = 0;
         EntryList entries;
@@ -539,6 +566,7 @@ public:
                 check_cuda("cudaEventCreate",
                            cudaEventCreateWithFlags(&event, cudaEventDisableTiming));
             }
+            slot_failures_.resize(slots);
             free_slots_.reserve(slots);
             for (std::size_t i = slots; i-- > 0;) free_slots_.push_back(static_cast<std::uint32_t>(i));
             ring_.resize(slots + 1);
@@ -578,7 +606,8 @@ public:
     // leased in the prepare step, released by the retirement, rolled back on failure.
     template <typename Launch>
     oid extension(std::initializer_list<const TensorView*> views,
-                  std::initializer_list<RawWorkspaceView> workspaces, Launch launch) noexcept {
+                  std::initializer_list<RawWorkspaceView> workspaces, Launch launch,
+                  std::initializer_list<RawWorkspaceView> shared = {}) noexcept {
         try {
             validate_views(queue_device(), views);
             if (workspaces.size() > kMaxLeases) throw std::invalid_argument("too many workspaces");
@@ -601,6 +630,12 @@ public:
                         queue_device(), workspace, workspace.empty() ? 1 : workspace.byte_size(), 32,
                         std::span<const TensorView>(operands.data(), operands.size()));
                 prepared->workspaces.push_back(workspace);
+            }
+            for (const RawWorkspaceView& workspace : shared) {
+                (void)detail::WorkspaceValidation::validated(
+                        queue_device(), workspace, workspace.empty() ? 1 : workspace.byte_size(), 32,
+                        std::span<const TensorView>(operands.data(), operands.size()));
+                prepared->owners.add(workspace);
             }
             check_pre_acceptance_faults();
             detail::RegistryState& state = device_->registry_state();
@@ -637,18 +672,18 @@ public:
                         }
                     },
                     [this, prepared, launch](std::uint64_t sequence) {
-                        // A failed launch leaves nothing in flight: the facade runs the
-                        // rollback and reports the failure.
                         const std::uint32_t slot = acquire_event_slot();
+                        Retirement record;
                         try {
                             device_->activate();
                             inject_launch_fault();
                             check_status(launch(stream_));
                         } catch (...) {
-                            release_event_slot(slot);
-                            throw;
+                            // The operation is accepted: its failure is retained and
+                            // rethrown by every wait (src/shared/gpu_queue_operations.inl:1030-1056).
+                            slot_failures_[slot] = std::current_exception();
+                            record.launch_failed = true;
                         }
-                        Retirement record;
                         record.entries = prepared->entries;
                         record.leases = prepared->leases;
                         record.lease_count = prepared->lease_count;
@@ -699,9 +734,11 @@ public:
         }
         const iomb_view vs = to_view(source), vd = to_view(destination);
         auto* words = static_cast<std::uint32_t*>(detail::WorkspaceValidation::address(control));
-        return extension({&source, &destination}, {control}, [vs, vd, words](cudaStream_t stream) {
+        // The control range is registered, not leased: the K and V appends of every layer
+        // of a step share one range of offsets, and the queue runs them in order.
+        return extension({&source, &destination}, {}, [vs, vd, words](cudaStream_t stream) {
             return iomb_cache_append_batched(&vs, &vd, words + 8, words, stream);
-        });
+        }, {control});
     }
 
     oid sumsq(const TensorView& x, RawWorkspaceView workspace) noexcept {
@@ -771,6 +808,7 @@ public:
             if (capturing_) throw std::logic_error("a recording cannot be replayed while recording");
             return submit([this, recorded](std::uint64_t sequence) {
                 const std::uint32_t slot = acquire_event_slot();
+                Retirement record;
                 try {
                     device_->activate();
                     inject_launch_fault();
@@ -779,10 +817,9 @@ public:
                     }
                     check_cuda("cudaGraphLaunch", cudaGraphLaunch(recorded->exec, stream_));
                 } catch (...) {
-                    release_event_slot(slot);
-                    throw;
+                    slot_failures_[slot] = std::current_exception();
+                    record.launch_failed = true;
                 }
-                Retirement record;
                 record.capture_first = recorded->first_cell;
                 record.capture_count = recorded->cell_count;
                 retire(sequence, slot, record);
@@ -1034,8 +1071,10 @@ private:
         free_slots_.push_back(slot);      // capacity reserved at construction
     }
 
-    // Launches through `launch`, then retires. A launch that fails has put nothing in
-    // flight: the exception reaches the facade, whose rollback drops the registrations.
+    // Launches through `launch`, then retires. The operation has been accepted by the time
+    // this runs, so a failing native step is a retained failure: the token completes with
+    // the exception and every wait rethrows it (src/shared/gpu_queue_operations.inl:1030-1056).
+    // Only the lack of a free event leaves the node parked.
     template <typename Launch>
     void launch_and_retire(std::uint64_t sequence, const EntryList& entries,
                            detail::WorkspaceLease lease, Launch&& launch,
@@ -1068,8 +1107,9 @@ private:
                 record.has_status = !capturing_;
             }
         } catch (...) {
-            release_event_slot(slot);
-            throw;
+            slot_failures_[slot] = std::current_exception();
+            record.launch_failed = true;
+            record.has_status = false;
         }
         record.entries = entries;
         if (lease.entry_id != 0) {
@@ -1085,8 +1125,10 @@ private:
         record.sequence = sequence;
         record.event_slot = slot;
         if (capturing_) {
+            std::exception_ptr failure;
+            if (record.launch_failed) failure = std::move(slot_failures_[slot]);
             release_event_slot(slot);
-            finish(record, true, nullptr);
+            finish(record, true, std::move(failure));
             return;
         }
         bool recorded = false;
@@ -1159,7 +1201,12 @@ private:
                 failure = std::make_exception_ptr(std::runtime_error(
                         "B200 operation: completion could not be proven"));
             }
-            if (proven) {
+            if (record.launch_failed) {
+                std::exception_ptr retained = std::move(slot_failures_[record.event_slot]);
+                slot_failures_[record.event_slot] = nullptr;
+                if (failure == nullptr) failure = std::move(retained);
+            }
+            if (proven && failure == nullptr) {
                 bool invalid_id = record.has_status && status_cells_[record.event_slot] != 0;
                 for (std::uint32_t i = 0; i < record.capture_count; ++i) {
                     if (capture_cells_[record.capture_first + i] != 0) invalid_id = true;
@@ -1198,6 +1245,7 @@ private:
     cudaStream_t stream_ = nullptr;
     std::vector<cudaEvent_t> events_;
     std::vector<std::uint32_t> free_slots_;
+    std::vector<std::exception_ptr> slot_failures_;   // one per event, set before publication
     std::mutex slot_mutex_;
     std::uint32_t* status_cells_ = nullptr;
     std::uint32_t* capture_cells_ = nullptr;

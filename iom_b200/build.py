@@ -81,7 +81,72 @@ def build(force: bool = False, verbose: bool = False, defines: tuple = (),
     return library
 
 
+# ---- the C++ backend (needs the reference checkout: it subclasses the reference's classes) ----
+
+BACKEND_LIBRARY = PACKAGE_DIR / "libiom_b200_backend.so"
+BACKEND_ARCHIVE = PACKAGE_DIR / "libiom_b200_backend.a"
+BACKEND_SOURCES = ["b200_backend.cpp", "b200_capi.cpp"]
+# The reference's backend-neutral sources a backend links with (its "common op layer"),
+# compiled unmodified from where they lie; flags follow the reference's CMake configuration
+# (C++20 ISO mode, -O2, no fast-math: CMakeLists.txt:60-63).
+REFERENCE_COMMON = ["device_ops", "device_ops_copy", "device_ops_binary", "device_ops_cache_append",
+                    "device_ops_rmsnorm", "device_ops_embedding", "device_ops_neural", "workspace",
+                    "tensor", "tensor_view", "alloc"]
+
+
+def build_backend(reference: Path, force: bool = False) -> Path:
+    """Builds libiom_b200_backend.a (the backend's own objects: what a maintainer of the
+    reference adds to its build) and libiom_b200_backend.so (those objects, the reference's
+    common sources and the C driver interface of include/iom_b200_backend_c.h, linked
+    against libiom_b200.so)."""
+    reference = Path(reference)
+    if not (reference / "include" / "iom" / "iom.hpp").exists():
+        raise RuntimeError(f"{reference} is not a checkout of the reference")
+    build(force=False)
+    backend_dir = PACKAGE_DIR / "backend"
+    inputs = [backend_dir / name for name in BACKEND_SOURCES] + [
+        PACKAGE_DIR.parent / "include" / name
+        for name in ("iom_b200.h", "iom_b200_backend.hpp", "iom_b200_backend_c.h")]
+    if (not force and BACKEND_LIBRARY.exists()
+            and all(path.stat().st_mtime <= BACKEND_LIBRARY.stat().st_mtime for path in inputs)
+            and LIBRARY.stat().st_mtime <= BACKEND_LIBRARY.stat().st_mtime):
+        return BACKEND_LIBRARY
+    cuda_home = Path(os.environ.get("CUDA_HOME", "/usr/local/cuda"))
+    out_dir = PACKAGE_DIR / "build" / "backend"
+    out_dir.mkdir(parents=True, exist_ok=True)
+    cxx = os.environ.get("CXX", "g++")
+    flags = ["-std=c++20", "-O2", "-fPIC", f"-I{reference / 'include'}", f"-I{reference / 'src'}",
+             f"-I{PACKAGE_DIR.parent / 'include'}", f"-I{cuda_home / 'include'}"]
+    jobs = []
+    own, common = [], []
+    for name in BACKEND_SOURCES:
+        obj = out_dir / (Path(name).stem + ".o")
+        own.append(obj)
+        jobs.append((name, subprocess.Popen([cxx, *flags, "-c", str(backend_dir / name), "-o", str(obj)])))
+    for name in REFERENCE_COMMON:
+        obj = out_dir / f"reference_{name}.o"
+        common.append(obj)
+        jobs.append((name, subprocess.Popen([cxx, *flags, "-c", str(reference / "src" / f"{name}.cpp"),
+                                             "-o", str(obj)])))
+    for name, proc in jobs:
+        if proc.wait() != 0:
+            raise RuntimeError(f"compiling {name} failed")
+    if BACKEND_ARCHIVE.exists():
+        BACKEND_ARCHIVE.unlink()
+    subprocess.run(["ar", "rcs", str(BACKEND_ARCHIVE), str(own[0])], check=True)
+    subprocess.run([cxx, "-shared", "-o", str(BACKEND_LIBRARY), *map(str, own), *map(str, common),
+                    f"-L{PACKAGE_DIR}", "-liom_b200", "-Wl,-rpath,$ORIGIN",
+                    f"-L{cuda_home / 'lib64'}", "-lcudart_static", "-ldl", "-lrt", "-lpthread"],
+                   check=True)
+    return BACKEND_LIBRARY
+
+
 if __name__ == "__main__":
+    backend = [a.split("=", 1)[1] for a in sys.argv if a.startswith("--backend=")]
+    if backend:
+        # --backend=<reference checkout> builds the C++ backend against that checkout
+        print(build_backend(Path(backend[0]), force="--force" in sys.argv))
+        sys.exit(0)
     variant = [a.split("=", 1)[1] for a in sys.argv if a.startswith("--variant=")]
     if variant:
         # --variant=name:DEFINE=1[,DEFINE2=..] builds libiom_b200_<name>.so with those defines

@@ -24,6 +24,8 @@ constexpr uint32_t kMaxLead = IOMB_MAX_LEADING;
 void set_error(const char* text);
 int fail(int status, const char* text);
 int check_launch(const char* what);
+// Names the kernel instance a dispatcher chose, behind iomb_last_launch().
+void note_launch(const char* text);
 
 // Number of SMs of the current device (cached per device ordinal).
 int sm_count();

@@ -12,7 +12,12 @@ namespace iomb {
 
 namespace {
 thread_local char g_error[256] = "";
+thread_local char g_launch[160] = "";
 }  // namespace
+
+void note_launch(const char* text) {
+    snprintf(g_launch, sizeof g_launch, "%s", text ? text : "");
+}
 
 void set_error(const char* text) {
     snprintf(g_error, sizeof g_error, "%s", text ? text : "");
@@ -279,6 +284,8 @@ Operand make_operand(const iomb_view& view, const ViewFacts& facts,
 extern "C" {
 
 const char* iomb_last_error(void) { return iomb::g_error; }
+
+const char* iomb_last_launch(void) { return iomb::g_launch; }
 
 uint32_t iomb_abi_version(void) { return 2; }
 

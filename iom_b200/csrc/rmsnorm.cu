@@ -22,6 +22,7 @@
 // the reference's per-row fallback (reduction.cpp:109-129) needs no branch.
 #include "rmsnorm.cuh"
 
+#include <stdio.h>
 #include <stdlib.h>
 
 namespace iomb {
@@ -487,6 +488,7 @@ static int rms_dispatch(const iomb_view* x, const iomb_view* residual, const iom
     if (order == IOMB_RMS_LANES16 && fx.tile_cols > 128 && long_rows_enabled()) {
         bool launched = false;
         const int status = launch_rmsnorm_long(p, elem, fused, row_bytes, p.leading.planes * p.tile_rows,
+                                               x->storage_bytes, fused ? residual->storage_bytes : 0,
                                                static_cast<cudaStream_t>(stream), &launched);
         if (launched || status != IOMB_OK) return status;
     }
@@ -563,6 +565,11 @@ static int rms_dispatch(const iomb_view* x, const iomb_view* residual, const iom
     const bool one_shot = fx.cols <= 2048;
     const unsigned grid = one_shot ? grid_one_shot(p.units) : grid_for(p.units, per_sm);
     kernel<<<grid, kRmsThreads, smem_bytes, static_cast<cudaStream_t>(stream)>>>(p);
+    char text[160];
+    snprintf(text, sizeof text, "rmsnorm_kernel<elem %u, rows %u, %s, scale %s> %s order, %u CTAs x %d",
+             elem, g, fused ? "fused" : "unfused", scale_smem ? "in shared memory" : "through L1",
+             order == IOMB_RMS_LANES16 ? "lane" : "sequential", grid, kRmsThreads);
+    note_launch(text);
     return check_launch("rmsnorm launch");
 }
 

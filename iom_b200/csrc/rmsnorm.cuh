@@ -211,6 +211,7 @@ __device__ __forceinline__ unsigned char* rms_unit_base(
 // rmsnorm_long.cu. Returns IOMB_OK after a launch, IOMB_ERR_UNSUPPORTED (without
 // touching the error text) when the request is not one it serves.
 int launch_rmsnorm_long(const RmsParams& base, uint32_t elem, bool fused, uint64_t row_bytes,
-                        uint64_t bands, cudaStream_t stream, bool* launched);
+                        uint64_t bands, uint64_t x_storage_bytes, uint64_t residual_storage_bytes,
+                        cudaStream_t stream, bool* launched);
 
 }  // namespace iomb

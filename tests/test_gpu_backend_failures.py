@@ -46,13 +46,19 @@ def expect_sum(a_payload, b_payload, out):
     assert np.array_equal(got, (a_payload.astype(np.int64) + b_payload).astype(np.int32).reshape(-1))
 
 
-def test_launch_fault_is_a_synchronous_error_and_leaves_the_queue_usable(gpu):
+def test_launch_fault_is_a_retained_failure_and_leaves_the_queue_usable(gpu):
     rng = np.random.default_rng(1)
     a, pa = filled(gpu, (33, 70), DataType.I32, rng)
     b, pb = filled(gpu, (33, 70), DataType.I32, rng)
     out = gpu.tensor((33, 70), DataType.I32)
+    before = out.read()
     gpu.lib.iomref_inject_fault_b200(LAUNCH)
-    assert add(gpu, a, b, out) == -5                     # DeviceError before acceptance
+    token = add(gpu, a, b, out)
+    assert token > 0                                     # accepted: the failure is retained
+    assert gpu.lib.iomref_wait(gpu.queue, token) == 5
+    assert gpu.lib.iomref_wait(gpu.queue, token) == 5    # rethrown on every wait
+    assert np.array_equal(out.read(), before)            # nothing was launched
+    assert gpu.lib.iomref_quarantined_events_b200(gpu.queue) == 0
     token = add(gpu, a, b, out)
     assert token > 0 and gpu.run(token) == 0
     expect_sum(pa, pb, out)
@@ -140,8 +146,9 @@ def test_embedding_status_copy_fault(gpu):
     ids.view().from_host(rng.integers(0, 50, size=(1, 19)).astype(np.uint32))
     out = gpu.tensor((19, 40), DataType.BF16)
     gpu.lib.iomref_inject_fault_b200(STATUS_COPY)
-    assert gpu.lib.iomref_embedding(gpu.queue, table.view().handle, ids.view().handle,
-                                    out.view().handle) == -5
+    token = gpu.lib.iomref_embedding(gpu.queue, table.view().handle, ids.view().handle,
+                                     out.view().handle)
+    assert token > 0 and gpu.lib.iomref_wait(gpu.queue, token) == 5      # retained
     token = gpu.lib.iomref_embedding(gpu.queue, table.view().handle, ids.view().handle,
                                      out.view().handle)
     assert token > 0 and gpu.run(token) == 0
