@@ -27,6 +27,7 @@ from __future__ import annotations
 import argparse
 import json
 import os
+import re
 import statistics
 import subprocess
 import sys
@@ -46,8 +47,8 @@ METRIC = "achieved HBM GB/s, fused residual ADD + RMSNorm (BF16 [262144,8192], r
 # per row, from the ncu capture summarised in profiles/add_rmsnorm_bf16_long_rows.md
 # (taken on a [32768,8192] shard: 2.1 GB per launch, 17 times the L2, so the written
 # lines cannot stay in the cache; traffic is proportional to the rows processed).
-NCU_READ_BYTES_PER_ROW = None
-NCU_WRITE_BYTES_PER_ROW = None
+NCU_READ_BYTES_PER_ROW = 937082112 / 28416       # dram__bytes_read.sum of a 28416-row launch
+NCU_WRITES_LEFT_IN_L2_BYTES = 28416 * 2 * 8192 * 2 - 882120192   # algorithmic - dram__bytes_write.sum
 
 
 def configure(rows: int) -> None:
@@ -286,9 +287,16 @@ def run_ours(args) -> dict:
         per_launch_ms = elapsed_ms / args.steps
         total_bytes = step_bytes(ROWS) + (world - 1) * HIDDEN * ELEM
         achieved = step_bytes(rows) / per_launch_ms / 1e6        # this rank's kernel
+        # DRAM traffic of one step from the ncu capture of a [32768,8192] shard: reads scale
+        # with the rows; so do writes, except for the lines still dirty in L2 when the last
+        # launch ends (bounded by the L2 size, the same at every row count), which the DRAM
+        # counters of a kernel never see.
         traffic = None
         if NCU_READ_BYTES_PER_ROW is not None:
-            traffic = (NCU_READ_BYTES_PER_ROW + NCU_WRITE_BYTES_PER_ROW) * rows
+            traffic = (NCU_READ_BYTES_PER_ROW * rows + 2 * HIDDEN * ELEM * rows
+                       - NCU_WRITES_LEFT_IN_L2_BYTES)
+        found = re.search(r"(\d+) launch\(es\)", kernel_name)
+        launches_per_step = int(found.group(1)) if found else 1
         result = {
             "metric": METRIC,
             "value": total_bytes * args.steps / elapsed_ms / 1e6,
@@ -302,7 +310,7 @@ def run_ours(args) -> dict:
             "vs_baseline": None,
             "dtype": "f32 accumulate, bf16 storage",
             "data": "synthetic (seeded normal, the large sharded configuration's distributions)",
-            "config": {"workload": workload(world), "launches_per_step": 1,
+            "config": {"workload": workload(world), "launches_per_step": launches_per_step,
                        "rows_per_rank": rows, "first_row_of_rank_0": first_row,
                        "algorithmic_bytes_per_step": total_bytes,
                        "l2": f"inputs larger than L2 ({step_bytes(rows) / 1e9:.2f} GB touched per rank "
@@ -310,7 +318,7 @@ def run_ours(args) -> dict:
                        "order": "LANES16 (the reference's AVX-512 BF16 order)",
                        "host_layer": "C++ backend (libiom_b200_backend.so: b200::add_rmsnorm on a device "
                                      "from make_b200_device), launches issued from C++",
-                       "timing": f"{args.steps} launches back to back between one pair of CUDA events "
+                       "timing": f"{args.steps} steps back to back between one pair of CUDA events "
                                  "on the queue's stream, max over ranks",
                        "pct_of_8TBps_per_gpu": 100.0 * achieved / 8000.0},
             "clocks": clocks,
@@ -323,14 +331,17 @@ def run_ours(args) -> dict:
                             "TensorView::copy_from_host(x), copy_from_host(residual), "
                             "b200::add_rmsnorm, wait, copy_to_host(out); pinned host buffers in the "
                             "logical row-major layout; host wall clock, max over ranks"},
-            "gpu_launches": args.steps,
+            "gpu_launches": args.steps * launches_per_step,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": traffic,
                          "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one "
-                                           "launch on a [32768,8192] shard, scaled by rows "
-                                           "(profiles/add_rmsnorm_bf16_long_rows.md)",
+                                           "launch on a [32768,8192] shard, scaled by rows; writes "
+                                           "still dirty in L2 at the end of the step are not DRAM "
+                                           "traffic of the kernel (profiles/add_rmsnorm_bf16_long_rows.md)",
+                         "launches": f"{launches_per_step} launch(es) of this kernel per step; achieved = "
+                                     "algorithmic bytes of a step / duration of a step",
                          "peak_source": f"of {peak_kind}", "kernel": kernel_name,
-                         "algorithmic_bytes_per_launch": step_bytes(rows), "per": "GPU (rank 0's shard)"},
+                         "algorithmic_bytes_per_step": step_bytes(rows), "per": "GPU (rank 0's shard)"},
             "sumsq_across_ranks": sumsq_info,
         }
         if table is not None:
@@ -414,6 +425,9 @@ def backend_sequences(ordinal: int) -> dict:
             op(bd.ADD, [V["total"], V["attn"], V["h"]]),
         ]
     program.append(op(bd.RMSNORM, [V["h"], V["w"], V["normed"]], eps=1e-5))
+    # A decode step ends with the host reading the result: the step's tokens are collected
+    # (which also returns the embedding's status-word lease before the next step).
+    program.append(op(bd.WAIT))
     launches = sum(1 for record in program if record.opcode != bd.WAIT)
     for name, mode in (("decode_step_eager_cpp", bd.EAGER), ("decode_step_recorded_cpp", bd.RECORDED)):
         plain = [record for record in program if record.opcode != bd.WAIT] if mode == bd.RECORDED else program

@@ -103,6 +103,12 @@ const char* iomb_last_error(void);
  * empty before the first such call. No counterpart in the reference. */
 const char* iomb_last_launch(void);
 
+/* The long-row RMSNorm kernels wait for their asynchronous copies a bounded number of
+ * polls. A launch in which a wait gave up (never expected: its results are incomplete)
+ * adds one per CTA to a device counter; this reads it (synchronous, after the launches of
+ * interest have completed). */
+int iomb_rmsnorm_copy_timeouts(unsigned int* count);
+
 /* Library/ABI version, bumped when a struct or signature changes. */
 uint32_t iomb_abi_version(void);
 

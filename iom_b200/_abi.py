@@ -50,6 +50,7 @@ _U64P = ctypes.POINTER(ctypes.c_uint64)
 PROTOTYPES = {
     "iomb_last_error": (ctypes.c_char_p, []),
     "iomb_last_launch": (ctypes.c_char_p, []),
+    "iomb_rmsnorm_copy_timeouts": (ctypes.c_int, [ctypes.POINTER(ctypes.c_uint)]),
     "iomb_abi_version": (ctypes.c_uint32, []),
     "iomb_dtype_bits": (ctypes.c_uint32, [ctypes.c_uint32]),
     "iomb_tiled_storage_nbytes": (ctypes.c_int, [_U64P, ctypes.c_uint32, ctypes.c_uint32, _U64P]),

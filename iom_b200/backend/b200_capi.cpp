@@ -7,6 +7,7 @@
 #include <cuda_runtime_api.h>
 
 #include <chrono>
+#include <deque>
 #include <cstddef>
 #include <exception>
 #include <memory>
@@ -36,6 +37,7 @@ struct ViewBox {
 };
 struct QueueBox {
     std::unique_ptr<iom::DeviceOps> ops;
+    std::size_t credits = 1;      // operations the queue keeps in flight before it parks one
 };
 
 int classify(std::exception_ptr failure) {
@@ -151,7 +153,9 @@ void iomb_backend_device_destroy(void* device) { delete static_cast<DeviceBox*>(
 void* iomb_backend_queue_create(void* device) {
     return guarded([&]() -> void* {
         auto box = std::make_unique<QueueBox>();
-        box->ops = static_cast<DeviceBox*>(device)->device->create_ops();
+        iom::Device& owner = *static_cast<DeviceBox*>(device)->device;
+        box->ops = owner.create_ops();
+        box->credits = owner.queue_config().max_in_flight_per_queue;
         return box.release();
     });
 }
@@ -220,8 +224,11 @@ int iomb_backend_run(void* queue, const iomb_backend_op* operations, uint32_t co
         const cudaStream_t stream = static_cast<cudaStream_t>(iom::b200::native_stream(ops));
         if (stream == nullptr) throw std::invalid_argument("not a queue of the B200 backend");
         using clock = std::chrono::steady_clock;
-        std::vector<iom::oid> tokens;
-        tokens.reserve(count);
+        // Tokens not yet collected, oldest first. Never more than the queue's credits: an
+        // operation beyond them would be accepted but parked and launched by a later
+        // retirement, that is after the event that closes the timed region.
+        const std::size_t credits = static_cast<QueueBox*>(queue)->credits;
+        std::deque<iom::oid> tokens;
         double submit_seconds = 0.0;
         std::uint64_t issued = 0;
         auto wait_all = [&] {
@@ -235,6 +242,10 @@ int iomb_backend_run(void* queue, const iomb_backend_op* operations, uint32_t co
                 if (op.opcode == IOMB_BACKEND_WAIT) {
                     wait_all();
                     continue;
+                }
+                while (tokens.size() >= credits) {
+                    ops.wait(tokens.front());
+                    tokens.pop_front();
                 }
                 const auto before = clock::now();
                 const iom::oid token = issue(ops, op);
@@ -275,6 +286,10 @@ int iomb_backend_run(void* queue, const iomb_backend_op* operations, uint32_t co
                 issued += 1;
             }
             if (token <= 0) throw std::runtime_error("replay was refused with oid " + std::to_string(token));
+            while (tokens.size() >= credits) {
+                ops.wait(tokens.front());
+                tokens.pop_front();
+            }
             tokens.push_back(token);
         };
         for (uint32_t i = 0; i < warmup; ++i) {
@@ -288,9 +303,6 @@ int iomb_backend_run(void* queue, const iomb_backend_op* operations, uint32_t co
         check_cuda("cudaEventRecord", cudaEventRecord(start, stream));
         for (uint32_t i = 0; i < passes; ++i) {
             if (recording) replay(true); else pass(true);
-            // Tokens are kept bounded: a pass's tokens are collected before the next pass
-            // only when the program itself asks (IOMB_BACKEND_WAIT) or at the end.
-            if (tokens.size() > 4096) wait_all();
         }
         check_cuda("cudaEventRecord", cudaEventRecord(stop, stream));
         wait_all();

@@ -395,16 +395,6 @@ int prepare_rmsnorm_kernels() {
     return status;
 }
 
-// IOMB_RMS_LONG=0 in the environment keeps long rows on the staged kernel above (for
-// side-by-side measurements); read once.
-static bool long_rows_enabled() {
-    static const bool enabled = [] {
-        const char* text = getenv("IOMB_RMS_LONG");
-        return text == nullptr || text[0] != '0';
-    }();
-    return enabled;
-}
-
 static int rms_dispatch(const iomb_view* x, const iomb_view* residual, const iomb_view* scale,
                         const iomb_view* sum, const iomb_view* out, float eps, int order,
                         void* stream) {
@@ -485,7 +475,7 @@ static int rms_dispatch(const iomb_view* x, const iomb_view* residual, const iom
     p.eps = eps;
     p.order = static_cast<uint32_t>(order);
     // Rows of more than 2048 values in the lane order take the pipelined kernel.
-    if (order == IOMB_RMS_LANES16 && fx.tile_cols > 128 && long_rows_enabled()) {
+    if (order == IOMB_RMS_LANES16 && fx.tile_cols > 128) {
         bool launched = false;
         const int status = launch_rmsnorm_long(p, elem, fused, row_bytes, p.leading.planes * p.tile_rows,
                                                x->storage_bytes, fused ? residual->storage_bytes : 0,

@@ -24,7 +24,8 @@ struct RmsParams {
     uint32_t tile_cols;
     uint32_t group_rows;        // g
     uint32_t groups_per_band;   // 16 / g
-    uint64_t units;
+    uint64_t units;             // units of this launch
+    uint64_t first_unit;        // first unit of this launch (long rows are launched in parts)
     float eps;
     uint32_t order;
 };

@@ -4,26 +4,30 @@
 // Replaces standard_tiled_rmsnorm_kernel (src/shared/standard_tiled_rmsnorm.inl:437-637)
 // where a 16-row band no longer fits shared memory (8192 BF16 features: 256 KiB).
 // Rows are independent, so the unit of work is G rows of one band (G * 32 or G * 64
-// contiguous bytes of every tile of the band) sized so that three units fit one SM.
-// One persistent CTA of 512 threads per SM keeps a ring of three unit slots in shared
-// memory and, in iteration k, works on three units at once:
+// contiguous bytes of every tile of the band). One persistent CTA of 512 threads per SM
+// keeps a ring of unit slots in shared memory; its warps have one job each and hand units
+// on through mbarriers, so no job waits for another longer than the data demands:
 //
-//   copy     bulk tensor copies bring the next unit into its slot, issued by one thread
-//            at the top of the iteration; an mbarrier per slot counts the bytes. Unfused:
-//            unit k + 1 of x (three slots). Fused: unit k + 2 of x and of the residual
-//            (four slots for x, which becomes the rounded sum in place, two for the
-//            residual; the units are half as tall so that the six slots fit).
-//   add      fused only: the mover warps add unit k + 1 in its slot and store the sum.
-//   chain    the chain warps run the 16 column accumulators of every row of unit k through
+//   copy     one thread issues bulk tensor copies (TMA) of the next unit of x (and of the
+//            residual) into a free slot, and asks for the unit after it to be brought into
+//            L2. An mbarrier per slot counts the bytes that landed.
+//   add      fused only: the mover warps add a landed unit in its slot (x becomes the
+//            rounded sum in place) and store the sum.
+//   chain    a chain warp runs the 16 column accumulators of every row of a unit through
 //            its tiles in order: a thread owns two neighbouring columns of one row (one
-//            32- or 64-bit load per tile, two products, one packed FP32 addition), then the
-//            fixed tree and the row's inverse.
-//   emit     the mover warps normalise unit k - 1 from its slot and store it.
+//            32- or 64-bit load per tile, one packed product, one packed FP32 addition),
+//            then the fixed tree and the row's inverse. This is the latency-bound part (one
+//            dependent addition per tile, whatever G is). When a unit is so small that one
+//            chain no longer keeps up with HBM (fused, G <= 4), two chain warps take
+//            alternate units and each has two units' time.
+//   emit     the mover warps normalise a chained unit from its slot and store it.
 //
-// The chain is the latency-bound part (one dependent addition per tile): its warps sit on
-// their own warp schedulers and the movers are the warps of the other schedulers, so the
-// chain never waits for an issue slot. One barrier per iteration. A unit is read from HBM
-// exactly once; every loop walks with constant strides (no index arithmetic per vector).
+// Chain warps sit on warp schedulers of their own (warp w issues on scheduler w % 4); the
+// movers are the warps of the other schedulers and keep their part of the scale row in
+// registers. A unit is read from HBM exactly once; every loop walks with constant strides.
+//
+// Every wait is bounded: a wait that gives up sets a flag that ends all jobs of the CTA, and
+// the launch is counted in a device counter the host can read (iomb_rmsnorm_copy_timeouts).
 //
 // Accumulation order (src/cpu/avx512_bf16_rmsnorm_reduction.cpp:69-81,130-148): per
 // row 16 column accumulators, each acc = acc + fl(x * x) over the tiles in order, then
@@ -41,8 +45,6 @@ namespace iomb {
 
 constexpr int kLongThreads = 512;
 constexpr uint32_t kSharedCap = 227 * 1024;
-// pair sums (256 floats) + two sets of 16 inverses and 16 flags + a flag word
-constexpr uint32_t kLongFixedBytes = 256 * 4 + 2 * 16 * 4 + 2 * 16 * 4 + 32 + 4 * 8;
 
 struct LongShape {
     uint32_t scale_in_smem;   // the scale row, widened to FP32, is kept in shared memory
@@ -50,17 +52,6 @@ struct LongShape {
     uint32_t box_tiles;       // tiles per bulk copy (the tensor maps' box height)
     uint32_t boxes;           // copies per unit and operand: boxes * box_tiles >= tile_cols
 };
-
-// Two FP32 additions in one instruction, each rounded to nearest even (the products that
-// feed it are separate scalar multiplications, so nothing can be contracted into an FMA).
-__device__ __forceinline__ void add_pair(float& a0, float& a1, float s0, float s1) {
-    asm("{\n\t.reg .b64 acc, add;\n\t"
-        "mov.b64 acc, {%0, %1};\n\t"
-        "mov.b64 add, {%2, %3};\n\t"
-        "add.rn.f32x2 acc, acc, add;\n\t"
-        "mov.b64 {%0, %1}, acc;\n\t}"
-        : "+f"(a0), "+f"(a1) : "f"(s0), "f"(s1));
-}
 
 // acc += fl(x * x) for two lanes: one packed multiplication and one packed addition, each
 // lane rounded separately exactly like the scalar pair.
@@ -74,26 +65,55 @@ __device__ __forceinline__ void square_add_pair(float& a0, float& a1, float x0, 
         : "+f"(a0), "+f"(a1) : "f"(x0), "f"(x1));
 }
 
-// Geometry shared by the kernel and its launcher: chain warps and mover warps of a CTA for
-// groups of g rows, and the tiles the movers cover in one step of their walk.
-__host__ __device__ constexpr uint32_t long_chain_warps(uint32_t g) { return (g * kTile / 2 + 31) / 32; }
-__host__ __device__ constexpr uint32_t long_mover_warps(uint32_t g) {
-    return long_chain_warps(g) < 4 ? kLongThreads / 128 * (4 - long_chain_warps(g)) : kLongThreads / 32 - 4;
+// Geometry shared by the kernel and its launcher, for groups of g rows.
+// Columns a chain thread owns (one while the chain then still fits two warps: a thread's
+// step is then a load, a decode, a product and the dependent addition, the shortest there
+// is; two neighbouring columns with packed arithmetic otherwise), the warps of one chain,
+// and chains that run side by side on alternate units:
+__host__ __device__ constexpr uint32_t long_chain_pack(uint32_t g, bool) { return g <= 4 ? 1 : 2; }
+__host__ __device__ constexpr uint32_t long_chain_warps(uint32_t g, bool fused) {
+    return (g * kTile / long_chain_pack(g, fused) + 31) / 32;
 }
-__host__ __device__ constexpr uint32_t long_move_tiles_per_step(uint32_t elem, uint32_t g) {
-    return long_mover_warps(g) * 32 / (g * kTile * elem / 16);
+__host__ __device__ constexpr uint32_t long_chains(uint32_t g, bool fused) {
+    return fused && long_chain_warps(g, fused) == 1 ? 2 : 1;
+}
+// Movers: the warps of the schedulers without a chain warp (all other warps when every
+// scheduler has one), and the tiles they cover in one step of their walk.
+__host__ __device__ constexpr uint32_t long_mover_warps(uint32_t g, bool fused) {
+    return long_chain_warps(g, fused) * long_chains(g, fused) < 4
+            ? kLongThreads / 128 * (4 - long_chain_warps(g, fused) * long_chains(g, fused))
+            : kLongThreads / 32 - 4;
+}
+__host__ __device__ constexpr uint32_t long_move_tiles_per_step(uint32_t elem, uint32_t g, bool fused) {
+    return long_mover_warps(g, fused) * 32 / (g * kTile * elem / 16);
+}
+// Slots of x: a unit holds its slot from the copy (one unit ahead) through the add (fused),
+// the chain (one unit's time per chain) and the emit. The residual has two slots of its own.
+__host__ __device__ constexpr uint32_t long_x_slots(uint32_t g, bool fused) {
+    return fused ? 3 + long_chains(g, fused) : 3;
+}
+__host__ __device__ constexpr uint32_t long_slots(uint32_t g, bool fused) {
+    return long_x_slots(g, fused) + (fused ? 2 : 0);
+}
+// Shared memory besides the slots: the chains' lane sums, per slot 16 inverses and 16
+// flags, two flag words, four mbarriers per slot.
+__host__ __device__ constexpr uint32_t long_fixed_bytes(uint32_t g, bool fused) {
+    return long_chains(g, fused) * g * kTile * 4 + long_x_slots(g, fused) * (16 * 4 + 16 * 4) + 16
+            + long_x_slots(g, fused) * 4 * 8;
 }
 // A mover keeps the scale vectors of the tiles it walks in registers when its walk has at
 // most this many steps (the scale depends on the column only, so one load serves every unit).
-constexpr uint32_t kScaleSteps = 12;
+// (Sixteen vectors are 64 registers. The fused kernel's movers also add, and ran 13 % slower
+// with that many registers held: they keep eight, which covers 8192 features.)
+__host__ __device__ constexpr uint32_t long_scale_steps(bool fused) { return fused ? 8 : 16; }
 
-// ---- tensor-map copies (TMA) ---------------------------------------------------------
-// The unfused kernel fetches a unit with bulk tensor copies: one thread issues them, the
-// copy engine generates the addresses and writes shared memory, and an mbarrier counts the
-// bytes. No other thread spends an instruction on the copy, and the load/store pipeline
-// the chain warps read through stays free of copy instructions.
+// ---- tensor-map copies (TMA) and mbarriers ---------------------------------------------
+// A unit is fetched with bulk tensor copies: one thread issues them, the copy engine
+// generates the addresses and writes shared memory, and an mbarrier counts the bytes. No
+// other thread spends an instruction on the copy, and the load/store pipeline the chain
+// warps read through stays free of copy instructions.
 constexpr uint32_t kMaxBoxTiles = 256;         // a box dimension's limit
-constexpr uint32_t kWaitPolls = 1u << 22;      // bounded wait: gives up and reports
+constexpr long long kWaitCycles = 1ll << 31;   // bounded wait (about a second): gives up and reports
 
 __device__ unsigned int g_rms_copy_timeouts;   // counts waits that gave up (never expected)
 
@@ -105,17 +125,30 @@ __device__ __forceinline__ void mbarrier_expect_tx(uint64_t* bar, uint32_t bytes
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(
             static_cast<uint32_t>(__cvta_generic_to_shared(bar))), "r"(bytes) : "memory");
 }
-// True when the phase with this parity has completed; polls a bounded number of times.
-__device__ __forceinline__ bool mbarrier_wait(uint64_t* bar, uint32_t parity) {
-    const uint32_t address = static_cast<uint32_t>(__cvta_generic_to_shared(bar));
-    for (uint32_t poll = 0; poll < kWaitPolls; ++poll) {
-        uint32_t done;
-        asm volatile("{\n\t.reg .pred p;\n\t"
-                     "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-                     "selp.u32 %0, 1, 0, p;\n\t}"
-                     : "=r"(done) : "r"(address), "r"(parity) : "memory");
-        if (done) return true;
-    }
+__device__ __forceinline__ void mbarrier_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(
+            static_cast<uint32_t>(__cvta_generic_to_shared(bar))) : "memory");
+}
+__device__ __forceinline__ bool mbarrier_test(uint64_t* bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(done) : "r"(static_cast<uint32_t>(__cvta_generic_to_shared(bar))), "r"(parity)
+                 : "memory");
+    return done != 0;
+}
+// True when the phase with this parity has completed. Polls for a bounded time and gives
+// up at once when another wait of the CTA has given up (`stop`); a wait that gives up sets
+// `stop` itself.
+__device__ __forceinline__ bool mbarrier_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* stop) {
+    if (mbarrier_test(bar, parity)) return true;
+    const long long start = clock64();
+    do {
+        if (mbarrier_test(bar, parity)) return true;
+        if (*stop != 0) return false;
+    } while (clock64() - start < kWaitCycles);
+    *stop = 1;
     return false;
 }
 // One box of the tensor map: coordinates (element in tile, tile column, band of the owner).
@@ -138,26 +171,12 @@ __device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap* map, uint32_t
 // Units the L2 prefetch runs ahead of the copy into shared memory: the slots bound how far
 // the copies can run ahead (one unit), which leaves HBM idle while a copy's tail lands; the
 // prefetch keeps reads in flight across that gap.
+// Units a CTA works through in one launch (see launch_rmsnorm_long).
+#ifndef IOMB_RMS_UNITS_PER_CTA
+#define IOMB_RMS_UNITS_PER_CTA 96
+#endif
 #ifndef IOMB_RMS_L2_AHEAD
 #define IOMB_RMS_L2_AHEAD 1
-#endif
-
-#ifdef IOMB_RMS_TIMING
-// Measurement build only: cycles spent per phase by the chain warp and by one mover warp
-// of CTA 0 (index 0 wait for copies, 1 barrier, 2 issue, 3 chain, 4 produce, 5 emit, 6 total,
-// 7 iterations), chain warp in [0..7], mover warp in [8..15].
-__device__ unsigned long long g_rms_timing[16];
-#define RMS_TICK(slot)                                                              \
-    do {                                                                            \
-        if (timing_on) {                                                            \
-            const long long now = clock64();                                        \
-            atomicAdd(&g_rms_timing[timing_base + (slot)],                          \
-                      static_cast<unsigned long long>(now - timing_last));          \
-            timing_last = now;                                                      \
-        }                                                                           \
-    } while (false)
-#else
-#define RMS_TICK(slot) do {} while (false)
 #endif
 
 template <int ELEM, int G, bool FUSED>
@@ -165,30 +184,37 @@ __global__ void __launch_bounds__(kLongThreads, 1)
 rmsnorm_long_kernel(const RmsParams p, const LongShape shape, const __grid_constant__ CUtensorMap x_map,
                     const __grid_constant__ CUtensorMap r_map) {
     extern __shared__ __align__(128) unsigned char smem[];
-    constexpr uint32_t kSlots = FUSED ? 4 : 3;               // slots of x
-    constexpr uint32_t kResidualSlots = FUSED ? 2 : 0;
     constexpr uint32_t kTileBytes = kTileSlots * ELEM;
     constexpr uint32_t kRowBytes = kTile * ELEM;             // one in-tile row
     constexpr uint32_t kVectorsPerRow = kRowBytes / 16;      // 2 (16-bit) or 4 (32-bit)
     constexpr uint32_t kPerVector = 16 / ELEM;
     constexpr uint32_t kPieceBytes = G * kRowBytes;          // a unit's part of one tile
     constexpr uint32_t kPieceVectors = G * kVectorsPerRow;   // 2 .. 64
-    constexpr uint32_t kPairs = G * kTile / 2;               // chain threads: (row, column pair)
-    constexpr uint32_t kChainWarps = (kPairs + 31) / 32;     // 1, 2 or 4
+    constexpr uint32_t kScaleSteps = long_scale_steps(FUSED);
+    constexpr uint32_t kPack = long_chain_pack(G, FUSED);           // columns per chain thread
+    constexpr uint32_t kPairs = G * kTile / kPack;           // threads of a chain
+    constexpr uint32_t kChainWarps = long_chain_warps(G, FUSED);    // 1, 2 or 4
+    constexpr uint32_t kChains = long_chains(G, FUSED);      // chains on alternate units
     constexpr uint32_t kChainThreads = kChainWarps * 32;
-    // Warp w issues on scheduler w % 4. The chain warps are warps 0 .. kChainWarps - 1;
+    constexpr uint32_t kAllChainWarps = kChainWarps * kChains;
+    // Warp w issues on scheduler w % 4. The chain warps are warps 0 .. kAllChainWarps - 1;
     // the movers are the warps of the remaining schedulers (all other warps when every
     // scheduler has a chain warp).
-    constexpr uint32_t kFreeSchedulers = kChainWarps < 4 ? 4 - kChainWarps : 0;
-    constexpr uint32_t kMoverWarps = long_mover_warps(G);
+    constexpr uint32_t kFreeSchedulers = kAllChainWarps < 4 ? 4 - kAllChainWarps : 0;
+    constexpr uint32_t kMoverWarps = long_mover_warps(G, FUSED);
     constexpr uint32_t kMovers = kMoverWarps * 32;
     static_assert(kMovers % kPieceVectors == 0,
                   "a thread keeps one vector position of every tile it touches");
-    constexpr uint32_t kIssuer = 128;                        // warp 4: idle, or the first mover
-    constexpr uint32_t kMoveTilesPerStep = kMovers / kPieceVectors;
-    static_assert(kChainWarps == long_chain_warps(G) && kMoverWarps == long_mover_warps(G)
-                          && kMoveTilesPerStep == long_move_tiles_per_step(ELEM, G),
-                  "the launcher sizes the movers' walk with the same geometry");
+    constexpr uint32_t kIssuer = 128;                        // warp 4: no other job, or the first mover
+    constexpr uint32_t kMoveTilesPerStep = long_move_tiles_per_step(ELEM, G, FUSED);
+    static_assert(kMoveTilesPerStep == kMovers / kPieceVectors, "the launcher sizes the walk alike");
+    // The pipeline, in units: the copy runs kCopyAhead units ahead of the movers' step; the
+    // emit follows kLag units behind it (the chains' time, plus the add's when fused).
+    constexpr uint32_t kSlots = long_x_slots(G, FUSED);
+    constexpr uint32_t kResidualSlots = FUSED ? 2 : 0;
+    constexpr uint32_t kCopyAhead = 1;
+    constexpr uint32_t kLag = FUSED ? kChains + 1 : kChains;
+    static_assert(kSlots == kCopyAhead + kLag + 1, "a slot is free again when its unit was emitted");
 
     // A slot holds whole boxes (the last box of a unit may reach past the row's tiles: the
     // copy engine fills that part with zeros).
@@ -197,12 +223,19 @@ rmsnorm_long_kernel(const RmsParams p, const LongShape shape, const __grid_const
     unsigned char* scale_wide = residual_slots + static_cast<size_t>(kResidualSlots) * unit_bytes;
     float* lanes = reinterpret_cast<float*>(
             scale_wide + (shape.scale_in_smem ? static_cast<size_t>(p.tile_cols) * kTile * 4 : 0));
-    float* inverse = lanes + 256;                            // [2][16]
-    uint32_t* clean = reinterpret_cast<uint32_t*>(inverse + 32);   // [2][16]
-    uint32_t* scale_not_finite = clean + 32;
-    uint64_t* full = reinterpret_cast<uint64_t*>(scale_not_finite + 2);   // [kSlots] mbarriers
+    float* inverse = lanes + kChains * G * kTile;            // [kSlots][16]
+    uint32_t* clean = reinterpret_cast<uint32_t*>(inverse + kSlots * 16);   // [kSlots][16]
+    uint32_t* scale_not_finite = clean + kSlots * 16;
+    volatile uint32_t* stop = scale_not_finite + 1;          // a wait gave up: every job ends
+    // Per slot: the copy landed; (fused) the sum is in the slot; the inverses are known; the
+    // unit was emitted.
+    uint64_t* landed_bar = reinterpret_cast<uint64_t*>(scale_not_finite + 4);
+    uint64_t* added_bar = landed_bar + kSlots;
+    uint64_t* chained_bar = added_bar + kSlots;
+    uint64_t* emitted_bar = chained_bar + kSlots;
     const uint32_t tid = threadIdx.x;
     const uint32_t warp = tid >> 5;
+    const uint32_t lane = tid & 31u;
     const uint32_t full_tiles = p.cols / kTile;
     const uint32_t tail_cols = p.cols % kTile;
 
@@ -210,8 +243,8 @@ rmsnorm_long_kernel(const RmsParams p, const LongShape shape, const __grid_const
     // This thread's index among the movers, or kMovers when it is not one.
     uint32_t mover = kMovers;
     if constexpr (kFreeSchedulers != 0) {
-        if ((warp & 3u) >= kChainWarps) {
-            mover = ((warp >> 2) * kFreeSchedulers + (warp & 3u) - kChainWarps) * 32 + (tid & 31u);
+        if ((warp & 3u) >= kAllChainWarps) {
+            mover = ((warp >> 2) * kFreeSchedulers + (warp & 3u) - kAllChainWarps) * 32 + lane;
         }
     } else {
         if (warp >= 4) mover = tid - 128;
@@ -222,29 +255,44 @@ rmsnorm_long_kernel(const RmsParams p, const LongShape shape, const __grid_const
     const uint32_t count = blockIdx.x < p.units
             ? static_cast<uint32_t>((p.units - blockIdx.x + gridDim.x - 1) / gridDim.x) : 0;
     auto unit_of = [&](uint32_t k) {
-        return static_cast<uint64_t>(blockIdx.x) + static_cast<uint64_t>(k) * gridDim.x;
+        return p.first_unit + blockIdx.x + static_cast<uint64_t>(k) * gridDim.x;
     };
     auto slot_of = [&](uint32_t k) { return smem + static_cast<size_t>(k % kSlots) * unit_bytes; };
     auto residual_slot_of = [&](uint32_t k) {
         return residual_slots + static_cast<size_t>(k % (FUSED ? 2 : 1)) * unit_bytes;
     };
+    // Unit k's turn on one of the per-slot barriers: slot k % kSlots, phase k / kSlots.
+    auto await = [&](uint64_t* bars, uint32_t k) {
+        return mbarrier_wait(bars + k % kSlots, (k / kSlots) & 1u, stop);
+    };
+    // One arrival per warp, after all its lanes' reads and writes of the unit.
+    auto warp_arrives = [&](uint64_t* bars, uint32_t k) {
+        __syncwarp();
+        if (lane == 0) mbarrier_arrive(bars + k % kSlots);
+    };
 
-    // Starts the copies of unit k into its slot(s): one thread issues the unit's boxes (a
-    // copy instruction takes a few hundred cycles to issue: the thread belongs to a warp
-    // with no other job whenever the CTA has one, that is unless all four schedulers chain), and asks for a later unit's boxes to be brought into
-    // L2. Every unit, valid or not, completes its barrier phase, so the waits stay in step.
+    // Starts the copies of unit k into its slot(s) once those are free, and asks for a
+    // later unit's boxes to be brought into L2. One thread does this (a copy instruction
+    // takes a few hundred cycles to issue: the thread belongs to a warp with no other job
+    // whenever the CTA has one, that is unless all four schedulers chain). Every unit,
+    // valid or not, completes its barrier phases, so the waits stay in step.
     auto issue = [&](uint32_t k) {
-        if (tid != kIssuer) return;
+        if (tid != kIssuer) return true;
         const uint32_t boxes = shape.boxes;
         const uint32_t box_tiles = shape.box_tiles;
         if (k < count) {
+            // The slot of x held unit k - kSlots (emitted?), the residual's unit k - 2 (added?).
+            if (k >= kSlots && !await(emitted_bar, k - kSlots)) return false;
+            if constexpr (FUSED) {
+                if (k >= 2 && !await(added_bar, k - 2)) return false;
+            }
             const RmsUnit at = rms_locate<G>(p, unit_of(k));
-            uint64_t* bar = full + k % kSlots;
+            uint64_t* bar = landed_bar + k % kSlots;
             if (!at.valid) {
                 mbarrier_expect_tx(bar, 0);
             } else {
-                // The slots were last read and written with ordinary instructions (before
-                // the barrier this call follows): order those before the copy engine's writes.
+                // The slots were last read and written with ordinary instructions: order
+                // those before the copy engine's writes.
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 mbarrier_expect_tx(bar, (FUSED ? 2u : 1u) * boxes * box_tiles * kPieceBytes);
                 const uint32_t x_band = static_cast<uint32_t>(
@@ -282,42 +330,48 @@ rmsnorm_long_kernel(const RmsParams p, const LongShape shape, const __grid_const
                 }
             }
         }
+        return true;
     };
 
-    // Row sums of squares of unit k, then the rows' inverses (chain warps). Thread c owns
-    // columns 2 * (c % 8), + 1 of row c / 8.
-    auto chain = [&](uint32_t k, bool scale_finite) {
+    // Row sums of squares of unit k, then the rows' inverses (the warps of one chain).
+    // Thread c of the chain owns kPack neighbouring columns of one row: column
+    // kPack * (c % (16 / kPack)) of row c / (16 / kPack).
+    auto chain = [&](uint32_t k, uint32_t chain_tid, float* chain_lanes, bool scale_finite) {
         const RmsUnit at = rms_locate<G>(p, unit_of(k));
         if (!at.valid) return;                               // uniform per CTA
-        const bool active = tid < kPairs;
-        const uint32_t c = active ? tid : 0;
-        const unsigned char* cursor = slot_of(k) + c * (2 * ELEM);
-        float acc0 = 0.0f, acc1 = 0.0f;
-        // One load per tile: two BF16 codes in a word, or two floats.
-        using Raw = typename std::conditional<ELEM == 2, uint32_t, float2>::type;
-        auto squares_of = [&](Raw raw, float& s0, float& s1) {
-            float x0, x1;
-            if constexpr (ELEM == 2) {
-                x0 = bf16_lo(raw);
-                x1 = bf16_hi(raw);
+        constexpr uint32_t kThreadsPerRow = kTile / kPack;
+        const bool active = chain_tid < kPairs;
+        const uint32_t c = active ? chain_tid : 0;
+        const unsigned char* cursor = slot_of(k) + c * (kPack * ELEM);
+        float acc0 = 0.0f, acc1 = 0.0f;                      // acc1: the second column (kPack == 2)
+        // One load per tile: one element, or two in one word.
+        using Raw = typename std::conditional<
+                kPack == 1, typename std::conditional<ELEM == 2, uint16_t, float>::type,
+                typename std::conditional<ELEM == 2, uint32_t, float2>::type>::type;
+        auto first_of = [](Raw raw) {
+            if constexpr (kPack == 1 && ELEM == 2) return __uint_as_float(static_cast<uint32_t>(raw) << 16);
+            else if constexpr (kPack == 1) return raw;
+            else if constexpr (ELEM == 2) return bf16_lo(raw);
+            else return raw.x;
+        };
+        auto second_of = [](Raw raw) {
+            if constexpr (kPack == 1) return 0.0f;
+            else if constexpr (ELEM == 2) return bf16_hi(raw);
+            else return raw.y;
+        };
+        auto step = [&](Raw raw) {
+            if constexpr (kPack == 1) {
+                const float x = first_of(raw);
+                acc0 = __fadd_rn(acc0, __fmul_rn(x, x));
             } else {
-                x0 = raw.x;
-                x1 = raw.y;
+                square_add_pair(acc0, acc1, first_of(raw), second_of(raw));
             }
-            s0 = __fmul_rn(x0, x0);
-            s1 = __fmul_rn(x1, x1);
         };
-        auto squares = [&](const unsigned char* from, float& s0, float& s1) {
-            squares_of(*reinterpret_cast<const Raw*>(from), s0, s1);
-        };
-        // The raw words of sixteen tiles at a time in two register sets: while one set
-        // runs through the dependent additions, the loads of the other are in flight (a
-        // lane is one addition every four cycles at best; a load from shared memory takes
-        // thirty cycles on an idle SM and several times that while the movers stream).
-#ifndef IOMB_RMS_BATCH
-#define IOMB_RMS_BATCH 32
-#endif
-        constexpr uint32_t kBatch = ELEM == 2 ? IOMB_RMS_BATCH : IOMB_RMS_BATCH / 2;
+        // The raw words of kBatch tiles at a time in two register sets: while one set runs
+        // through the dependent additions, the loads of the other are in flight (a lane is
+        // one addition every four cycles at best; a load from shared memory takes thirty
+        // cycles on an idle SM and many times that while the movers stream).
+        constexpr uint32_t kBatch = sizeof(Raw) <= 4 ? 32 : 16;
         uint32_t tile = 0;
         auto fetch = [&](Raw* raw, uint32_t first) {
             const unsigned char* from = cursor + static_cast<size_t>(first) * kPieceBytes;
@@ -328,13 +382,7 @@ rmsnorm_long_kernel(const RmsParams p, const LongShape shape, const __grid_const
         };
         auto fold = [&](const Raw* raw) {
 #pragma unroll
-            for (uint32_t j = 0; j < kBatch; ++j) {
-                if constexpr (ELEM == 2) {
-                    square_add_pair(acc0, acc1, bf16_lo(raw[j]), bf16_hi(raw[j]));
-                } else {
-                    square_add_pair(acc0, acc1, raw[j].x, raw[j].y);
-                }
-            }
+            for (uint32_t j = 0; j < kBatch; ++j) step(raw[j]);
         };
         if (tile + kBatch <= full_tiles) {
             Raw even[kBatch], odd[kBatch];
@@ -352,29 +400,26 @@ rmsnorm_long_kernel(const RmsParams p, const LongShape shape, const __grid_const
             }
         }
         for (; tile < full_tiles; ++tile) {
-            float s0, s1;
-            squares(cursor + static_cast<size_t>(tile) * kPieceBytes, s0, s1);
-            acc0 = __fadd_rn(acc0, s0);
-            acc1 = __fadd_rn(acc1, s1);
+            step(*reinterpret_cast<const Raw*>(cursor + static_cast<size_t>(tile) * kPieceBytes));
         }
         if (tail_cols != 0) {
             // The ragged last tile: only its logical columns join the sums.
-            float s0, s1;
-            squares(cursor + static_cast<size_t>(full_tiles) * kPieceBytes, s0, s1);
-            const uint32_t column = 2 * (c % 8);
-            if (column < tail_cols) acc0 = __fadd_rn(acc0, s0);
-            if (column + 1 < tail_cols) acc1 = __fadd_rn(acc1, s1);
+            const Raw raw = *reinterpret_cast<const Raw*>(cursor + static_cast<size_t>(full_tiles) * kPieceBytes);
+            const uint32_t column = kPack * (c % kThreadsPerRow);
+            const float x0 = first_of(raw), x1 = second_of(raw);
+            if (column < tail_cols) acc0 = __fadd_rn(acc0, __fmul_rn(x0, x0));
+            if (kPack == 2 && column + 1 < tail_cols) acc1 = __fadd_rn(acc1, __fmul_rn(x1, x1));
         }
         if (active) {
-            lanes[2 * c] = acc0;                             // lanes[row * 16 + column]
-            lanes[2 * c + 1] = acc1;
+            chain_lanes[kPack * c] = acc0;                   // [row * 16 + column]
+            if constexpr (kPack == 2) chain_lanes[kPack * c + 1] = acc1;
         }
-        __syncwarp();
-        if (active && (c % 8) == 0) {
-            const uint32_t row = c / 8;
-            const float sum = combine_lanes(lanes + row * kTile);
-            inverse[(k & 1u) * 16 + row] = row_inverse(sum, p.cols, p.eps);
-            clean[(k & 1u) * 16 + row] = row_is_clean(sum, scale_finite) ? 1u : 0u;
+        __syncwarp();                                        // a row's threads share a warp
+        if (active && (c % kThreadsPerRow) == 0) {
+            const uint32_t row = c / kThreadsPerRow;
+            const float sum = combine_lanes(chain_lanes + row * kTile);
+            inverse[(k % kSlots) * 16 + row] = row_inverse(sum, p.cols, p.eps);
+            clean[(k % kSlots) * 16 + row] = row_is_clean(sum, scale_finite) ? 1u : 0u;
         }
     };
 
@@ -383,7 +428,6 @@ rmsnorm_long_kernel(const RmsParams p, const LongShape shape, const __grid_const
     // + kMoveTilesPerStep, ...
     auto add = [&](uint32_t k) {
         if constexpr (FUSED) {
-            if (k >= count || mover >= kMovers) return;
             const RmsUnit at = rms_locate<G>(p, unit_of(k));
             if (!at.valid) return;
             const uint32_t v = mover % kPieceVectors;
@@ -424,7 +468,6 @@ rmsnorm_long_kernel(const RmsParams p, const LongShape shape, const __grid_const
 
     // Normalises unit k from its slot and stores it (movers).
     auto emit = [&](uint32_t k) {
-        if (mover >= kMovers) return;
         const RmsUnit at = rms_locate<G>(p, unit_of(k));
         if (!at.valid) return;
         const uint32_t v = mover % kPieceVectors;
@@ -433,84 +476,31 @@ rmsnorm_long_kernel(const RmsParams p, const LongShape shape, const __grid_const
         if (row >= min(static_cast<uint32_t>(G), at.rows_in_band - at.row0)) return;
         const uint32_t col_in_tile = cv * kPerVector;
         const uint32_t first_tile = mover / kPieceVectors;
-        const float inv = inverse[(k & 1u) * 16 + row];
-        const bool fast = clean[(k & 1u) * 16 + row] != 0;
+        const float inv = inverse[(k % kSlots) * 16 + row];
+        const bool fast = clean[(k % kSlots) * 16 + row] != 0;
         unsigned char* out = rms_unit_base<ELEM>(p, p.out, at) + v * 16
                 + static_cast<size_t>(first_tile) * kTileBytes;
         const unsigned char* in = slot_of(k) + static_cast<size_t>(mover) * 16;
         const uint32_t steps = first_tile < full_tiles
                 ? (full_tiles - first_tile + kMoveTilesPerStep - 1) / kMoveTilesPerStep : 0;
-        auto walk = [&](auto wide_tag, auto fast_tag) {
-            constexpr bool kWide = decltype(wide_tag)::value;
-            constexpr bool kFast = decltype(fast_tag)::value;
-            const unsigned char* w_cursor = kWide
-                    ? scale_wide + (static_cast<size_t>(first_tile) * kTile + col_in_tile) * 4
-                    : p.scale_row + static_cast<size_t>(first_tile) * kTileBytes + cv * 16;
-            constexpr size_t kScaleStep = kWide ? static_cast<size_t>(kMoveTilesPerStep) * kTile * 4
-                                                : static_cast<size_t>(kMoveTilesPerStep) * kTileBytes;
-            auto load_scale = [&](const unsigned char* from, float* w) {
-                if constexpr (kWide) {
-                    const float4 w0 = reinterpret_cast<const float4*>(from)[0];
-                    w[0] = w0.x; w[1] = w0.y; w[2] = w0.z; w[3] = w0.w;
-                    if constexpr (ELEM == 2) {
-                        const float4 w1 = reinterpret_cast<const float4*>(from)[1];
-                        w[4] = w1.x; w[5] = w1.y; w[6] = w1.z; w[7] = w1.w;
-                    }
-                } else {
-                    widen_vector<ELEM>(__ldg(reinterpret_cast<const uint4*>(from)), w);
-                }
-            };
-            uint32_t step = 0;
-            for (; step + 2 <= steps; step += 2) {
-                float w0[kPerVector], w1[kPerVector];
-                const uint4 x0 = *reinterpret_cast<const uint4*>(in);
-                const uint4 x1 = *reinterpret_cast<const uint4*>(
-                        in + static_cast<size_t>(kMoveTilesPerStep) * kPieceBytes);
-                load_scale(w_cursor, w0);
-                load_scale(w_cursor + kScaleStep, w1);
-                store_u4_stream(out, normalize_vector<ELEM>(x0, w0, inv, kFast));
-                store_u4_stream(out + static_cast<size_t>(kMoveTilesPerStep) * kTileBytes,
-                                normalize_vector<ELEM>(x1, w1, inv, kFast));
-                in += 2 * static_cast<size_t>(kMoveTilesPerStep) * kPieceBytes;
-                out += 2 * static_cast<size_t>(kMoveTilesPerStep) * kTileBytes;
-                w_cursor += 2 * kScaleStep;
-            }
-            if (step < steps) {
-                float w[kPerVector];
-                load_scale(w_cursor, w);
-                store_u4_stream(out, normalize_vector<ELEM>(*reinterpret_cast<const uint4*>(in), w,
-                                                            inv, kFast));
-                in += static_cast<size_t>(kMoveTilesPerStep) * kPieceBytes;
-                out += static_cast<size_t>(kMoveTilesPerStep) * kTileBytes;
-                w_cursor += kScaleStep;
-            }
-            // The ragged last tile, for the thread whose walk reaches it.
-            if (tail_cols > col_in_tile && first_tile + steps * kMoveTilesPerStep == full_tiles) {
-                float w[kPerVector];
-                load_scale(w_cursor, w);
-                store_vector_masked<ELEM>(
-                        out, normalize_vector<ELEM>(*reinterpret_cast<const uint4*>(in), w, inv, kFast),
-                        min(kPerVector, tail_cols - col_in_tile));
-            }
-        };
-        // The walk with the scale in registers: loads of three steps, then their stores.
+        constexpr size_t kSlotStep = static_cast<size_t>(kMoveTilesPerStep) * kPieceBytes;
+        constexpr size_t kGlobalStep = static_cast<size_t>(kMoveTilesPerStep) * kTileBytes;
+        // The walk with the scale in registers: loads of four steps, then their stores.
         auto walk_regs = [&](auto fast_tag) {
             constexpr bool kFast = decltype(fast_tag)::value;
-            constexpr size_t kSlotStep = static_cast<size_t>(kMoveTilesPerStep) * kPieceBytes;
-            constexpr size_t kGlobalStep = static_cast<size_t>(kMoveTilesPerStep) * kTileBytes;
 #pragma unroll
-            for (uint32_t half = 0; half < kScaleSteps; half += 3) {
-                uint4 xs[3];
+            for (uint32_t first = 0; first < kScaleSteps; first += 4) {
+                uint4 xs[4];
 #pragma unroll
-                for (uint32_t j = 0; j < 3; ++j) {
-                    if (half + j < steps) xs[j] = *reinterpret_cast<const uint4*>(in + (half + j) * kSlotStep);
+                for (uint32_t j = 0; j < 4; ++j) {
+                    if (first + j < steps) xs[j] = *reinterpret_cast<const uint4*>(in + (first + j) * kSlotStep);
                 }
 #pragma unroll
-                for (uint32_t j = 0; j < 3; ++j) {
-                    if (half + j < steps) {
+                for (uint32_t j = 0; j < 4; ++j) {
+                    if (first + j < steps) {
                         float w[kPerVector];
-                        widen_vector<ELEM>(scale_regs[half + j], w);
-                        store_u4_stream(out + (half + j) * kGlobalStep,
+                        widen_vector<ELEM>(scale_regs[first + j], w);
+                        store_u4_stream(out + (first + j) * kGlobalStep,
                                         normalize_vector<ELEM>(xs[j], w, inv, kFast));
                     }
                 }
@@ -531,6 +521,60 @@ rmsnorm_long_kernel(const RmsParams p, const LongShape shape, const __grid_const
                         min(kPerVector, tail_cols - col_in_tile));
             }
         };
+        // The walk with the scale row widened in shared memory, or read through L1.
+        auto walk = [&](auto wide_tag, auto fast_tag) {
+            constexpr bool kWide = decltype(wide_tag)::value;
+            constexpr bool kFast = decltype(fast_tag)::value;
+            const unsigned char* w_cursor = kWide
+                    ? scale_wide + (static_cast<size_t>(first_tile) * kTile + col_in_tile) * 4
+                    : p.scale_row + static_cast<size_t>(first_tile) * kTileBytes + cv * 16;
+            constexpr size_t kScaleStep = kWide ? static_cast<size_t>(kMoveTilesPerStep) * kTile * 4
+                                                : static_cast<size_t>(kMoveTilesPerStep) * kTileBytes;
+            auto load_scale = [&](const unsigned char* from, float* w) {
+                if constexpr (kWide) {
+                    const float4 w0 = reinterpret_cast<const float4*>(from)[0];
+                    w[0] = w0.x; w[1] = w0.y; w[2] = w0.z; w[3] = w0.w;
+                    if constexpr (ELEM == 2) {
+                        const float4 w1 = reinterpret_cast<const float4*>(from)[1];
+                        w[4] = w1.x; w[5] = w1.y; w[6] = w1.z; w[7] = w1.w;
+                    }
+                } else {
+                    widen_vector<ELEM>(__ldg(reinterpret_cast<const uint4*>(from)), w);
+                }
+            };
+            const unsigned char* from = in;
+            unsigned char* to = out;
+            uint32_t step = 0;
+            for (; step + 2 <= steps; step += 2) {
+                float w0[kPerVector], w1[kPerVector];
+                const uint4 x0 = *reinterpret_cast<const uint4*>(from);
+                const uint4 x1 = *reinterpret_cast<const uint4*>(from + kSlotStep);
+                load_scale(w_cursor, w0);
+                load_scale(w_cursor + kScaleStep, w1);
+                store_u4_stream(to, normalize_vector<ELEM>(x0, w0, inv, kFast));
+                store_u4_stream(to + kGlobalStep, normalize_vector<ELEM>(x1, w1, inv, kFast));
+                from += 2 * kSlotStep;
+                to += 2 * kGlobalStep;
+                w_cursor += 2 * kScaleStep;
+            }
+            if (step < steps) {
+                float w[kPerVector];
+                load_scale(w_cursor, w);
+                store_u4_stream(to, normalize_vector<ELEM>(*reinterpret_cast<const uint4*>(from), w,
+                                                           inv, kFast));
+                from += kSlotStep;
+                to += kGlobalStep;
+                w_cursor += kScaleStep;
+            }
+            // The ragged last tile, for the thread whose walk reaches it.
+            if (tail_cols > col_in_tile && first_tile + steps * kMoveTilesPerStep == full_tiles) {
+                float w[kPerVector];
+                load_scale(w_cursor, w);
+                store_vector_masked<ELEM>(
+                        to, normalize_vector<ELEM>(*reinterpret_cast<const uint4*>(from), w, inv, kFast),
+                        min(kPerVector, tail_cols - col_in_tile));
+            }
+        };
         using yes = std::true_type;
         using no = std::false_type;
         if (shape.scale_in_regs) {
@@ -542,15 +586,20 @@ rmsnorm_long_kernel(const RmsParams p, const LongShape shape, const __grid_const
         }
     };
 
-    // ---- prologue: the first copies, then the scale row ---------------------------
+    // ---- prologue: the barriers, the first copy, then the scale row ----------------
     if (tid == 0) {
         *scale_not_finite = 0;
-        for (uint32_t slot = 0; slot < kSlots; ++slot) mbarrier_init(full + slot, 1);
+        *stop = 0;
+        for (uint32_t slot = 0; slot < kSlots; ++slot) {
+            mbarrier_init(landed_bar + slot, 1);             // the issuing thread (+ the bytes)
+            mbarrier_init(added_bar + slot, kMoverWarps);
+            mbarrier_init(chained_bar + slot, kChainWarps);
+            mbarrier_init(emitted_bar + slot, kMoverWarps);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-    issue(0);
-    if constexpr (FUSED) issue(1);
+    for (uint32_t k = 0; k < kCopyAhead; ++k) (void)issue(k);
     for (uint32_t i = tid; i < p.tile_cols * kVectorsPerRow; i += kLongThreads) {
         const uint32_t tile = i / kVectorsPerRow, part = i % kVectorsPerRow;
         const uint4 raw = __ldg(reinterpret_cast<const uint4*>(
@@ -573,101 +622,72 @@ rmsnorm_long_kernel(const RmsParams p, const LongShape shape, const __grid_const
     }
     __syncthreads();
     const bool scale_finite = *scale_not_finite == 0;
-    // Iteration k: unit k is chained and unit k - 1 emitted; unfused, unit k + 1 is being
-    // copied; fused, unit k + 1 is added and unit k + 2 copied. At the barrier unit k is
-    // complete in its slot (the copy, or the sum), the inverses of unit k - 1 are known, and
-    // the slot the new copies go to has been emitted (x) or added (residual) in the
-    // iteration before.
-    //
-    // Who reads what the copy engine wrote waits for that unit's mbarrier itself: the chain
-    // warps (unfused) before the iteration's barrier, the movers right before they first
-    // read the unit (its copy has had an iteration or more by then, so they seldom poll).
-    // Warps with neither job only take part in the barriers. A wait that gives up (it never
-    // should) makes every thread leave at the next barrier, before anything more is
-    // computed from a slot that may be incomplete.
-#ifdef IOMB_RMS_TIMING
-    const bool timing_on = blockIdx.x == 0 && (tid == 0 || tid == 32);
-    const uint32_t timing_base = tid == 0 ? 0 : 8;
-    long long timing_last = clock64();
-    const long long timing_start = timing_last;
-#endif
-    bool copies_arrive = true;
-    auto landed = [&](uint32_t k) {
-        if (k < count && !mbarrier_wait(full + k % kSlots, (k / kSlots) & 1u)) copies_arrive = false;
-        return copies_arrive;
-    };
-    auto meet = [&]() {
-        RMS_TICK(0);
-        if (__syncthreads_or(!copies_arrive)) {
-            if (tid == 0) atomicAdd(&g_rms_copy_timeouts, 1u);
-            copies_arrive = false;
-            return false;
-        }
-        RMS_TICK(1);
-        return true;
-    };
-    // The chain warps and the others run loops of their own (the same barriers in the same
-    // order), so that neither side's registers count against the other's.
-    if (tid < kChainThreads) {
-        bool running = true;
-        if constexpr (FUSED) running = meet();               // unit 0 has been added
-        for (uint32_t k = 0; running && k <= count; ++k) {
-            if constexpr (!FUSED) landed(k);
-            if (!meet()) break;
-            if (k < count) chain(k, scale_finite);
-            RMS_TICK(3);
+
+    // ---- the jobs ---------------------------------------------------------------------
+    // Who reads what the copy engine wrote waits for that unit's `landed` barrier itself.
+    // The jobs have loops of their own, so that neither side's registers count against the
+    // other's.
+    if (warp < kAllChainWarps) {
+        // Chain `mine` takes units mine, mine + kChains, ...
+        const uint32_t mine = warp / kChainWarps;
+        const uint32_t chain_tid = tid - mine * kChainThreads;
+        float* chain_lanes = lanes + mine * G * kTile;
+        for (uint32_t k = mine; k < count; k += kChains) {
+            if (!await(FUSED ? added_bar : landed_bar, k)) break;
+            chain(k, chain_tid, chain_lanes, scale_finite);
+            warp_arrives(chained_bar, k);
         }
     } else {
         const bool moves = mover < kMovers;
-        bool running = true;
+        if (moves) {
 #pragma unroll
-        for (uint32_t j = 0; j < kScaleSteps; ++j) scale_regs[j] = make_uint4(0, 0, 0, 0);
-        if (shape.scale_in_regs && moves) {
-            const uint32_t first_tile = mover / kPieceVectors;
-            const uint32_t cv = mover % kPieceVectors % kVectorsPerRow;
+            for (uint32_t j = 0; j < kScaleSteps; ++j) scale_regs[j] = make_uint4(0, 0, 0, 0);
+            if (shape.scale_in_regs) {
+                const uint32_t first_tile = mover / kPieceVectors;
+                const uint32_t cv = mover % kPieceVectors % kVectorsPerRow;
 #pragma unroll
-            for (uint32_t j = 0; j < kScaleSteps; ++j) {
-                const uint32_t tile = first_tile + j * kMoveTilesPerStep;
-                if (tile < p.tile_cols) {
-                    scale_regs[j] = __ldg(reinterpret_cast<const uint4*>(
-                            p.scale_row + static_cast<size_t>(tile) * kTileBytes + cv * 16));
+                for (uint32_t j = 0; j < kScaleSteps; ++j) {
+                    const uint32_t tile = first_tile + j * kMoveTilesPerStep;
+                    if (tile < p.tile_cols) {
+                        scale_regs[j] = __ldg(reinterpret_cast<const uint4*>(
+                                p.scale_row + static_cast<size_t>(tile) * kTileBytes + cv * 16));
+                    }
                 }
             }
         }
-        if constexpr (FUSED) {
-            // Unit 0 is added before the loop: from then on the add runs one unit ahead of
-            // the chain.
-            if (moves && landed(0)) add(0);
-            running = meet();
-        }
-        for (uint32_t k = 0; running && k <= count; ++k) {
-            if (!meet()) break;
-            issue(k + (FUSED ? 2 : 1));
-            RMS_TICK(2);
-            if (moves) {
-                if (k >= 1 && (FUSED || landed(k - 1))) emit(k - 1);
-                RMS_TICK(5);
-                if constexpr (FUSED) {
-                    if (landed(k + 1)) add(k + 1);
+        // Step u: unit u + kCopyAhead is issued, unit u added (fused), unit u - kLag emitted.
+        for (uint32_t u = 0; u < count + kLag; ++u) {
+            if (!issue(u + kCopyAhead)) break;
+            if (!moves) continue;
+            if constexpr (FUSED) {
+                if (u < count) {
+                    if (!await(landed_bar, u)) break;
+                    add(u);
+                    warp_arrives(added_bar, u);
                 }
-                RMS_TICK(4);
+            }
+            if (u >= kLag) {
+                const uint32_t e = u - kLag;
+                if constexpr (!FUSED) {
+                    if (!await(landed_bar, e)) break;        // long landed: the chain waited for it
+                }
+                if (!await(chained_bar, e)) break;
+                emit(e);
+                warp_arrives(emitted_bar, e);
             }
         }
     }
-    // Leaving early with copies possibly in flight: give them a bounded time to land
-    // before the CTA's shared memory is handed to another CTA.
-    if (!copies_arrive && tid == 0) {
+    // Every job is done, or a wait gave up (it never should). Then copies may still be in
+    // flight: give them a bounded time to land before the shared memory goes to another CTA.
+    __syncthreads();
+    if (*stop != 0 && tid == 0) {
+        atomicAdd(&g_rms_copy_timeouts, 1u);
         for (uint32_t slot = 0; slot < kSlots; ++slot) {
-            (void)mbarrier_wait(full + slot, 0);
-            (void)mbarrier_wait(full + slot, 1);
+            for (uint32_t poll = 0; poll < (1u << 16); ++poll) {
+                if (mbarrier_test(landed_bar + slot, 0) || mbarrier_test(landed_bar + slot, 1)) break;
+            }
         }
     }
-#ifdef IOMB_RMS_TIMING
-    if (timing_on) {
-        atomicAdd(&g_rms_timing[timing_base + 6], static_cast<unsigned long long>(clock64() - timing_start));
-        atomicAdd(&g_rms_timing[timing_base + 7], static_cast<unsigned long long>(count + 1));
-    }
-#endif
 }
 
 using LongKernel = void (*)(const RmsParams, const LongShape, const CUtensorMap, const CUtensorMap);
@@ -741,28 +761,29 @@ int launch_rmsnorm_long(const RmsParams& base, uint32_t elem, bool fused, uint64
                         cudaStream_t stream, bool* launched) {
     *launched = false;
     // A unit is copied as `boxes` equal boxes of at most kMaxBoxTiles tiles; the slots hold
-    // whole boxes. Largest group of rows of which the slots (and the fixed part) fit one SM.
-    const uint64_t room = kSharedCap - kLongFixedBytes;
-    const uint64_t slots = fused ? 6 : 3;
+    // whole boxes. Largest group of rows of which the slots (and the rest) fit one SM.
     const uint32_t boxes = (base.tile_cols + kMaxBoxTiles - 1) / kMaxBoxTiles;
     // (a multiple of four tiles, so that every box starts on a 128-byte boundary of its slot)
     const uint32_t box_tiles = ((base.tile_cols + boxes - 1) / boxes + 3) / 4 * 4;
     const uint64_t slot_row_bytes = static_cast<uint64_t>(boxes) * box_tiles * kTile * elem;
-    if (slots * slot_row_bytes > room) return IOMB_OK;     // not served here
+    auto slot_bytes = [&](uint32_t rows) { return long_slots(rows, fused) * rows * slot_row_bytes; };
+    auto fits = [&](uint32_t rows) { return slot_bytes(rows) + long_fixed_bytes(rows, fused) <= kSharedCap; };
+    if (!fits(1)) return IOMB_OK;                          // not served here
     uint32_t g = kTile;
-    while (g > 1 && slots * g * slot_row_bytes > room) g /= 2;
+    while (g > 1 && !fits(g)) g /= 2;
     // Few rows (decode steps): smaller groups spread the bands over more SMs.
     const uint64_t sms = static_cast<uint64_t>(sm_count() > 0 ? sm_count() : 148);
     while (g > 1 && bands * (kTile / g) < sms) g /= 2;
-    const uint64_t unit_bytes = g * slot_row_bytes;
     const uint64_t scale_bytes = row_bytes / elem * 4;     // row 0 of every scale tile as FP32
     LongShape shape{};
     shape.boxes = boxes;
     shape.box_tiles = box_tiles;
-    const uint64_t walk_tiles = long_move_tiles_per_step(elem, g);
-    shape.scale_in_regs = (base.tile_cols + walk_tiles - 1) / walk_tiles <= kScaleSteps ? 1u : 0u;
-    shape.scale_in_smem = !shape.scale_in_regs && slots * unit_bytes + scale_bytes <= room ? 1u : 0u;
-    const uint64_t smem_bytes = slots * unit_bytes + (shape.scale_in_smem ? scale_bytes : 0) + kLongFixedBytes;
+    const uint64_t walk_tiles = long_move_tiles_per_step(elem, g, fused);
+    shape.scale_in_regs = (base.tile_cols + walk_tiles - 1) / walk_tiles <= long_scale_steps(fused) ? 1u : 0u;
+    shape.scale_in_smem = !shape.scale_in_regs
+                    && slot_bytes(g) + scale_bytes + long_fixed_bytes(g, fused) <= kSharedCap ? 1u : 0u;
+    const uint64_t smem_bytes = slot_bytes(g) + (shape.scale_in_smem ? scale_bytes : 0)
+            + long_fixed_bytes(g, fused);
 
     RmsParams p = base;
     p.group_rows = g;
@@ -778,28 +799,39 @@ int launch_rmsnorm_long(const RmsParams& base, uint32_t elem, bool fused, uint64
             : (fused ? pick_long<4, true>(g) : pick_long<4, false>(g));
     const int prepared = allow_full_shared_memory(reinterpret_cast<const void*>(kernel));
     if (prepared != IOMB_OK) return prepared;
-    const uint64_t grid = p.units < sms ? p.units : sms;
-    kernel<<<static_cast<unsigned>(grid), kLongThreads, smem_bytes, stream>>>(p, shape, x_map, r_map);
+    // The CTAs of a launch start on neighbouring units (the groups of one band, then the
+    // next band) and nothing keeps them in step afterwards. Once they have drifted apart,
+    // the 64- or 128-byte pieces of one tile are fetched at different times and DRAM opens a
+    // row for each piece: measured on [262144, 8192] BF16, one launch ran at 0.55 of the
+    // rate of the same rows in launches of 32768. So a launch covers a bounded number of
+    // units per CTA; the launches of one call follow one another on the stream.
+    const uint64_t all_units = p.units;
+    const uint64_t per_launch = sms * IOMB_RMS_UNITS_PER_CTA;
+    uint32_t launches = 0;
+    for (uint64_t first = 0; first < all_units; first += per_launch, ++launches) {
+        p.first_unit = first;
+        p.units = all_units - first < per_launch ? all_units - first : per_launch;
+        const uint64_t grid = p.units < sms ? p.units : sms;
+        kernel<<<static_cast<unsigned>(grid), kLongThreads, smem_bytes, stream>>>(p, shape, x_map, r_map);
+    }
+    const uint64_t grid = all_units < sms ? all_units : sms;
     *launched = true;
     char text[160];
-    snprintf(text, sizeof text, "rmsnorm_long_kernel<elem %u, rows %u, %s> %s, scale %s, %u CTAs x %d",
-             elem, g, fused ? "fused" : "unfused", "tensor-map copies",
-             shape.scale_in_regs ? "in registers" : shape.scale_in_smem ? "in shared memory" : "through L1", static_cast<unsigned>(grid),
-             kLongThreads);
+    snprintf(text, sizeof text,
+             "rmsnorm_long_kernel<elem %u, rows %u, %s> %u chain(s), %u slots, scale %s, %u CTAs x %d, %u launch(es)",
+             elem, g, fused ? "fused" : "unfused", long_chains(g, fused), long_slots(g, fused),
+             shape.scale_in_regs ? "in registers" : shape.scale_in_smem ? "in shared memory" : "through L1",
+             static_cast<unsigned>(grid), kLongThreads, launches);
     note_launch(text);
     return check_launch("rmsnorm launch");
 }
 
 }  // namespace iomb
 
-#ifdef IOMB_RMS_TIMING
-extern "C" int iomb_debug_rms_timing(unsigned long long* out, int reset) {
-    if (cudaDeviceSynchronize() != cudaSuccess) return 1;
-    if (cudaMemcpyFromSymbol(out, iomb::g_rms_timing, sizeof(unsigned long long) * 16) != cudaSuccess) return 2;
-    if (reset) {
-        unsigned long long zero[16] = {};
-        if (cudaMemcpyToSymbol(iomb::g_rms_timing, zero, sizeof zero) != cudaSuccess) return 3;
+extern "C" int iomb_rmsnorm_copy_timeouts(unsigned int* count) {
+    if (count == nullptr) return iomb::fail(IOMB_ERR_INVALID_ARGUMENT, "iomb_rmsnorm_copy_timeouts: null result");
+    if (cudaMemcpyFromSymbol(count, iomb::g_rms_copy_timeouts, sizeof(unsigned int)) != cudaSuccess) {
+        return iomb::fail(IOMB_ERR_DEVICE, "iomb_rmsnorm_copy_timeouts: reading the counter failed");
     }
-    return 0;
+    return IOMB_OK;
 }
-#endif

@@ -253,3 +253,16 @@ def test_long_rows_through_transformed_views(gpu, dtype, features):
     run(queue, queue.rmsnorm(like(xv, dx), dw.view(), like(ov2, do2), 1e-6, order=order))
     assert oracle().iomo_rmsnorm(abi(xv), abi(w.view()), abi(ov2), 1e-6, order) == 0
     assert np.array_equal(download(do2), out2.storage)
+
+
+def test_zz_no_long_row_wait_gave_up(gpu):
+    """The long-row kernels bound their waits for asynchronous copies; a wait that gives up
+    is counted on the device. After every case above the counter is still zero."""
+    import ctypes
+
+    import torch
+    device, _ = gpu
+    torch.cuda.synchronize()
+    count = ctypes.c_uint(123)
+    assert device._lib.iomb_rmsnorm_copy_timeouts(ctypes.byref(count)) == 0
+    assert count.value == 0
