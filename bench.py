@@ -43,10 +43,11 @@ for entry in (str(ROOT), str(ROOT / "tests")):
 ROWS, HIDDEN, EPS = 262144, 8192, 1e-6
 ELEM = 2
 METRIC = "achieved HBM GB/s, fused residual ADD + RMSNorm (BF16 [262144,8192], row-sharded)"
-# dram__bytes_read.sum / dram__bytes_write.sum of one launch of the kernel the step runs,
-# per row, from the ncu capture summarised in profiles/add_rmsnorm_bf16_long_rows.md
-# (taken on a [32768,8192] shard: 2.1 GB per launch, 17 times the L2, so the written
-# lines cannot stay in the cache; traffic is proportional to the rows processed).
+# dram__bytes_read.sum and dram__bytes_write.sum of one launch of the kernel the step runs,
+# from the ncu capture summarised in profiles/add_rmsnorm_bf16_long_rows.md (the first
+# launch of a [32768,8192] shard: 28416 rows, 1.86 GB, 15 times the L2). Reads are
+# proportional to the rows. Writes are the algorithmic bytes less the lines still dirty in
+# L2 when the launch ends, which does not grow with the rows.
 NCU_READ_BYTES_PER_ROW = 937082112 / 28416       # dram__bytes_read.sum of a 28416-row launch
 NCU_WRITES_LEFT_IN_L2_BYTES = 28416 * 2 * 8192 * 2 - 882120192   # algorithmic - dram__bytes_write.sum
 
