@@ -648,7 +648,8 @@ def ops_table(device, queue, only=None, iters: int = 10) -> dict:
                    lambda: ok(queue.sdpa_canonicalize_output(merged.view())),
                    "[16,8192,2048] read, nothing to rewrite")
             release()
-    if only is None or only in ("embedding_prefill", "cache_append_prefill"):
+    if only is None or only in ("embedding_prefill", "embedding_prefill_sorted",
+                                "embedding_prefill_repeated", "cache_append_prefill"):
         # Prefill-sized data movement: 131072 token rows of the TinyLlama table (537 MB out),
         # and 64 sequences x 4 KV heads x 2048 new rows appended into 4096-row caches.
         table = tensor((32000, 2048), DataType.BF16)
@@ -660,9 +661,22 @@ def ops_table(device, queue, only=None, iters: int = 10) -> dict:
                           dtype=torch.int32))
         out = tensor((count, 2048), DataType.BF16)
         ws = device.create_workspace(32)
-        record("embedding_prefill", 2 * count * 2048 * 2 + count * 4,
-               lambda: ok(queue.embedding(table.view(), ids.view(), out.view(), ws.view())),
-               f"table [32000,2048], {count} ids")
+        gather = lambda: ok(queue.embedding(table.view(), ids.view(), out.view(), ws.view()))  # noqa: E731
+        if only in (None, "embedding_prefill"):
+            record("embedding_prefill", 2 * count * 2048 * 2 + count * 4, gather,
+                   f"table [32000,2048], {count} uniform random ids")
+        # The same gather with ids in ascending order (neighbouring output rows read
+        # neighbouring table rows), and with every id equal (one table row, always in cache):
+        # what the table side of the random case costs.
+        if only in (None, "embedding_prefill_sorted"):
+            flat = ids.storage().view(torch.int32)
+            flat.copy_(torch.sort(flat).values)
+            record("embedding_prefill_sorted", 2 * count * 2048 * 2 + count * 4, gather,
+                   f"table [32000,2048], {count} ids in ascending order")
+        if only in (None, "embedding_prefill_repeated"):
+            ids.storage().view(torch.int32).fill_(12345)
+            record("embedding_prefill_repeated", count * 2048 * 2 + 2048 * 2 + count * 4, gather,
+                   f"table [32000,2048], {count} equal ids (bytes: the output, one table row)")
         ws.close()
         release()
         k = tensor((64, 4, 2048, 64), DataType.BF16)

@@ -1177,6 +1177,7 @@ private:
     void run_worker() noexcept {
         (void)cudaSetDevice(static_cast<int>(device_->backend_device()));
         std::uint64_t consumed = 0;
+        std::uint64_t proven_count = 0;     // ring records known complete through a later event
         for (;;) {
             std::uint64_t available = published_.load(std::memory_order_acquire);
             while (available == consumed) {
@@ -1189,8 +1190,27 @@ private:
             ++consumed;
             std::exception_ptr failure;
             bool proven = true;
-            if (record.proof == Proof::event) {
-                const cudaError_t status = cudaEventSynchronize(events_[record.event_slot]);
+            if (record.proof == Proof::event && consumed <= proven_count) {
+                // A later operation of this stream has completed: so has this one.
+            } else if (record.proof == Proof::event) {
+                // The stream runs its operations in order, so a later event that has already
+                // completed proves every record before it: when this thread is behind, one
+                // query retires the whole backlog (the submitting thread shares the driver
+                // with this one, and fewer blocking waits leave it more room). Otherwise the
+                // record's own event is waited for, so no token completes later than its
+                // operation.
+                std::uint64_t newest = consumed - 1;
+                for (std::uint64_t i = consumed; i < available; ++i) {
+                    if (shutdown_.load(std::memory_order_acquire) && i + 1 == available) break;
+                    if (ring_[i % ring_.size()].proof == Proof::event) newest = i;
+                }
+                cudaError_t status = cudaErrorNotReady;
+                if (newest != consumed - 1) {
+                    status = cudaEventQuery(events_[ring_[newest % ring_.size()].event_slot]);
+                    if (status == cudaSuccess) proven_count = newest + 1;   // records [0, newest]
+                    else (void)cudaGetLastError();
+                }
+                if (status != cudaSuccess) status = cudaEventSynchronize(events_[record.event_slot]);
                 if (status != cudaSuccess) {
                     proven = false;
                     failure = std::make_exception_ptr(std::runtime_error(

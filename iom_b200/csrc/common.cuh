@@ -155,6 +155,19 @@ __device__ __forceinline__ void store_u4(void* address, uint4 value) {
 __device__ __forceinline__ void store_u4_stream(void* address, uint4 value) {
     __stcs(reinterpret_cast<uint4*>(address), value);
 }
+// A load that asks L2 to keep the line (for data read again and again, such as an embedding
+// table, beside a stream that would otherwise push it out).
+__device__ __forceinline__ uint64_t l2_keep_policy() {
+    uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(policy));
+    return policy;
+}
+__device__ __forceinline__ uint4 load_u4_keep(const void* address, uint64_t policy) {
+    uint4 v;
+    asm volatile("ld.global.nc.L2::cache_hint.v4.u32 {%0,%1,%2,%3}, [%4], %5;"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(address), "l"(policy));
+    return v;
+}
 // 256-bit streaming accesses (sm_100): 32-byte-aligned address, one instruction
 // for two neighbouring 16-byte vectors.
 __device__ __forceinline__ void load_u8_stream(const void* address, uint4* lo, uint4* hi) {

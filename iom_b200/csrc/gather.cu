@@ -15,7 +15,16 @@ namespace iomb {
 
 constexpr int kRowThreads = 256;
 constexpr int kRowWarps = kRowThreads / 32;
-constexpr uint32_t kTilesPerItem = 4;     // neighbouring tiles of a band one warp moves at once
+// Neighbouring tiles of a band one warp moves at once (template parameter TILES): more
+// bytes in flight per decoded id when the request has items to spare, fewer when it is a
+// decode step that has to be spread over the SMs.
+__host__ inline uint32_t tiles_per_item(uint64_t bands, uint64_t tile_cols, uint32_t widest) {
+    const uint64_t warps = static_cast<uint64_t>(sm_count() > 0 ? sm_count() : 148) * 32;
+    for (uint32_t tiles = widest; tiles > 1; tiles /= 2) {
+        if (bands * ((tile_cols + tiles - 1) / tiles) >= 2 * warps && tile_cols >= tiles) return tiles;
+    }
+    return 1;
+}
 
 struct RowGeometry {
     uint32_t elem;          // leaf bytes
@@ -25,11 +34,12 @@ struct RowGeometry {
 };
 
 // Stores one 16-byte vector, or only its first `valid` elements at the feature tail.
+template <bool STREAM = false>
 __device__ __forceinline__ void store_row_vector(unsigned char* address, uint4 value,
                                                  uint32_t valid, uint32_t per_vector,
                                                  uint32_t elem) {
     if (valid >= per_vector) {
-        store_u4(address, value);
+        if constexpr (STREAM) store_u4_stream(address, value); else store_u4(address, value);
         return;
     }
     const uint32_t words[4] = {value.x, value.y, value.z, value.w};
@@ -64,7 +74,7 @@ struct EmbeddingParams {
     uint32_t index_bits;      // 2, 4, 8, 16, 32 or 64
     uint32_t index_signed;
     uint64_t vocabulary;
-    uint64_t items;           // planes * run_tiles * ceil(tile_cols / kTilesPerItem)
+    uint64_t items;           // planes * run_tiles * ceil(tile_cols / TILES)
     uint32_t* status;
 };
 
@@ -93,12 +103,16 @@ __device__ __forceinline__ bool read_index(const EmbeddingParams& p, uint64_t in
     return !negative && id < p.vocabulary;
 }
 
+template <uint32_t kTilesPerItem>
 __global__ void __launch_bounds__(kRowThreads)
 embedding_kernel(const EmbeddingParams p) {
     const uint32_t lane = threadIdx.x & 31u;
     const uint64_t warp = static_cast<uint64_t>(blockIdx.x) * kRowWarps + (threadIdx.x >> 5);
     const uint64_t warps = static_cast<uint64_t>(gridDim.x) * kRowWarps;
     const uint32_t elem = p.row.elem;
+    // The table is read again and again while the output streams through L2 once: the table's
+    // lines are asked to stay, the output's to leave first.
+    const uint64_t keep = l2_keep_policy();
     const uint32_t vectors_per_row = elem;                 // (16 * elem) / 16
     const uint32_t per_vector = 16 / elem;
     const uint32_t tile_vectors = kTile * vectors_per_row;
@@ -133,14 +147,14 @@ embedding_kernel(const EmbeddingParams p) {
             uint4 value[kTilesPerItem];
 #pragma unroll
             for (uint32_t t = 0; t < kTilesPerItem; ++t) {
-                if (t < tiles) value[t] = load_u4(src + t * tile_bytes);
+                if (t < tiles) value[t] = load_u4_keep(src + t * tile_bytes, keep);
             }
 #pragma unroll
             for (uint32_t t = 0; t < kTilesPerItem; ++t) {
                 if (t >= tiles) continue;
                 const uint32_t col = (first_tc + t) * kTile + cv * per_vector;
                 if (col >= p.row.cols) continue;
-                store_row_vector(dst + t * tile_bytes, value[t], min(per_vector, p.row.cols - col),
+                store_row_vector<true>(dst + t * tile_bytes, value[t], min(per_vector, p.row.cols - col),
                                  per_vector, elem);
             }
         }
@@ -160,10 +174,11 @@ struct AppendParams {
     uint64_t a;                 // scalar offset (positions == nullptr)
     const uint32_t* positions;  // per index of the first leading axis, or nullptr
     uint64_t planes_per_batch;  // logical planes per index of the first leading axis
-    uint64_t items;             // planes * row_tiles * ceil(tile_cols / kTilesPerItem)
+    uint64_t items;             // planes * row_tiles * ceil(tile_cols / TILES)
     uint32_t* status;           // batched only
 };
 
+template <uint32_t kTilesPerItem>
 __global__ void __launch_bounds__(kRowThreads)
 cache_append_kernel(const AppendParams p) {
     const uint32_t lane = threadIdx.x & 31u;
@@ -298,7 +313,8 @@ static int append_dispatch(const iomb_view* source, const iomb_view* destination
     p.positions = positions;
     p.planes_per_batch = fs.planes / source->dims[0];
     p.row_tiles = static_cast<uint32_t>(fs.tile_rows);
-    p.items = fs.planes * fs.tile_rows * ((fs.tile_cols + kTilesPerItem - 1) / kTilesPerItem);
+    const uint32_t tiles = tiles_per_item(fs.planes * fs.tile_rows, fs.tile_cols, 4);
+    p.items = fs.planes * fs.tile_rows * ((fs.tile_cols + tiles - 1) / tiles);
     p.status = status;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (positions != nullptr) {
@@ -307,7 +323,11 @@ static int append_dispatch(const iomb_view* source, const iomb_view* destination
         }
     }
     const unsigned grid = grid_one_shot((p.items + kRowWarps - 1) / kRowWarps);
-    cache_append_kernel<<<grid, kRowThreads, 0, s>>>(p);
+    switch (tiles) {
+        case 4: cache_append_kernel<4><<<grid, kRowThreads, 0, s>>>(p); break;
+        case 2: cache_append_kernel<2><<<grid, kRowThreads, 0, s>>>(p); break;
+        default: cache_append_kernel<1><<<grid, kRowThreads, 0, s>>>(p); break;
+    }
     return check_launch("cache_append launch");
 }
 
@@ -410,7 +430,8 @@ extern "C" int iomb_embedding(const iomb_view* table, const iomb_view* indices,
     p.index_signed = index_signed ? 1u : 0u;
     p.vocabulary = ft.rows;
     p.run_tiles = static_cast<uint32_t>(fo.tile_rows);
-    p.items = p.leading.planes * fo.tile_rows * ((fo.tile_cols + kTilesPerItem - 1) / kTilesPerItem);
+    const uint32_t tiles = tiles_per_item(p.leading.planes * fo.tile_rows, fo.tile_cols, 8);
+    p.items = p.leading.planes * fo.tile_rows * ((fo.tile_cols + tiles - 1) / tiles);
     p.status = status;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     // Reset in queue order, as the reference does before its kernel
@@ -425,7 +446,12 @@ extern "C" int iomb_embedding(const iomb_view* table, const iomb_view* indices,
         return check_launch("embedding launch");
     }
     const unsigned grid = grid_one_shot((p.items + kRowWarps - 1) / kRowWarps);
-    embedding_kernel<<<grid, kRowThreads, 0, s>>>(p);
+    switch (tiles) {
+        case 8: embedding_kernel<8><<<grid, kRowThreads, 0, s>>>(p); break;
+        case 4: embedding_kernel<4><<<grid, kRowThreads, 0, s>>>(p); break;
+        case 2: embedding_kernel<2><<<grid, kRowThreads, 0, s>>>(p); break;
+        default: embedding_kernel<1><<<grid, kRowThreads, 0, s>>>(p); break;
+    }
     return check_launch("embedding launch");
 }
 
