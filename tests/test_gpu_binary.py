@@ -264,3 +264,37 @@ def test_binary_f64(gpu, op, numpy_op):
     mask.view().copy_from_host(np.full(shape, -1, dtype=np.int64))
     outside = mask.storage == 0
     assert np.array_equal(got.storage[outside], out.storage[outside])
+
+
+@pytest.mark.parametrize("op", ["add", "sub", "mul", "div"])
+def test_binary_bf16_every_pair_equals_one_rounded_binary32_operation(gpu, op):
+    """All 2^32 pairs of BF16 codes: the kernel's result (packed BF16 instructions for ADD,
+    SUB and MUL) equals RNE(binary32 operation) with every NaN canonical, which is what the
+    reference's codec computes (src/shared/scalar_binary_codec.hpp:45-178; equality of the
+    codec with one binary32 operation is shown on the CPU in test_layout_and_codec.py).
+    The binary32 side is evaluated by torch on the device, block by block: 2048 left codes
+    against all 65 536 right codes at a time, laid over the raw storage of tile-multiple
+    tensors (elementwise work pairs equal storage positions, whatever the tile map)."""
+    import torch
+
+    device, queue = gpu
+    block = 2048
+    spec = HostTensor((block, 65536), DataType.BF16, fill=None).spec
+    dl, dr, do = (device.create_tensor(spec) for _ in range(3))
+    right = torch.arange(65536, dtype=torch.int32, device=device.torch_device).to(torch.int16)
+    dr.storage().view(torch.int16).view(block, 65536).copy_(right.expand(block, 65536))
+    fn = {"add": torch.add, "sub": torch.sub, "mul": torch.mul, "div": torch.div}[op]
+    for first in range(0, 65536, block):
+        left = torch.arange(first, first + block, dtype=torch.int32, device=device.torch_device).to(torch.int16)
+        dl.storage().view(torch.int16).view(block, 65536).copy_(left.unsqueeze(1).expand(block, 65536))
+        run(queue, getattr(queue, op)(dl.view(), dr.view(), do.view()))
+        torch.cuda.synchronize()
+        a = dl.storage().view(torch.bfloat16).view(block, 65536).float()
+        b = dr.storage().view(torch.bfloat16).view(block, 65536).float()
+        want = fn(a, b).to(torch.bfloat16).view(torch.int16)
+        want = torch.where(torch.isnan(fn(a, b)), torch.full_like(want, 0x7FC0), want)
+        got = do.storage().view(torch.int16).view(block, 65536)
+        mismatches = int((got != want).sum().item())
+        assert mismatches == 0, f"{op}: {mismatches} pairs differ in the block of left codes {first}.."
+    for t in (dl, dr, do):
+        t.close()
