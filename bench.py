@@ -89,23 +89,35 @@ class ClockSampler:
     def __init__(self, index: int):
         self.index = index
         self.proc = None
-        self.lines = []
+        self.lines = []          # (arrival time, text)
+        self.begin = self.end = None
+
+    def mark_begin(self):
+        """The timed region starts here (the sampler itself was started earlier, so that
+        nvidia-smi is already reporting)."""
+        self.begin = time.monotonic()
+
+    def mark_end(self):
+        self.end = time.monotonic()
 
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
+            deadline = time.monotonic() + 2.0      # until nvidia-smi reports
+            while not self.lines and time.monotonic() < deadline:
+                time.sleep(0.01)
         except OSError:
             self.proc = None
         return self
 
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.monotonic(), line.strip()))
 
     def __exit__(self, *exc):
         if self.proc is not None:
@@ -119,7 +131,12 @@ class ClockSampler:
     def summary(self):
         clocks, maxima, reasons = [], [], set()
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        for line in self.lines:
+        for arrival, line in self.lines:
+            # A sample describes the interval before its arrival.
+            if self.begin is not None and arrival < self.begin + 0.01:
+                continue
+            if self.end is not None and arrival > self.end + 0.03:
+                continue
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 6:
                 continue
@@ -206,12 +223,14 @@ def run_ours(args) -> dict:
         torch.cuda.synchronize()
 
     # ---- device-resident throughput (`value`) -----------------------------
-    backend.run(step, passes=args.warmup)
-    kernel_name = (kernel_lib.iomb_last_launch() or b"").decode()
-    barrier()
     with ClockSampler(local_rank) as sampler:
+        backend.run(step, passes=args.warmup)
+        kernel_name = (kernel_lib.iomb_last_launch() or b"").decode()
+        barrier()
+        sampler.mark_begin()
         timing = backend.run(step, passes=args.steps)
         barrier()
+        sampler.mark_end()
     elapsed_ms = float(timing.device_ms)
     clocks = sampler.summary()
 
@@ -1067,7 +1086,7 @@ def run_reference(args) -> dict | None:
 def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--steps", type=int, default=40)
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
     parser.add_argument("--no-cpu-baseline", action="store_true")

@@ -74,8 +74,7 @@ constexpr int kLinearUnroll = 4;
 // CTAs, so the grid covers the whole stream.
 template <Leaf L, int OP>
 __global__ void __launch_bounds__(kLinearThreads)
-binary_linear_kernel(const uint4* __restrict__ lhs, const uint4* __restrict__ rhs,
-                     uint4* __restrict__ out, uint64_t vectors) {
+binary_linear_kernel(const uint4* lhs, const uint4* rhs, uint4* out, uint64_t vectors) {
     constexpr uint64_t kChunk = static_cast<uint64_t>(kLinearThreads) * kLinearUnroll;
     const uint64_t chunks = (vectors + kChunk - 1) / kChunk;
     for (uint64_t chunk = blockIdx.x; chunk < chunks; chunk += gridDim.x) {

@@ -171,13 +171,9 @@ __device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap* map, uint32_t
 // Units the L2 prefetch runs ahead of the copy into shared memory: the slots bound how far
 // the copies can run ahead (one unit), which leaves HBM idle while a copy's tail lands; the
 // prefetch keeps reads in flight across that gap.
+constexpr uint32_t kL2Ahead = 1;
 // Units a CTA works through in one launch (see launch_rmsnorm_long).
-#ifndef IOMB_RMS_UNITS_PER_CTA
-#define IOMB_RMS_UNITS_PER_CTA 96
-#endif
-#ifndef IOMB_RMS_L2_AHEAD
-#define IOMB_RMS_L2_AHEAD 1
-#endif
+constexpr uint32_t kUnitsPerCtaAndLaunch = 96;
 
 template <int ELEM, int G, bool FUSED>
 __global__ void __launch_bounds__(kLongThreads, 1)
@@ -313,8 +309,8 @@ rmsnorm_long_kernel(const RmsParams p, const LongShape shape, const __grid_const
                 }
             }
         }
-        if (IOMB_RMS_L2_AHEAD != 0 && k + IOMB_RMS_L2_AHEAD < count) {
-            const RmsUnit at = rms_locate<G>(p, unit_of(k + IOMB_RMS_L2_AHEAD));
+        if (kL2Ahead != 0 && k + kL2Ahead < count) {
+            const RmsUnit at = rms_locate<G>(p, unit_of(k + kL2Ahead));
             if (at.valid) {
                 const uint32_t x_band = static_cast<uint32_t>(
                         operand_plane(p.x, p.leading, at.index) * p.x.tile_rows + at.tr);
@@ -806,7 +802,7 @@ int launch_rmsnorm_long(const RmsParams& base, uint32_t elem, bool fused, uint64
     // rate of the same rows in launches of 32768. So a launch covers a bounded number of
     // units per CTA; the launches of one call follow one another on the stream.
     const uint64_t all_units = p.units;
-    const uint64_t per_launch = sms * IOMB_RMS_UNITS_PER_CTA;
+    const uint64_t per_launch = sms * kUnitsPerCtaAndLaunch;
     uint32_t launches = 0;
     for (uint64_t first = 0; first < all_units; first += per_launch, ++launches) {
         p.first_unit = first;

@@ -606,6 +606,17 @@ __device__ __forceinline__ uint32_t canonical_pair(uint32_t word) {
     return lo | (hi << 16);
 }
 
+// Non-zero when one of the word's two BF16 codes may need rewriting: an all-ones exponent
+// (infinity or NaN) or a zero magnitude with the sign set. Seven logic / add operations per
+// word; the exact rule (canonical_pair) then runs only on words that are flagged.
+__device__ __forceinline__ uint32_t suspicious_pair(uint32_t word) {
+    // 0x7f80 + 0x0080 reaches bit 15 exactly for an all-ones exponent (no carry across halves)
+    const uint32_t special = ((word & 0x7f807f80u) + 0x00800080u) & 0x80008000u;
+    // a magnitude m <= 0x7fff plus 0x7fff reaches bit 15 exactly when m != 0
+    const uint32_t nonzero = ((word & 0x7fff7fffu) + 0x7fff7fffu) & 0x80008000u;
+    return special | (word & ~nonzero & 0x80008000u);
+}
+
 __global__ void __launch_bounds__(kCanonThreads)
 canonicalize_kernel(const CanonParams p) {
     constexpr int kWarps = kCanonThreads / 32;
@@ -639,6 +650,10 @@ canonicalize_kernel(const CanonParams p) {
         for (uint32_t k = 0; k < kCanonTiles; ++k) {
             if (valid[k] == 0) continue;
             unsigned char* address = first + (tc0 + k) * 512ull;
+            if ((suspicious_pair(value[k].x) | suspicious_pair(value[k].y) | suspicious_pair(value[k].z)
+                 | suspicious_pair(value[k].w)) == 0) {
+                continue;
+            }
             const uint4 clean = make_uint4(canonical_pair(value[k].x), canonical_pair(value[k].y),
                                            canonical_pair(value[k].z), canonical_pair(value[k].w));
             if (valid[k] == 8) {
@@ -676,6 +691,11 @@ canonicalize_linear_kernel(unsigned char* data, uint64_t pairs) {
         for (int u = 0; u < kUnroll; ++u) {
             const uint64_t i = first + static_cast<uint64_t>(u) * kCanonThreads;
             if (i >= pairs) break;
+            if ((suspicious_pair(lo[u].x) | suspicious_pair(lo[u].y) | suspicious_pair(lo[u].z)
+                 | suspicious_pair(lo[u].w) | suspicious_pair(hi[u].x) | suspicious_pair(hi[u].y)
+                 | suspicious_pair(hi[u].z) | suspicious_pair(hi[u].w)) == 0) {
+                continue;
+            }
             const uint4 a = make_uint4(canonical_pair(lo[u].x), canonical_pair(lo[u].y),
                                        canonical_pair(lo[u].z), canonical_pair(lo[u].w));
             const uint4 b = make_uint4(canonical_pair(hi[u].x), canonical_pair(hi[u].y),
