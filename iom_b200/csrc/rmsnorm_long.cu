@@ -22,9 +22,10 @@
 //            alternate units and each has two units' time.
 //   emit     the mover warps normalise a chained unit from its slot and store it.
 //
-// Chain warps sit on warp schedulers of their own (warp w issues on scheduler w % 4); the
-// movers are the warps of the other schedulers and keep their part of the scale row in
-// registers. A unit is read from HBM exactly once; every loop walks with constant strides.
+// Unfused, chain warps sit on warp schedulers of their own (warp w issues on scheduler
+// w % 4) and the movers are the warps of the other schedulers; fused, where the movers do
+// twice the work, they are all warps but the chains' and the issuing thread's. Movers keep
+// their part of the scale row in registers. A unit is read from HBM exactly once; every loop walks with constant strides.
 //
 // Every wait is bounded: a wait that gives up sets a flag that ends all jobs of the CTA, and
 // the launch is counted in a device counter the host can read (iomb_rmsnorm_copy_timeouts).
@@ -77,9 +78,17 @@ __host__ __device__ constexpr uint32_t long_chain_warps(uint32_t g, bool fused) 
 __host__ __device__ constexpr uint32_t long_chains(uint32_t g, bool fused) {
     return fused && long_chain_warps(g, fused) == 1 ? 2 : 1;
 }
-// Movers: the warps of the schedulers without a chain warp (all other warps when every
-// scheduler has one), and the tiles they cover in one step of their walk.
+// Movers, and the tiles they cover in one step of their walk. Unfused: the warps of the
+// schedulers without a chain warp (all other warps when every scheduler has one).
+// The fused kernel's movers do twice the work per byte (add, then emit) and run on every
+// scheduler, beside the chain warps (all warps but the chains' and the issuing thread's:
+// measured +3-4 % on [262144, 8192] and [32768, 8192]); the unfused kernel's movers keep to
+// the schedulers without a chain warp (sharing them cost it 14 %).
+__host__ __device__ constexpr bool long_movers_everywhere(bool fused) { return fused; }
 __host__ __device__ constexpr uint32_t long_mover_warps(uint32_t g, bool fused) {
+    if (long_movers_everywhere(fused) && long_chain_warps(g, fused) * long_chains(g, fused) < 4) {
+        return kLongThreads / 32 - long_chain_warps(g, fused) * long_chains(g, fused) - 1;
+    }
     return long_chain_warps(g, fused) * long_chains(g, fused) < 4
             ? kLongThreads / 128 * (4 - long_chain_warps(g, fused) * long_chains(g, fused))
             : kLongThreads / 32 - 4;
@@ -172,8 +181,8 @@ __device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap* map, uint32_t
 // the copies can run ahead (one unit), which leaves HBM idle while a copy's tail lands; the
 // prefetch keeps reads in flight across that gap.
 constexpr uint32_t kL2Ahead = 1;
-// Units a CTA works through in one launch (see launch_rmsnorm_long).
-constexpr uint32_t kUnitsPerCtaAndLaunch = 96;
+// Most units a CTA works through in one launch (see launch_rmsnorm_long).
+constexpr uint32_t kUnitsPerCtaAndLaunch = 128;
 
 template <int ELEM, int G, bool FUSED>
 __global__ void __launch_bounds__(kLongThreads, 1)
@@ -194,8 +203,8 @@ rmsnorm_long_kernel(const RmsParams p, const LongShape shape, const __grid_const
     constexpr uint32_t kChainThreads = kChainWarps * 32;
     constexpr uint32_t kAllChainWarps = kChainWarps * kChains;
     // Warp w issues on scheduler w % 4. The chain warps are warps 0 .. kAllChainWarps - 1;
-    // the movers are the warps of the remaining schedulers (all other warps when every
-    // scheduler has a chain warp).
+    // the movers are the warps of the remaining schedulers (unfused) or every other warp
+    // but the issuing thread's (fused); all other warps when every scheduler has a chain warp.
     constexpr uint32_t kFreeSchedulers = kAllChainWarps < 4 ? 4 - kAllChainWarps : 0;
     constexpr uint32_t kMoverWarps = long_mover_warps(G, FUSED);
     constexpr uint32_t kMovers = kMoverWarps * 32;
@@ -238,7 +247,11 @@ rmsnorm_long_kernel(const RmsParams p, const LongShape shape, const __grid_const
     uint4 scale_regs[kScaleSteps];                           // movers, when shape.scale_in_regs
     // This thread's index among the movers, or kMovers when it is not one.
     uint32_t mover = kMovers;
-    if constexpr (kFreeSchedulers != 0) {
+    if constexpr (long_movers_everywhere(FUSED) && kFreeSchedulers != 0) {
+        if (warp >= kAllChainWarps && warp != 4) {
+            mover = (warp - kAllChainWarps - (warp > 4 ? 1u : 0u)) * 32 + lane;
+        }
+    } else if constexpr (kFreeSchedulers != 0) {
         if ((warp & 3u) >= kAllChainWarps) {
             mover = ((warp >> 2) * kFreeSchedulers + (warp & 3u) - kAllChainWarps) * 32 + lane;
         }
@@ -800,9 +813,12 @@ int launch_rmsnorm_long(const RmsParams& base, uint32_t elem, bool fused, uint64
     // the 64- or 128-byte pieces of one tile are fetched at different times and DRAM opens a
     // row for each piece: measured on [262144, 8192] BF16, one launch ran at 0.55 of the
     // rate of the same rows in launches of 32768. So a launch covers a bounded number of
-    // units per CTA; the launches of one call follow one another on the stream.
+    // units per CTA (equal launches: a short last one would run at a lower rate); the
+    // launches of one call follow one another on the stream.
     const uint64_t all_units = p.units;
-    const uint64_t per_launch = sms * kUnitsPerCtaAndLaunch;
+    const uint64_t per_cta = (all_units + sms - 1) / sms;
+    const uint64_t parts = (per_cta + kUnitsPerCtaAndLaunch - 1) / kUnitsPerCtaAndLaunch;
+    const uint64_t per_launch = sms * ((per_cta + parts - 1) / parts);     // equal launches
     uint32_t launches = 0;
     for (uint64_t first = 0; first < all_units; first += per_launch, ++launches) {
         p.first_unit = first;

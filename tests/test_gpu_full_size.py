@@ -10,6 +10,7 @@ through properties that do not need a CPU pass over gigabytes:
 
 Comparisons of whole tensors run on the device (torch.equal on the storage bytes)."""
 import ctypes
+import re
 
 import numpy as np
 import pytest
@@ -116,6 +117,58 @@ def test_rmsnorm_at_the_sharded_size(big):
         t.close()
     scratch.close()
     cell.close()
+
+
+def test_long_rows_issued_as_several_launches(big):
+    """BF16 [81920 + 16, 8192], eps 1e-6: more row groups than one launch of the long-row
+    kernel takes per SM, so the call is issued as several launches (the fused form with its
+    half-height groups as more of them). 320 copies of a 256-row pattern plus one ragged
+    16-row band: every copy must equal the oracle's result for the pattern, and the fused
+    entry must equal add then rmsnorm on the whole tensor."""
+    device, queue = big
+    rng = np.random.default_rng(103)
+    pattern, copies = (256, 8192), 320
+    hx, hr, hs, ho = (HostTensor(pattern, DataType.BF16) for _ in range(4))
+    hx.view().copy_from_host(random_payload(rng, pattern, DataType.BF16, "normal"))
+    hr.view().copy_from_host(random_payload(rng, pattern, DataType.BF16, "normal"))
+    hw = HostTensor((1, 8192), DataType.BF16)
+    hw.view().copy_from_host(f32_to_bf16_bits((1.0 + 0.02 * rng.standard_normal((1, 8192))).astype(np.float32)))
+    rows = copies * 256 + 16
+    shape = (rows, 8192)
+    band = 16 * 8192 * 2
+
+    def replicated(host):
+        tensor = device.create_tensor(TensorSpec(shape, DataType.BF16))
+        piece = torch.from_numpy(host.storage.copy()).to(device.torch_device)
+        body = tensor.storage()[:copies * piece.numel()]
+        body.view(copies, piece.numel()).copy_(piece.unsqueeze(0).expand(copies, -1))
+        tensor.storage()[copies * piece.numel():].copy_(piece[:band])     # the last band: rows 0..15
+        return tensor
+
+    x, r = replicated(hx), replicated(hr)
+    w = device.create_tensor(hw.spec)
+    w.storage().copy_(torch.from_numpy(hw.storage.copy()))
+    total, out, total2, out2 = (device.create_tensor(TensorSpec(shape, DataType.BF16)) for _ in range(4))
+    torch.cuda.synchronize()
+    run(queue, queue.add_rmsnorm(x.view(), r.view(), w.view(), total.view(), out.view(), 1e-6))
+    launched = (device._lib.iomb_last_launch() or b"").decode()
+    assert "rmsnorm_long_kernel" in launched, launched
+    assert int(re.search(r"(\d+) launch\(es\)", launched).group(1)) > 1, launched
+    assert oracle().iomo_binary(0, abi(hx.view()), abi(hr.view()), abi(hs.view()), 0) == 0
+    assert oracle().iomo_rmsnorm(abi(hs.view()), abi(hw.view()), abi(ho.view()), 1e-6, 0) == 0
+    for got, host in ((total, hs), (out, ho)):
+        want = torch.from_numpy(host.storage.copy()).to(device.torch_device)
+        body = got.storage()[:copies * want.numel()].view(copies, -1)
+        assert torch.equal(body, want.unsqueeze(0).expand(copies, -1))
+        assert torch.equal(got.storage()[copies * want.numel():], want[:band])
+    run(queue, queue.add(x.view(), r.view(), total2.view()))
+    run(queue, queue.rmsnorm(total2.view(), w.view(), out2.view(), 1e-6))
+    assert torch.equal(total.storage(), total2.storage())
+    assert torch.equal(out.storage(), out2.storage())
+    count = ctypes.c_uint(1)
+    assert device._lib.iomb_rmsnorm_copy_timeouts(ctypes.byref(count)) == 0 and count.value == 0
+    for t in (x, r, w, total, out, total2, out2):
+        t.close()
 
 
 @pytest.mark.parametrize("dtype,op", [(DataType.F32, "mul"), (DataType.I32, "add"), (DataType.BF16, "add")])
