@@ -198,7 +198,7 @@ def run_ours(args) -> dict:
     tensor_bytes = elements * ELEM
     kernel_lib = _abi.load_library()
     # Arena: the shard's four tensors, the host-transfer staging range, small change.
-    arena = 4 * tensor_bytes + (0 if args.no_e2e else tensor_bytes + (1 << 20)) + (256 << 20)
+    arena = 4 * tensor_bytes + (0 if args.no_e2e else 3 * tensor_bytes + (1 << 20)) + (256 << 20)
     backend = bd.Backend(local_rank, arena)
     x, r, total, out = (backend.tensor((rows, HIDDEN), DataType.BF16) for _ in range(4))
     scale = backend.tensor((1, HIDDEN), DataType.BF16)
@@ -236,6 +236,7 @@ def run_ours(args) -> dict:
 
     # ---- end to end through the public interface with host buffers (`e2e`) -------
     e2e_ms = float("nan")
+    e2e_sync_ms = float("nan")
     e2e_submit_us = None
     if not args.no_e2e:
         pinned = {name: torch.empty(tensor_bytes, dtype=torch.uint8, pin_memory=True)
@@ -245,21 +246,81 @@ def run_ours(args) -> dict:
         pinned["x"].copy_(backend.storage(x))
         pinned["r"].copy_(backend.storage(r))
         staging = backend.workspace(tensor_bytes + 64)
-        e2e_program = [
-            bd.Backend.op(bd.FROM_HOST, [vx], workspace=staging, host=pinned["x"].data_ptr(),
-                          host_bytes=tensor_bytes),
-            bd.Backend.op(bd.FROM_HOST, [vr], workspace=staging, host=pinned["r"].data_ptr(),
-                          host_bytes=tensor_bytes),
-            bd.Backend.op(bd.ADD_RMSNORM, [vx, vr, vw, vt, vo], eps=EPS),
-            bd.Backend.op(bd.WAIT),
-            bd.Backend.op(bd.TO_HOST, [vo], workspace=staging, host=pinned["out"].data_ptr(),
-                          host_bytes=tensor_bytes),
-        ]
-        backend.run(e2e_program, passes=1)
+        staging_down = backend.workspace(tensor_bytes + 64)
+        out_b = backend.tensor((rows, HIDDEN), DataType.BF16)
+        outs = [vo, backend.view(out_b)]
+
+        def upload_and_compute(destination):
+            return [
+                bd.Backend.op(bd.FROM_HOST, [vx], workspace=staging, host=pinned["x"].data_ptr(),
+                              host_bytes=tensor_bytes),
+                bd.Backend.op(bd.FROM_HOST, [vr], workspace=staging, host=pinned["r"].data_ptr(),
+                              host_bytes=tensor_bytes),
+                bd.Backend.op(bd.ADD_RMSNORM, [vx, vr, vw, vt, destination], eps=EPS),
+                bd.Backend.op(bd.WAIT),
+            ]
+
+        def download(source):
+            return [bd.Backend.op(bd.TO_HOST, [source], workspace=staging_down,
+                                  host=pinned["out"].data_ptr(), host_bytes=tensor_bytes)]
+
+        # (a) One host thread, the contract's synchronous calls one after another.
+        synchronous = upload_and_compute(vo) + download(vo)
+        backend.run(synchronous, passes=1)
         barrier()
-        e2e_timing = backend.run(e2e_program, passes=args.steps)
+        sync_steps = min(args.steps, 8)
+        sync_timing = backend.run(synchronous, passes=sync_steps)
         barrier()
-        e2e_ms = e2e_timing.host_seconds * 1e3
+        e2e_sync_ms = sync_timing.host_seconds * 1e3 / sync_steps
+
+        # (b) The same synchronous calls from two host threads: one uploads and computes
+        # step s + 1 while the other reads the result of step s back (two output tensors
+        # in turn), so both directions of the host link are busy. Every step still moves
+        # its inputs in and its result out inside the timed region.
+        failures = []
+        computed = [threading.Semaphore(0), threading.Semaphore(0)]
+        drained = [threading.Semaphore(1), threading.Semaphore(1)]
+
+        def producer(count):
+            try:
+                for s_index in range(count):
+                    drained[s_index % 2].acquire()
+                    backend.run(upload_and_compute(outs[s_index % 2]), passes=1)
+                    computed[s_index % 2].release()
+            except Exception as error:          # noqa: BLE001 - reported by the main thread
+                failures.append(error)
+                for semaphore in computed:
+                    semaphore.release()
+
+        def consumer(count):
+            try:
+                for s_index in range(count):
+                    computed[s_index % 2].acquire()
+                    if failures:
+                        return
+                    backend.run(download(outs[s_index % 2]), passes=1)
+                    drained[s_index % 2].release()
+            except Exception as error:          # noqa: BLE001
+                failures.append(error)
+                for semaphore in drained:
+                    semaphore.release()
+
+        def pipelined(count):
+            threads = [threading.Thread(target=producer, args=(count,)),
+                       threading.Thread(target=consumer, args=(count,))]
+            begin = time.perf_counter()
+            for thread in threads:
+                thread.start()
+            for thread in threads:
+                thread.join()
+            if failures:
+                raise failures[0]
+            return (time.perf_counter() - begin) * 1e3
+
+        pipelined(2)
+        barrier()
+        e2e_ms = pipelined(args.steps)
+        barrier()
 
     # ---- whole-tensor sum of squares across ranks (the one exchange step) ----
     sumsq_bytes = 32 + int(kernel_lib.iomb_sumsq_scratch_bytes())
@@ -296,10 +357,10 @@ def run_ours(args) -> dict:
     if world == 1 and not args.no_ops:
         table = ops_table_all(local_rank)
 
-    times = torch.tensor([elapsed_ms, e2e_ms], dtype=torch.float64, device="cuda")
+    times = torch.tensor([elapsed_ms, e2e_ms, e2e_sync_ms], dtype=torch.float64, device="cuda")
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    elapsed_ms, e2e_ms = (float(v) for v in times.tolist())
+    elapsed_ms, e2e_ms, e2e_sync_ms = (float(v) for v in times.tolist())
 
     result = None
     if rank == 0:
@@ -347,10 +408,15 @@ def run_ours(args) -> dict:
                     "h2d_bytes_per_step": 2 * ROWS * HIDDEN * ELEM,
                     "d2h_bytes_per_step": ROWS * HIDDEN * ELEM,
                     "steps": args.steps,
+                    "synchronous_value": (total_bytes / e2e_sync_ms / 1e6
+                                          if e2e_sync_ms == e2e_sync_ms else None),
                     "path": "C++ backend through the reference's public interface, every step: "
                             "TensorView::copy_from_host(x), copy_from_host(residual), "
                             "b200::add_rmsnorm, wait, copy_to_host(out); pinned host buffers in the "
-                            "logical row-major layout; host wall clock, max over ranks"},
+                            "logical row-major layout; host wall clock over all steps, max over ranks. "
+                            "`value`: those synchronous calls from two host threads (one uploads and "
+                            "computes step s+1 while the other reads step s back, two output tensors in "
+                            "turn); `synchronous_value`: one thread, one call after another"},
             "gpu_launches": args.steps * launches_per_step,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": traffic,

@@ -195,12 +195,15 @@ public:
             allocator_ = std::make_unique<ListAllocator>(arena_, arena_bytes_, 256);
             check_cuda("cudaStreamCreate(transfer)",
                        cudaStreamCreateWithFlags(&transfer_stream_, cudaStreamNonBlocking));
+            check_cuda("cudaStreamCreate(download)",
+                       cudaStreamCreateWithFlags(&download_stream_, cudaStreamNonBlocking));
             // One-time set-up of the kernel library on this device (function attributes,
             // the BF16 SiLU table), so that no operation does it later.
             check_status(iomb_prepare_device(transfer_stream_));
             check_cuda("cudaStreamSynchronize(set-up)", cudaStreamSynchronize(transfer_stream_));
         } catch (...) {
             if (transfer_stream_ != nullptr) (void)cudaStreamDestroy(transfer_stream_);
+            if (download_stream_ != nullptr) (void)cudaStreamDestroy(download_stream_);
             if (rotary_ != nullptr) (void)cudaFree(rotary_);
             (void)cudaFree(arena_);
             throw;
@@ -209,6 +212,7 @@ public:
 
     ~B200Device() override {
         if (transfer_stream_ != nullptr) (void)cudaStreamDestroy(transfer_stream_);
+        if (download_stream_ != nullptr) (void)cudaStreamDestroy(download_stream_);
         // Parked storage goes back to the allocator while the allocator still exists
         // (src/cuda/device.cpp:106-116).
         registry_state_.quarantine.drain();
@@ -241,6 +245,11 @@ public:
     }
     [[nodiscard]] Allocator& data_allocator() noexcept { return *allocator_; }
     [[nodiscard]] cudaStream_t transfer_stream() const noexcept { return transfer_stream_; }
+    // Device-to-host transfers have a stream and a lock of their own, so that a thread
+    // reading results back and a thread uploading the next inputs use both directions of
+    // the link at once (each call is still synchronous for its caller).
+    [[nodiscard]] cudaStream_t download_stream() const noexcept { return download_stream_; }
+    [[nodiscard]] std::mutex& download_mutex() noexcept { return download_mutex_; }
     [[nodiscard]] std::mutex& transfer_mutex() noexcept { return transfer_mutex_; }
 
     // Rotary cache: device table of (cos, sin) for positions 0 .. rows-1 of one
@@ -302,6 +311,8 @@ private:
     std::unique_ptr<ListAllocator> allocator_;
     std::mutex allocator_mutex_;
     cudaStream_t transfer_stream_ = nullptr;
+    cudaStream_t download_stream_ = nullptr;
+    std::mutex download_mutex_;
     std::mutex transfer_mutex_;
     detail::RegistryState registry_state_;
     struct RopeTable {
@@ -433,10 +444,10 @@ private:
 
     void region_to_host(const TensorView& source, std::span<std::byte> destination,
                         RawWorkspaceView workspace) const override {
-        std::lock_guard<std::mutex> lock(device_.transfer_mutex());
+        std::lock_guard<std::mutex> lock(device_.download_mutex());
         device_.activate();
         void* staging = staging_address(device_, workspace, destination.size());
-        const cudaStream_t stream = device_.transfer_stream();
+        const cudaStream_t stream = device_.download_stream();
         const iomb_view view = to_view(source);
         check_status(iomb_gather(&view, staging, stream));
         check_cuda("cudaMemcpyAsync(D2H)",
