@@ -44,12 +44,12 @@ ROWS, HIDDEN, EPS = 262144, 8192, 1e-6
 ELEM = 2
 METRIC = "achieved HBM GB/s, fused residual ADD + RMSNorm (BF16 [262144,8192], row-sharded)"
 # dram__bytes_read.sum and dram__bytes_write.sum of one launch of the kernel the step runs,
-# from the ncu capture summarised in profiles/add_rmsnorm_bf16_long_rows.md (the first
-# launch of a [32768,8192] shard: 28416 rows, 1.86 GB, 15 times the L2). Reads are
-# proportional to the rows. Writes are the algorithmic bytes less the lines still dirty in
-# L2 when the launch ends, which does not grow with the rows.
-NCU_READ_BYTES_PER_ROW = 937082112 / 28416       # dram__bytes_read.sum of a 28416-row launch
-NCU_WRITES_LEFT_IN_L2_BYTES = 28416 * 2 * 8192 * 2 - 882120192   # algorithmic - dram__bytes_write.sum
+# from the ncu capture summarised in profiles/add_rmsnorm_bf16_long_rows.md (a [32768,8192]
+# shard in one launch: 2.15 GB, 17 times the L2). Reads are proportional to the rows. Writes
+# are the algorithmic bytes less the lines still dirty in L2 when the launch ends, which
+# does not grow with the rows.
+NCU_READ_BYTES_PER_ROW = 1075119000 / 32768      # dram__bytes_read.sum of the 32768-row launch
+NCU_WRITES_LEFT_IN_L2_BYTES = 32768 * 2 * 8192 * 2 - 1026173000   # algorithmic - dram__bytes_write.sum
 
 
 def configure(rows: int) -> None:
@@ -514,6 +514,40 @@ def backend_sequences(ordinal: int) -> dict:
     # A decode step ends with the host reading the result: the step's tokens are collected
     # (which also returns the embedding's status-word lease before the next step).
     program.append(op(bd.WAIT))
+    # The decode step's single operations and the other launches that last a few
+    # microseconds, issued back to back from C++ (the per-operation table times them through
+    # the Python mirror, whose submission costs more than these kernels run).
+    logits = backend.tensor((batch, 32000), DataType.BF16)
+    wide = backend.tensor((batch, 32000), DataType.F32)
+    a_c1, o_c1 = (backend.tensor((4096, 2048), DataType.F32) for _ in range(2))
+    bias_c1 = backend.tensor((1, 2048), DataType.F32)
+    k_big = backend.tensor((batch, heads, 2048, 64), DataType.BF16)
+    cache_big = backend.tensor((batch, heads, 4096, 64), DataType.BF16)
+    singles = [
+        ("embedding_decode_cpp", [op(bd.EMBEDDING, [V["table"], V["ids"], V["h"]], workspace=status_ws),
+                                  op(bd.WAIT)],
+         2 * batch * hidden * 2 + batch * 4 + 4, "table [32000,2048], 64 ids; waited for each time (the "
+                                                 "status word is a lease)"),
+        ("cache_append_decode_batched_cpp",
+         [op(bd.CACHE_APPEND_BATCHED, [V["k"], V["k_cache"]], workspace=control)],
+         2 * batch * heads * 64 * 2, "K [64,4,1,64] -> cache [64,4,512,64], one call"),
+        ("cast_logits_cpp", [op(bd.CAST, [backend.view(logits), backend.view(wide)])],
+         batch * 32000 * 6, "[64,32000] BF16 -> F32"),
+        ("add_f32_row_config1_cpp",
+         [op(bd.ADD, [backend.view(a_c1), backend.view(bias_c1), backend.view(o_c1)])],
+         2 * 4096 * 2048 * 4 + 2048 * 4, "[4096,2048] + [1,2048], one buffer set (L2-resident)"),
+        ("cache_append_prefill_cpp",
+         [op(bd.CACHE_APPEND, [backend.view(k_big), backend.view(cache_big)], a=1024)],
+         2 * batch * heads * 2048 * 64 * 2, "K [64,4,2048,64] -> cache [64,4,4096,64] at row 1024"),
+        ("rmsnorm_decode_cpp", [op(bd.RMSNORM, [V["h"], V["w"], V["normed"]], eps=1e-5)],
+         2 * batch * hidden * 2, "[64,2048] BF16"),
+    ]
+    for name, single, nbytes, note in singles:
+        timing = backend.run(single, passes=200, warmup=20)
+        results[name] = {
+            "us": timing.device_ms * 1e3 / 200, "GB/s": nbytes / (timing.device_ms / 200) / 1e6,
+            "host_us_per_submission": timing.submit_seconds * 1e6 / 200,
+            "note": note + "; 200 launches back to back from C++, CUDA events around them"}
     launches = sum(1 for record in program if record.opcode != bd.WAIT)
     for name, mode in (("decode_step_eager_cpp", bd.EAGER), ("decode_step_recorded_cpp", bd.RECORDED)):
         plain = [record for record in program if record.opcode != bd.WAIT] if mode == bd.RECORDED else program
