@@ -287,6 +287,7 @@ def test_binary_bf16_every_pair_equals_one_rounded_binary32_operation(gpu, op):
     for first in range(0, 65536, block):
         left = torch.arange(first, first + block, dtype=torch.int32, device=device.torch_device).to(torch.int16)
         dl.storage().view(torch.int16).view(block, 65536).copy_(left.unsqueeze(1).expand(block, 65536))
+        torch.cuda.synchronize()      # the fills ran on torch's stream, the operation uses the queue's
         run(queue, getattr(queue, op)(dl.view(), dr.view(), do.view()))
         torch.cuda.synchronize()
         a = dl.storage().view(torch.bfloat16).view(block, 65536).float()
