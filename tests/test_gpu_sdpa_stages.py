@@ -125,7 +125,20 @@ MANY_ROWS = [
 ]
 
 
-@pytest.mark.parametrize("geometry", GEOMETRIES + MANY_ROWS)
+# Thousands of rows of up to 2048 tokens, fewer or longer than the one-lane-per-row kernel
+# takes: many groups per CTA of the grouped kernel (ragged prefixes; L < a + R; decode-like
+# single rows per head).
+PIPELINED = [
+    (1, 32, 4, 100, 1200, 64, 1000, 1100),
+    (2, 16, 4, 64, 700, 32, 600, 640),
+    (1, 16, 2, 128, 2048, 64, 1920, 2048),
+    (1, 16, 4, 128, 300, 16, 100, 228),
+    (1, 8, 8, 300, 2048, 64, 0, 300),
+    (2000, 1, 1, 1, 2047, 8, 2040, 2041),
+]
+
+
+@pytest.mark.parametrize("geometry", GEOMETRIES + MANY_ROWS + PIPELINED)
 def test_stages_against_the_oracle(gpu, geometry):
     device, queue = gpu
     host = random_case(11, *geometry)
@@ -151,7 +164,7 @@ def test_stages_against_the_oracle(gpu, geometry):
     ds.close()
 
 
-@pytest.mark.parametrize("geometry", GEOMETRIES + MANY_ROWS)
+@pytest.mark.parametrize("geometry", GEOMETRIES + MANY_ROWS + PIPELINED)
 def test_stages_bit_identical_to_the_reference_kernels(gpu, geometry):
     lib = sdpa_reference_stages_or_skip()
     device, queue = gpu
@@ -172,7 +185,7 @@ def test_stages_bit_identical_to_the_reference_kernels(gpu, geometry):
 
 
 @pytest.mark.parametrize("keep", [False, True])
-@pytest.mark.parametrize("geometry", GEOMETRIES[:5] + MANY_ROWS)
+@pytest.mark.parametrize("geometry", GEOMETRIES[:5] + MANY_ROWS + PIPELINED)
 def test_fused_stage_equals_the_two_launches(gpu, geometry, keep):
     device, queue = gpu
     host = random_case(13, *geometry)
@@ -281,3 +294,4 @@ def test_rejections(gpu):
     assert queue.sdpa_canonicalize_output(f32.view()) < 0
     f32.close()
     workspace.close()
+
