@@ -18,14 +18,15 @@
 //            32- or 64-bit load per tile, one packed product, one packed FP32 addition),
 //            then the fixed tree and the row's inverse. This is the latency-bound part (one
 //            dependent addition per tile, whatever G is). When a unit is so small that one
-//            chain no longer keeps up with HBM (fused, G <= 4), two chain warps take
-//            alternate units and each has two units' time.
+//            chain no longer keeps up with HBM (G <= 2: long rows, or the fused kernel's
+//            half-height units), two or three chain warps take alternate units and each
+//            has that many units' time.
 //   emit     the mover warps normalise a chained unit from its slot and store it.
 //
-// Unfused, chain warps sit on warp schedulers of their own (warp w issues on scheduler
-// w % 4) and the movers are the warps of the other schedulers; fused, where the movers do
-// twice the work, they are all warps but the chains' and the issuing thread's. Movers keep
-// their part of the scale row in registers. A unit is read from HBM exactly once; every loop walks with constant strides.
+// With one chain of an unfused kernel, the chain warps sit on warp schedulers of their own
+// (warp w issues on scheduler w % 4) and the movers are the warps of the other schedulers;
+// fused, where the movers do twice the work, and with several chains, they are all warps but
+// the chains' and the issuing thread's. Movers keep their part of the scale row in registers. A unit is read from HBM exactly once; every loop walks with constant strides.
 //
 // Every wait is bounded: a wait that gives up sets a flag that ends all jobs of the CTA, and
 // the launch is counted in a device counter the host can read (iomb_rmsnorm_copy_timeouts).
@@ -69,46 +70,54 @@ __device__ __forceinline__ void square_add_pair(float& a0, float& a1, float x0, 
 // Geometry shared by the kernel and its launcher, for groups of g rows.
 // Columns a chain thread owns (one while the chain then still fits two warps: a thread's
 // step is then a load, a decode, a product and the dependent addition, the shortest there
-// is; two neighbouring columns with packed arithmetic otherwise), the warps of one chain,
-// and chains that run side by side on alternate units:
+// is; two neighbouring columns with packed arithmetic otherwise), and the warps of one chain:
 __host__ __device__ constexpr uint32_t long_chain_pack(uint32_t g, bool) { return g <= 4 ? 1 : 2; }
 __host__ __device__ constexpr uint32_t long_chain_warps(uint32_t g, bool fused) {
     return (g * kTile / long_chain_pack(g, fused) + 31) / 32;
 }
-__host__ __device__ constexpr uint32_t long_chains(uint32_t g, bool fused) {
-    return fused && long_chain_warps(g, fused) == 1 ? 2 : 1;
+// Chains that run side by side on alternate units: the time of a chain per unit does not
+// shrink with g (one dependent addition per tile of the row) while the unit's HBM time does,
+// so small groups need several (only chains of one warp are multiplied: g <= 2).
+constexpr uint32_t kMaxChains = 3;
+// (three chains were measured slower than two for the fused kernel: 0.63 against 0.69 of the
+// copy peak at 12288 features, where both fit)
+__host__ __device__ constexpr uint32_t long_most_chains(uint32_t g, bool fused) {
+    return long_chain_warps(g, fused) == 1 ? (fused ? 2 : kMaxChains) : 1;
 }
-// Movers, and the tiles they cover in one step of their walk. Unfused: the warps of the
-// schedulers without a chain warp (all other warps when every scheduler has one).
-// The fused kernel's movers do twice the work per byte (add, then emit) and run on every
-// scheduler, beside the chain warps (all warps but the chains' and the issuing thread's:
-// measured +3-4 % on [262144, 8192] and [32768, 8192]); the unfused kernel's movers keep to
-// the schedulers without a chain warp (sharing them cost it 14 %).
-__host__ __device__ constexpr bool long_movers_everywhere(bool fused) { return fused; }
-__host__ __device__ constexpr uint32_t long_mover_warps(uint32_t g, bool fused) {
-    if (long_movers_everywhere(fused) && long_chain_warps(g, fused) * long_chains(g, fused) < 4) {
-        return kLongThreads / 32 - long_chain_warps(g, fused) * long_chains(g, fused) - 1;
+// Movers, and the tiles they cover in one step of their walk. With one chain of an unfused
+// kernel they are the warps of the schedulers without a chain warp (sharing them cost that
+// kernel 14 %; all other warps when every scheduler has a chain warp). The fused kernel's
+// movers do twice the work per byte (add, then emit: measured +3-4 % on [262144, 8192] and
+// [32768, 8192]), and kernels with several chains leave few schedulers free: there the movers
+// are all warps but the chains' and the issuing thread's.
+__host__ __device__ constexpr bool long_movers_everywhere(bool fused, uint32_t chains) {
+    return fused || chains > 1;
+}
+__host__ __device__ constexpr uint32_t long_mover_warps(uint32_t g, bool fused, uint32_t chains) {
+    if (long_movers_everywhere(fused, chains) && long_chain_warps(g, fused) * chains < 4) {
+        return kLongThreads / 32 - long_chain_warps(g, fused) * chains - 1;
     }
-    return long_chain_warps(g, fused) * long_chains(g, fused) < 4
-            ? kLongThreads / 128 * (4 - long_chain_warps(g, fused) * long_chains(g, fused))
+    return long_chain_warps(g, fused) * chains < 4
+            ? kLongThreads / 128 * (4 - long_chain_warps(g, fused) * chains)
             : kLongThreads / 32 - 4;
 }
-__host__ __device__ constexpr uint32_t long_move_tiles_per_step(uint32_t elem, uint32_t g, bool fused) {
-    return long_mover_warps(g, fused) * 32 / (g * kTile * elem / 16);
+__host__ __device__ constexpr uint32_t long_move_tiles_per_step(uint32_t elem, uint32_t g, bool fused,
+                                                                uint32_t chains) {
+    return long_mover_warps(g, fused, chains) * 32 / (g * kTile * elem / 16);
 }
 // Slots of x: a unit holds its slot from the copy (one unit ahead) through the add (fused),
 // the chain (one unit's time per chain) and the emit. The residual has two slots of its own.
-__host__ __device__ constexpr uint32_t long_x_slots(uint32_t g, bool fused) {
-    return fused ? 3 + long_chains(g, fused) : 3;
+__host__ __device__ constexpr uint32_t long_x_slots(bool fused, uint32_t chains) {
+    return fused ? 3 + chains : 2 + chains;
 }
-__host__ __device__ constexpr uint32_t long_slots(uint32_t g, bool fused) {
-    return long_x_slots(g, fused) + (fused ? 2 : 0);
+__host__ __device__ constexpr uint32_t long_slots(bool fused, uint32_t chains) {
+    return long_x_slots(fused, chains) + (fused ? 2 : 0);
 }
 // Shared memory besides the slots: the chains' lane sums, per slot 16 inverses and 16
 // flags, two flag words, four mbarriers per slot.
-__host__ __device__ constexpr uint32_t long_fixed_bytes(uint32_t g, bool fused) {
-    return long_chains(g, fused) * g * kTile * 4 + long_x_slots(g, fused) * (16 * 4 + 16 * 4) + 16
-            + long_x_slots(g, fused) * 4 * 8;
+__host__ __device__ constexpr uint32_t long_fixed_bytes(uint32_t g, bool fused, uint32_t chains) {
+    return chains * g * kTile * 4 + long_x_slots(fused, chains) * (16 * 4 + 16 * 4) + 16
+            + long_x_slots(fused, chains) * 4 * 8;
 }
 // A mover keeps the scale vectors of the tiles it walks in registers when its walk has at
 // most this many steps (the scale depends on the column only, so one load serves every unit).
@@ -184,7 +193,7 @@ constexpr uint32_t kL2Ahead = 1;
 // Most units a CTA works through in one launch (see launch_rmsnorm_long).
 constexpr uint32_t kUnitsPerCtaAndLaunch = 128;
 
-template <int ELEM, int G, bool FUSED>
+template <int ELEM, int G, bool FUSED, int CHAINS>
 __global__ void __launch_bounds__(kLongThreads, 1)
 rmsnorm_long_kernel(const RmsParams p, const LongShape shape, const __grid_constant__ CUtensorMap x_map,
                     const __grid_constant__ CUtensorMap r_map) {
@@ -199,23 +208,23 @@ rmsnorm_long_kernel(const RmsParams p, const LongShape shape, const __grid_const
     constexpr uint32_t kPack = long_chain_pack(G, FUSED);           // columns per chain thread
     constexpr uint32_t kPairs = G * kTile / kPack;           // threads of a chain
     constexpr uint32_t kChainWarps = long_chain_warps(G, FUSED);    // 1, 2 or 4
-    constexpr uint32_t kChains = long_chains(G, FUSED);      // chains on alternate units
+    constexpr uint32_t kChains = CHAINS;                     // chains on alternate units
     constexpr uint32_t kChainThreads = kChainWarps * 32;
     constexpr uint32_t kAllChainWarps = kChainWarps * kChains;
     // Warp w issues on scheduler w % 4. The chain warps are warps 0 .. kAllChainWarps - 1;
     // the movers are the warps of the remaining schedulers (unfused) or every other warp
     // but the issuing thread's (fused); all other warps when every scheduler has a chain warp.
     constexpr uint32_t kFreeSchedulers = kAllChainWarps < 4 ? 4 - kAllChainWarps : 0;
-    constexpr uint32_t kMoverWarps = long_mover_warps(G, FUSED);
+    constexpr uint32_t kMoverWarps = long_mover_warps(G, FUSED, CHAINS);
     constexpr uint32_t kMovers = kMoverWarps * 32;
     static_assert(kMovers % kPieceVectors == 0,
                   "a thread keeps one vector position of every tile it touches");
     constexpr uint32_t kIssuer = 128;                        // warp 4: no other job, or the first mover
-    constexpr uint32_t kMoveTilesPerStep = long_move_tiles_per_step(ELEM, G, FUSED);
+    constexpr uint32_t kMoveTilesPerStep = long_move_tiles_per_step(ELEM, G, FUSED, CHAINS);
     static_assert(kMoveTilesPerStep == kMovers / kPieceVectors, "the launcher sizes the walk alike");
     // The pipeline, in units: the copy runs kCopyAhead units ahead of the movers' step; the
     // emit follows kLag units behind it (the chains' time, plus the add's when fused).
-    constexpr uint32_t kSlots = long_x_slots(G, FUSED);
+    constexpr uint32_t kSlots = long_x_slots(FUSED, CHAINS);
     constexpr uint32_t kResidualSlots = FUSED ? 2 : 0;
     constexpr uint32_t kCopyAhead = 1;
     constexpr uint32_t kLag = FUSED ? kChains + 1 : kChains;
@@ -247,7 +256,7 @@ rmsnorm_long_kernel(const RmsParams p, const LongShape shape, const __grid_const
     uint4 scale_regs[kScaleSteps];                           // movers, when shape.scale_in_regs
     // This thread's index among the movers, or kMovers when it is not one.
     uint32_t mover = kMovers;
-    if constexpr (long_movers_everywhere(FUSED) && kFreeSchedulers != 0) {
+    if constexpr (long_movers_everywhere(FUSED, CHAINS) && kFreeSchedulers != 0) {
         if (warp >= kAllChainWarps && warp != 4) {
             mover = (warp - kAllChainWarps - (warp > 4 ? 1u : 0u)) * 32 + lane;
         }
@@ -702,23 +711,31 @@ rmsnorm_long_kernel(const RmsParams p, const LongShape shape, const __grid_const
 using LongKernel = void (*)(const RmsParams, const LongShape, const CUtensorMap, const CUtensorMap);
 
 template <int ELEM, bool FUSED>
-static LongKernel pick_long(uint32_t g) {
+static LongKernel pick_long(uint32_t g, uint32_t chains) {
     switch (g) {
-        case 16: return rmsnorm_long_kernel<ELEM, 16, FUSED>;
-        case 8: return rmsnorm_long_kernel<ELEM, 8, FUSED>;
-        case 4: return rmsnorm_long_kernel<ELEM, 4, FUSED>;
-        case 2: return rmsnorm_long_kernel<ELEM, 2, FUSED>;
-        default: return rmsnorm_long_kernel<ELEM, 1, FUSED>;
+        case 16: return rmsnorm_long_kernel<ELEM, 16, FUSED, 1>;
+        case 8: return rmsnorm_long_kernel<ELEM, 8, FUSED, 1>;
+        case 4: return rmsnorm_long_kernel<ELEM, 4, FUSED, 1>;
+        case 2:
+            return chains == 3 ? rmsnorm_long_kernel<ELEM, 2, FUSED, 3>
+                               : (chains == 2 ? rmsnorm_long_kernel<ELEM, 2, FUSED, 2>
+                                              : rmsnorm_long_kernel<ELEM, 2, FUSED, 1>);
+        default:
+            return chains == 3 ? rmsnorm_long_kernel<ELEM, 1, FUSED, 3>
+                               : (chains == 2 ? rmsnorm_long_kernel<ELEM, 1, FUSED, 2>
+                                              : rmsnorm_long_kernel<ELEM, 1, FUSED, 1>);
     }
 }
 
 int prepare_rmsnorm_long_kernels() {
     for (uint32_t g = 1; g <= kTile; g *= 2) {
-        const LongKernel kernels[4] = {pick_long<2, false>(g), pick_long<2, true>(g),
-                                       pick_long<4, false>(g), pick_long<4, true>(g)};
-        for (const LongKernel kernel : kernels) {
-            const int status = allow_full_shared_memory(reinterpret_cast<const void*>(kernel));
-            if (status != IOMB_OK) return status;
+        for (uint32_t chains = 1; chains <= kMaxChains; ++chains) {
+            const LongKernel kernels[4] = {pick_long<2, false>(g, chains), pick_long<2, true>(g, chains),
+                                           pick_long<4, false>(g, chains), pick_long<4, true>(g, chains)};
+            for (const LongKernel kernel : kernels) {
+                const int status = allow_full_shared_memory(reinterpret_cast<const void*>(kernel));
+                if (status != IOMB_OK) return status;
+            }
         }
     }
     return IOMB_OK;
@@ -775,24 +792,45 @@ int launch_rmsnorm_long(const RmsParams& base, uint32_t elem, bool fused, uint64
     // (a multiple of four tiles, so that every box starts on a 128-byte boundary of its slot)
     const uint32_t box_tiles = ((base.tile_cols + boxes - 1) / boxes + 3) / 4 * 4;
     const uint64_t slot_row_bytes = static_cast<uint64_t>(boxes) * box_tiles * kTile * elem;
-    auto slot_bytes = [&](uint32_t rows) { return long_slots(rows, fused) * rows * slot_row_bytes; };
-    auto fits = [&](uint32_t rows) { return slot_bytes(rows) + long_fixed_bytes(rows, fused) <= kSharedCap; };
-    if (!fits(1)) return IOMB_OK;                          // not served here
-    uint32_t g = kTile;
-    while (g > 1 && !fits(g)) g /= 2;
+    auto slot_bytes = [&](uint32_t rows, uint32_t chains) {
+        return long_slots(fused, chains) * rows * slot_row_bytes;
+    };
+    auto fits = [&](uint32_t rows, uint32_t chains) {
+        return slot_bytes(rows, chains) + long_fixed_bytes(rows, fused, chains) <= kSharedCap;
+    };
+    if (!fits(1, 1)) return IOMB_OK;                       // not served here
     // Few rows (decode steps): smaller groups spread the bands over more SMs.
     const uint64_t sms = static_cast<uint64_t>(sm_count() > 0 ? sm_count() : 148);
-    while (g > 1 && bands * (kTile / g) < sms) g /= 2;
+    uint32_t largest = kTile;
+    while (largest > 1 && bands * (kTile / largest) < sms) largest /= 2;
+    // Rows chaining at once on an SM are g * chains: about four keep up with HBM (measured:
+    // g 4 with one chain unfused, g 2 with two chains fused; g 2 with one chain runs at half
+    // the rate). Among the shapes that fit, take the one with the most, then the tallest
+    // group, then the fewest chains.
+    uint32_t g = 0, chains = 1, best = 0;
+    for (uint32_t rows = largest; rows >= 1; rows /= 2) {
+        for (uint32_t c = 1; c <= long_most_chains(rows, fused); ++c) {
+            if (!fits(rows, c)) continue;
+            const uint32_t chaining = rows * c < 4 ? rows * c : 4;
+            if (chaining > best) {
+                best = chaining;
+                g = rows;
+                chains = c;
+            }
+        }
+    }
+    if (g == 0) return IOMB_OK;
     const uint64_t scale_bytes = row_bytes / elem * 4;     // row 0 of every scale tile as FP32
     LongShape shape{};
     shape.boxes = boxes;
     shape.box_tiles = box_tiles;
-    const uint64_t walk_tiles = long_move_tiles_per_step(elem, g, fused);
+    const uint64_t walk_tiles = long_move_tiles_per_step(elem, g, fused, chains);
     shape.scale_in_regs = (base.tile_cols + walk_tiles - 1) / walk_tiles <= long_scale_steps(fused) ? 1u : 0u;
     shape.scale_in_smem = !shape.scale_in_regs
-                    && slot_bytes(g) + scale_bytes + long_fixed_bytes(g, fused) <= kSharedCap ? 1u : 0u;
-    const uint64_t smem_bytes = slot_bytes(g) + (shape.scale_in_smem ? scale_bytes : 0)
-            + long_fixed_bytes(g, fused);
+                    && slot_bytes(g, chains) + scale_bytes + long_fixed_bytes(g, fused, chains) <= kSharedCap
+            ? 1u : 0u;
+    const uint64_t smem_bytes = slot_bytes(g, chains) + (shape.scale_in_smem ? scale_bytes : 0)
+            + long_fixed_bytes(g, fused, chains);
 
     RmsParams p = base;
     p.group_rows = g;
@@ -804,8 +842,8 @@ int launch_rmsnorm_long(const RmsParams& base, uint32_t elem, bool fused, uint64
         return IOMB_OK;                                    // no tensor maps here: not served
     }
     LongKernel kernel = elem == 2
-            ? (fused ? pick_long<2, true>(g) : pick_long<2, false>(g))
-            : (fused ? pick_long<4, true>(g) : pick_long<4, false>(g));
+            ? (fused ? pick_long<2, true>(g, chains) : pick_long<2, false>(g, chains))
+            : (fused ? pick_long<4, true>(g, chains) : pick_long<4, false>(g, chains));
     const int prepared = allow_full_shared_memory(reinterpret_cast<const void*>(kernel));
     if (prepared != IOMB_OK) return prepared;
     // The CTAs of a launch start on neighbouring units (the groups of one band, then the
@@ -831,7 +869,7 @@ int launch_rmsnorm_long(const RmsParams& base, uint32_t elem, bool fused, uint64
     char text[160];
     snprintf(text, sizeof text,
              "rmsnorm_long_kernel<elem %u, rows %u, %s> %u chain(s), %u slots, scale %s, %u CTAs x %d, %u launch(es)",
-             elem, g, fused ? "fused" : "unfused", long_chains(g, fused), long_slots(g, fused),
+             elem, g, fused ? "fused" : "unfused", chains, long_slots(fused, chains),
              shape.scale_in_regs ? "in registers" : shape.scale_in_smem ? "in shared memory" : "through L1",
              static_cast<unsigned>(grid), kLongThreads, launches);
     note_launch(text);
