@@ -38,6 +38,7 @@ struct ViewBox {
 struct QueueBox {
     std::unique_ptr<iom::DeviceOps> ops;
     std::size_t credits = 1;      // operations the queue keeps in flight before it parks one
+    int ordinal = 0;              // the device's CUDA ordinal (the runner's own events live there)
 };
 
 int classify(std::exception_ptr failure) {
@@ -156,6 +157,7 @@ void* iomb_backend_queue_create(void* device) {
         iom::Device& owner = *static_cast<DeviceBox*>(device)->device;
         box->ops = owner.create_ops();
         box->credits = owner.queue_config().max_in_flight_per_queue;
+        box->ordinal = static_cast<int>(owner.backend_device());
         return box.release();
     });
 }
@@ -221,6 +223,8 @@ int iomb_backend_run(void* queue, const iomb_backend_op* operations, uint32_t co
             throw std::invalid_argument("iomb_backend_run: null argument");
         }
         iom::DeviceOps& ops = *static_cast<QueueBox*>(queue)->ops;
+        // The current device is per host thread: a caller's worker thread starts on device 0.
+        check_cuda("cudaSetDevice", cudaSetDevice(static_cast<QueueBox*>(queue)->ordinal));
         const cudaStream_t stream = static_cast<cudaStream_t>(iom::b200::native_stream(ops));
         if (stream == nullptr) throw std::invalid_argument("not a queue of the B200 backend");
         using clock = std::chrono::steady_clock;
