@@ -801,6 +801,7 @@ public:
         std::lock_guard<std::mutex> order(submission_order_mutex_);
         if (!capturing_) throw std::logic_error("the queue is not recording");
         capturing_ = false;
+        device_->activate();
         auto recorded = std::make_shared<b200::CapturedSequence>();
         check_cuda("cudaStreamEndCapture", cudaStreamEndCapture(stream_, &recorded->graph));
         check_cuda("cudaGraphInstantiate", cudaGraphInstantiate(&recorded->exec, recorded->graph, 0));
