@@ -163,7 +163,13 @@ int iomb_prepare_device(void* stream);
  * (src/shared/gpu_queue_operations.inl:206-267,841-869; src/shared/standard_tiled_rmsnorm.inl:437-637);
  * arithmetic of rmsnorm_plane (src/cpu/queue.cpp:1145-1244): FP32 sum of rounded
  * squares, sum/F, +eps, 1/sqrtf (true division), (x*inv)*w, NaN sign cleared,
- * one RNE encode. Leaves: BF16, F32. `order` is an iomb_rms_order.
+ * one RNE encode. Leaves: BF16, F32. `order` is an iomb_rms_order. Any row length is
+ * served (the reference admits any F): rows of up to 2048 values and the sequential order
+ * by a kernel that stages whole row groups in shared memory, longer rows in the lane order
+ * by a pipelined kernel that fetches with bulk tensor copies (a call may then issue several
+ * launches on `stream`, see iomb_last_launch), rows beyond either one's shared memory from
+ * global memory directly. The output shares no owner with an input
+ * (src/device_ops_rmsnorm.cpp:75-127).
  */
 int iomb_rmsnorm(const iomb_view* x, const iomb_view* scale, const iomb_view* out,
                  float eps, int order, void* stream);
