@@ -127,14 +127,18 @@ def test_rmsnorm_special_rows(gpu, dtype, specials, order):
 
 @pytest.mark.parametrize("dtype,order", [(DataType.BF16, RMS_LANES16), (DataType.BF16, RMS_SEQUENTIAL),
                                          (DataType.F32, RMS_SEQUENTIAL)])
-@pytest.mark.parametrize("features", [4100, 8192])
-def test_rmsnorm_long_rows_special_values(gpu, dtype, order, features):
+@pytest.mark.parametrize("features,rows", [(4100, 40), (8192, 40),
+                                           # enough bands for groups of 8 and of 16 rows, whose
+                                           # chain threads own two columns and use packed
+                                           # arithmetic (a packed product feeding a packed sum
+                                           # must not be contracted)
+                                           (4100, 1200), (2064, 2400)])
+def test_rmsnorm_long_rows_special_values(gpu, dtype, order, features, rows):
     """Rows that defeat the clean-row shortcut, at lengths served by the band kernel:
     all-zero rows with eps 0, infinities, NaNs, overflowing and vanishing sums,
     and a scale row holding a NaN and an infinity."""
     device, queue = gpu
     rng = np.random.default_rng(features + int(dtype) + order)
-    rows = 40
     payload = random_payload(rng, (rows, features), dtype, "normal")
     bits = payload.view(np.uint16 if dtype == DataType.BF16 else np.uint32)
     code = (lambda v: np.float32(v).view(np.uint32) >> 16) if dtype == DataType.BF16 \
