@@ -55,16 +55,20 @@ struct LongShape {
     uint32_t boxes;           // copies per unit and operand: boxes * box_tiles >= tile_cols
 };
 
-// acc += fl(x * x) for two lanes: one packed multiplication and one packed addition, each
-// lane rounded separately exactly like the scalar pair.
+// acc += fl(x * x) for two lanes: two scalar multiplications, each rounded, and one packed
+// addition that rounds each lane like the scalar one. The products are not packed: a packed
+// product feeding a packed sum is contracted into a fused multiply-add by the assembler
+// whatever the rounding qualifiers say (F32 rows then differ from the separately rounded
+// recurrence of src/cpu/queue.cpp:1187-1196 in their last bits).
 __device__ __forceinline__ void square_add_pair(float& a0, float& a1, float x0, float x1) {
-    asm("{\n\t.reg .b64 acc, x, sq;\n\t"
+    const float s0 = __fmul_rn(x0, x0);
+    const float s1 = __fmul_rn(x1, x1);
+    asm("{\n\t.reg .b64 acc, add;\n\t"
         "mov.b64 acc, {%0, %1};\n\t"
-        "mov.b64 x, {%2, %3};\n\t"
-        "mul.rn.f32x2 sq, x, x;\n\t"
-        "add.rn.f32x2 acc, acc, sq;\n\t"
+        "mov.b64 add, {%2, %3};\n\t"
+        "add.rn.f32x2 acc, acc, add;\n\t"
         "mov.b64 {%0, %1}, acc;\n\t}"
-        : "+f"(a0), "+f"(a1) : "f"(x0), "f"(x1));
+        : "+f"(a0), "+f"(a1) : "f"(s0), "f"(s1));
 }
 
 // Geometry shared by the kernel and its launcher, for groups of g rows.

@@ -25,6 +25,8 @@ SHAPES = [(1, 1), (15, 17), (16, 16), (17, 33), (2, 3, 16, 31), (33, 15), (4, 25
           # long rows: whole bands streamed by one CTA (more bands than SMs, a band
           # longer than shared memory, ragged last band in every plane)
           (4800, 2064), (4000, 8200), (2, 170, 3000), (7, 20000), (3, 40000), (2400, 4096),
+          # groups of two rows with two chains (rows too long for taller groups)
+          (320, 12288),
           # a row beyond every staging capacity: the unstaged kernel
           (3, 100000)]
 
@@ -174,6 +176,36 @@ def test_rmsnorm_long_rows_special_values(gpu, dtype, order, features, rows):
             assert np.array_equal(download(do), out.storage)
 
 
+@pytest.mark.parametrize("features,rows", [(2304, 2400), (4100, 1200), (2064, 2400), (8192, 640)])
+def test_f32_lane_order_does_not_depend_on_the_group_height(gpu, features, rows):
+    """F32 in the lane order has no reference build to compare with bit for bit, so its own
+    consistency is pinned: many rows (tall groups, whose chain threads own two columns and add
+    with a packed instruction) give, row by row, the bits of the same rows run as a small
+    tensor (groups of one row, scalar arithmetic). A product contracted into the sum would
+    show here: F32 squares are not exact."""
+    device, queue = gpu
+    rng = np.random.default_rng(features)
+    x = seeded((rows, features), DataType.F32, rng)
+    w = seeded((1, features), DataType.F32, rng)
+    out = seeded((rows, features), DataType.F32, rng)
+    dx, dw, do = upload(device, x), upload(device, w), upload(device, out)
+    run(queue, queue.rmsnorm(dx.view(), dw.view(), do.view(), 1e-6, order=RMS_LANES16))
+    tall = HostTensor((rows, features), DataType.F32, fill=None)
+    tall.storage[:] = download(do)
+    tall_rows = tall.view().copy_to_host().view(np.uint32).reshape(rows, features)
+    few = 32
+    values = x.view().copy_to_host().view(np.uint32).reshape(rows, features)
+    small_x = HostTensor((few, features), DataType.F32).poison()
+    small_x.view().copy_from_host(values[:few].copy())
+    small_out = HostTensor((few, features), DataType.F32).poison()
+    dsx, dso = upload(device, small_x), upload(device, small_out)
+    run(queue, queue.rmsnorm(dsx.view(), dw.view(), dso.view(), 1e-6, order=RMS_LANES16))
+    got = HostTensor((few, features), DataType.F32, fill=None)
+    got.storage[:] = download(dso)
+    small_rows = got.view().copy_to_host().view(np.uint32).reshape(few, features)
+    assert np.array_equal(tall_rows[:few], small_rows)
+
+
 def test_rmsnorm_rejections(gpu):
     device, queue = gpu
     x = device.create_tensor(HostTensor((16, 32), DataType.BF16).spec)
@@ -194,7 +226,10 @@ def test_rmsnorm_rejections(gpu):
 @pytest.mark.parametrize("shape", [(17, 33), (64, 2048), (3, 16, 8192), (2, 3, 5, 100),
                                    # long rows: the pipelined kernel (more units than SMs,
                                    # ragged last band and last tile, several planes)
-                                   (1200, 8200), (2, 170, 3000), (7, 20000), (3, 40000), (2, 100000)])
+                                   (1200, 8200), (2, 170, 3000), (7, 20000), (3, 40000), (2, 100000),
+                                   # fused groups of 4 and of 8 rows (one chain), and of one
+                                   # row with two chains
+                                   (640, 4096), (2400, 2304), (320, 12288)])
 @pytest.mark.parametrize("order", [RMS_LANES16, RMS_SEQUENTIAL])
 def test_add_rmsnorm_equals_add_then_rmsnorm(gpu, dtype, shape, order):
     """The fused entry stores the rounded sum and normalises the rounded value."""
